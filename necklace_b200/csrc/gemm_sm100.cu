@@ -1,0 +1,546 @@
+// bf16 GEMM for sm_100a: C[M,N] = epilogue(alpha * A[M,K] * B[N,K]^T).
+//
+// Persistent, warp-specialised kernel, one CTA per SM:
+//   warp 0      TMA producer  (cp.async.bulk.tensor, 128-byte swizzle, per-CTA
+//               loads only; no cluster multicast)
+//   warp 1      tcgen05.mma issuer (one thread), owns the TMEM allocation
+//   warps 2..5  epilogue: tcgen05.ld -> registers -> fused math -> global
+// The accumulator (128 x BN fp32) lives in TMEM and is double-buffered, so the
+// epilogue of tile i overlaps the main loop of tile i+1.
+//
+// Both operands may be K-major (contraction index contiguous in memory) or
+// MN-major (the M / N index contiguous), which covers forward (X W^T), data
+// gradient (dY W) and weight gradient (dY^T X) of a linear layer without any
+// transpose pass.  This replaces the cuBLAS call under torch's F.linear that the
+// reference's tensor-parallel layers use (necklace/frmwrk/pytorch/mpnn/layers.py:239-249,
+// :314-328).
+//
+// All waits are bounded; on a timeout the kernel records a code in
+// `status`, releases its TMEM and returns.
+#include "ptx.cuh"
+#include "nkb_api.h"
+
+namespace nkb {
+
+constexpr int BM = 128;
+constexpr int BK = 64;  // 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int A_STAGE_BYTES = BM * BK * 2;
+constexpr int GEMM_THREADS = 192;
+
+struct GemmArgs {
+  int M, N, K;
+  void* C;
+  long long ldc;
+  int c_fp32;      // 1: C is float, 0: C is bf16
+  int accumulate;  // 1: C += result
+  float alpha;
+  const float* alpha_dev;     // optional device scalar multiplied into alpha
+  const __nv_bfloat16* bias;  // [N] or null
+  const __nv_bfloat16* res;   // [M, ldres] or null, added after the activation
+  long long ldres;
+  int epi;                    // NKB_EPI_*
+  __nv_bfloat16* aux_out;     // gelu fwd: pre-activation saved here, [M, ldaux]
+  const __nv_bfloat16* aux_in;  // gelu bwd: pre-activation read from here
+  long long ldaux;
+  int num_m_blocks, num_n_blocks;
+  int* status;
+  // Optional row-block readiness flags (all-gather fused in front of the GEMM):
+  // rows [i*rows_per_flag, (i+1)*rows_per_flag) of A may be read once
+  // ready_flags[i] >= ready_target.  Null = no waiting.
+  const int* ready_flags;
+  int rows_per_flag;
+  int ready_target;
+};
+
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  float u = k0 * (x + k1 * x * x * x);
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
+  return 0.5f * x * (1.f + t);
+}
+__device__ __forceinline__ float gelu_tanh_grad(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  float x2 = x * x;
+  float u = k0 * (x + k1 * x * x2);
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
+  float du = k0 * (1.f + 3.f * k1 * x2);
+  return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * du;
+}
+
+__device__ __forceinline__ void set_error(int* status, volatile int* abort_flag, int code) {
+  *abort_flag = 1;
+  if (status) atomicCAS(status, 0, code);
+}
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const GemmArgs g) {
+  constexpr int B_STAGE_BYTES = BN * BK * 2;
+  constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+  constexpr int STAGES = (BN == 256) ? 4 : 6;
+  constexpr uint32_t TMEM_COLS = (2 * BN <= 512) ? ((2 * BN < 32) ? 32 : 2 * BN) : 512;
+  static_assert(BN == 64 || BN == 128 || BN == 256, "BN");
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                              ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* acc_full = empty_bar + STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = g.num_m_blocks * g.num_n_blocks;
+  const int KB = (g.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 128);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const int mb = t % g.num_m_blocks, nb = t / g.num_m_blocks;
+        const int m0 = mb * BM, n0 = nb * BN;
+        if (g.ready_flags) {
+          int f0 = m0 / g.rows_per_flag;
+          int m_last = min(m0 + BM, g.M) - 1;
+          int f1 = m_last / g.rows_per_flag;
+          for (int f = f0; f <= f1 && ok; ++f) {
+            if (!wait_flag_ge(g.ready_flags + f, g.ready_target)) {
+              set_error(g.status, abort_flag, NKB_ERR_FLAG_WAIT);
+              ok = false;
+            }
+          }
+          if (!ok) break;
+          // data landed through the generic proxy of other SMs / GPUs; TMA reads
+          // it through the async proxy
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+        }
+        for (int kb = 0; kb < KB; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
+            set_error(g.status, abort_flag, NKB_ERR_EMPTY_WAIT);
+            ok = false;
+            break;
+          }
+          uint8_t* sA = smem + stage * STAGE_BYTES;
+          uint8_t* sB = sA + A_STAGE_BYTES;
+          mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+          if constexpr (!A_MN) {
+            tma_load_2d(sA, &tmA, &full_bar[stage], kb * BK, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              tma_load_2d(sA + j * (64 * BK * 2), &tmA, &full_bar[stage], m0 + j * 64, kb * BK);
+          }
+          if constexpr (!B_MN) {
+            tma_load_2d(sB, &tmB, &full_bar[stage], kb * BK, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(sB + j * (64 * BK * 2), &tmB, &full_bar[stage], n0 + j * 64, kb * BK);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag)) {
+          set_error(g.status, abort_flag, NKB_ERR_ACC_FREE);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < KB; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
+            set_error(g.status, abort_flag, NKB_ERR_TMA_WAIT);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t aA = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t aB = aA + A_STAGE_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            uint64_t da, db;
+            if constexpr (!A_MN)
+              da = umma_desc_sw128(aA + k * (UMMA_K * 2), 16, 1024);
+            else
+              da = umma_desc_sw128(aA + k * (UMMA_K * 128), 64 * BK * 2, 1024);
+            if constexpr (!B_MN)
+              db = umma_desc_sw128(aB + k * (UMMA_K * 2), 16, 1024);
+            else
+              db = umma_desc_sw128(aB + k * (UMMA_K * 128), 64 * BK * 2, 1024);
+            umma_bf16_ss(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);  // frees the stage when these MMAs retire
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        umma_commit(&acc_full[acc]);
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int lane_grp = warp & 3;  // TMEM lanes this warp may touch: 32*lane_grp ..
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const float alpha = g.alpha_dev ? g.alpha * __ldg(g.alpha_dev) : g.alpha;
+    const bool vec_ok = ((g.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(g.C) & 15) == 0) &&
+                        (!g.res || (((g.ldres & 7) == 0) &&
+                                    ((reinterpret_cast<uintptr_t>(g.res) & 15) == 0))) &&
+                        (!g.aux_out || (((g.ldaux & 7) == 0) &&
+                                        ((reinterpret_cast<uintptr_t>(g.aux_out) & 15) == 0))) &&
+                        (!g.aux_in || (((g.ldaux & 7) == 0) &&
+                                       ((reinterpret_cast<uintptr_t>(g.aux_in) & 15) == 0))) &&
+                        (!g.bias || ((reinterpret_cast<uintptr_t>(g.bias) & 15) == 0));
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+      const int mb = t % g.num_m_blocks, nb = t / g.num_m_blocks;
+      const int row = mb * BM + lane_grp * 32 + lane;
+      const int n0 = nb * BN;
+      if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag)) {
+        set_error(g.status, abort_flag, NKB_ERR_ACC_WAIT);
+        break;
+      }
+      tc_fence_after();
+      const uint32_t t_addr = tmem_base + (uint32_t(lane_grp * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_addr + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (row < g.M && col0 < g.N) {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * alpha;
+          const bool full = vec_ok && (col0 + 32 <= g.N);
+          if (full) {
+            if (g.bias) {
+              const uint4* bp = reinterpret_cast<const uint4*>(g.bias + col0);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint4 b = __ldg(bp + q);
+                uint32_t w[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  float2 f = unpack_bf16x2(w[j]);
+                  v[q * 8 + 2 * j] += f.x;
+                  v[q * 8 + 2 * j + 1] += f.y;
+                }
+              }
+            }
+            if (g.epi == NKB_EPI_GELU_FWD) {
+              uint4* ap = reinterpret_cast<uint4*>(g.aux_out + (long long)row * g.ldaux + col0);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint4 o;
+                o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+                o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+                o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+                o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+                ap[q] = o;
+              }
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
+            } else if (g.epi == NKB_EPI_GELU_BWD) {
+              const uint4* ap =
+                  reinterpret_cast<const uint4*>(g.aux_in + (long long)row * g.ldaux + col0);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint4 z = __ldg(ap + q);
+                uint32_t w[4] = {z.x, z.y, z.z, z.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  float2 f = unpack_bf16x2(w[j]);
+                  v[q * 8 + 2 * j] *= gelu_tanh_grad(f.x);
+                  v[q * 8 + 2 * j + 1] *= gelu_tanh_grad(f.y);
+                }
+              }
+            } else if (g.epi == NKB_EPI_RELU) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = fmaxf(v[i], 0.f);
+            }
+            if (g.res) {
+              const uint4* rp =
+                  reinterpret_cast<const uint4*>(g.res + (long long)row * g.ldres + col0);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint4 z = __ldg(rp + q);
+                uint32_t w[4] = {z.x, z.y, z.z, z.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  float2 f = unpack_bf16x2(w[j]);
+                  v[q * 8 + 2 * j] += f.x;
+                  v[q * 8 + 2 * j + 1] += f.y;
+                }
+              }
+            }
+            if (g.c_fp32) {
+              float4* cp = reinterpret_cast<float4*>(reinterpret_cast<float*>(g.C) +
+                                                     (long long)row * g.ldc + col0);
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                float4 o = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+                if (g.accumulate) {
+                  float4 p = cp[q];
+                  o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
+                }
+                cp[q] = o;
+              }
+            } else {
+              uint4* cp = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(g.C) +
+                                                   (long long)row * g.ldc + col0);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                if (g.accumulate) {
+                  uint4 p = cp[q];
+                  uint32_t w[4] = {p.x, p.y, p.z, p.w};
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    float2 f = unpack_bf16x2(w[j]);
+                    v[q * 8 + 2 * j] += f.x;
+                    v[q * 8 + 2 * j + 1] += f.y;
+                  }
+                }
+                uint4 o;
+                o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+                o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+                o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+                o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+                cp[q] = o;
+              }
+            }
+          } else {
+            // ragged edge or unaligned views: scalar path with bounds checks
+            for (int i = 0; i < 32; ++i) {
+              const int col = col0 + i;
+              if (col >= g.N) break;
+              float x = v[i];
+              if (g.bias) x += __bfloat162float(g.bias[col]);
+              if (g.epi == NKB_EPI_GELU_FWD) {
+                g.aux_out[(long long)row * g.ldaux + col] = __float2bfloat16(x);
+                x = gelu_tanh(x);
+              } else if (g.epi == NKB_EPI_GELU_BWD) {
+                x *= gelu_tanh_grad(__bfloat162float(g.aux_in[(long long)row * g.ldaux + col]));
+              } else if (g.epi == NKB_EPI_RELU) {
+                x = fmaxf(x, 0.f);
+              }
+              if (g.res) x += __bfloat162float(g.res[(long long)row * g.ldres + col]);
+              if (g.c_fp32) {
+                float* cp = reinterpret_cast<float*>(g.C) + (long long)row * g.ldc + col;
+                *cp = g.accumulate ? (*cp + x) : x;
+              } else {
+                __nv_bfloat16* cp =
+                    reinterpret_cast<__nv_bfloat16*>(g.C) + (long long)row * g.ldc + col;
+                *cp = __float2bfloat16(g.accumulate ? (__bfloat162float(*cp) + x) : x);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&acc_empty[acc]);
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+  }
+
+  // ------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    if (*abort_flag) {
+      // give copies/MMAs that are still in flight time to land before the
+      // shared memory and TMEM they target are released
+      for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+    }
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+            cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// 2-D bf16 tensor map: inner extent `inner` (contiguous), outer extent `outer`
+// with a row pitch of `ld` elements; box = box_inner x box_outer, 128B swizzle.
+int make_tmap_bf16_2d(CUtensorMap* out, const void* base, long long inner, long long outer,
+                      long long ld, int box_inner, int box_outer) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -1;
+  cuuint64_t gdim[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+  cuuint64_t gstride[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gdim, gstride,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -(int)r - 1000;
+}
+
+static int g_num_sms = 0;
+int num_sms() {
+  if (!g_num_sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (g_num_sms <= 0) g_num_sms = 148;
+  }
+  return g_num_sms;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs& g, int max_ctas,
+                       cudaStream_t stream) {
+  constexpr int STAGES = (BN == 256) ? 4 : 6;
+  constexpr int smem_bytes = STAGES * (A_STAGE_BYTES + BN * BK * 2) + 1024 + 256;
+  static bool configured = false;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
+  if (!configured) {
+    cudaError_t e =
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  g.num_m_blocks = (g.M + BM - 1) / BM;
+  g.num_n_blocks = (g.N + BN - 1) / BN;
+  int tiles = g.num_m_blocks * g.num_n_blocks;
+  int ctas = num_sms();
+  if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
+  if (tiles < ctas) ctas = tiles;
+  kern<<<ctas, GEMM_THREADS, smem_bytes, stream>>>(tmA, tmB, g);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace nkb
+
+using namespace nkb;
+
+extern "C" int nkb_gemm_bf16(const void* A, long long lda, int a_mn, const void* B, long long ldb,
+                             int b_mn, void* C, long long ldc, int c_fp32, int accumulate, int M,
+                             int N, int K, float alpha, const void* bias, const void* res,
+                             long long ldres, int epi, void* aux, long long ldaux, int* status,
+                             const int* ready_flags, int rows_per_flag, int ready_target,
+                             int max_ctas, int bn_hint, const float* alpha_dev, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return -2;
+  // TMA needs 16-byte aligned bases and row pitches
+  if ((lda & 7) || (ldb & 7) || (reinterpret_cast<uintptr_t>(A) & 15) ||
+      (reinterpret_cast<uintptr_t>(B) & 15))
+    return -3;
+  GemmArgs g;
+  g.M = M; g.N = N; g.K = K;
+  g.C = C; g.ldc = ldc; g.c_fp32 = c_fp32; g.accumulate = accumulate; g.alpha = alpha; g.alpha_dev = alpha_dev;
+  g.bias = static_cast<const __nv_bfloat16*>(bias);
+  g.res = static_cast<const __nv_bfloat16*>(res);
+  g.ldres = ldres;
+  g.epi = epi;
+  g.aux_out = (epi == NKB_EPI_GELU_FWD) ? static_cast<__nv_bfloat16*>(aux) : nullptr;
+  g.aux_in = (epi == NKB_EPI_GELU_BWD) ? static_cast<const __nv_bfloat16*>(aux) : nullptr;
+  g.ldaux = ldaux;
+  g.status = status;
+  g.ready_flags = ready_flags;
+  g.rows_per_flag = rows_per_flag > 0 ? rows_per_flag : 1;
+  g.ready_target = ready_target;
+
+  // Tile width: 256 unless N is small or the 256-wide grid would leave most SMs idle.
+  int BN = 256;
+  if (bn_hint == 128 || bn_hint == 256) {
+    BN = bn_hint;
+  } else {
+    long long mblk = (M + BM - 1) / BM;
+    long long t256 = mblk * ((N + 255) / 256);
+    long long t128 = mblk * ((N + 127) / 128);
+    int sms = num_sms();
+    // rounds of the persistent loop, in units of a 128-wide tile
+    long long r256 = ((t256 + sms - 1) / sms) * 2;
+    long long r128 = ((t128 + sms - 1) / sms);
+    if (N <= 128 || r128 < r256) BN = 128;
+  }
+
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (!a_mn) rc = make_tmap_bf16_2d(&tmA, A, K, M, lda, BK, BM);
+  else rc = make_tmap_bf16_2d(&tmA, A, M, K, lda, 64, BK);
+  if (rc) return rc;
+  if (!b_mn) rc = make_tmap_bf16_2d(&tmB, B, K, N, ldb, BK, BN);
+  else rc = make_tmap_bf16_2d(&tmB, B, N, K, ldb, 64, BK);
+  if (rc) return rc;
+
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define NKB_DISPATCH(BN_)                                                              \
+  if (!a_mn && !b_mn) return launch_gemm<BN_, false, false>(tmA, tmB, g, max_ctas, s); \
+  if (!a_mn && b_mn) return launch_gemm<BN_, false, true>(tmA, tmB, g, max_ctas, s);   \
+  if (a_mn && !b_mn) return launch_gemm<BN_, true, false>(tmA, tmB, g, max_ctas, s);   \
+  return launch_gemm<BN_, true, true>(tmA, tmB, g, max_ctas, s);
+  if (BN == 256) { NKB_DISPATCH(256) }
+  NKB_DISPATCH(128)
+#undef NKB_DISPATCH
+}

@@ -1,0 +1,134 @@
+// C ABI of the necklace_b200 native library (loaded from Python with ctypes).
+//
+// Conventions: every function returns 0 on success, a positive cudaError_t or a
+// negative library error.  Pointers are device pointers unless named host_*.
+// `stream` is a cudaStream_t passed as void*.  Nothing here allocates device
+// memory: callers own inputs, outputs and scratch.
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// GEMM epilogue selectors
+#define NKB_EPI_NONE 0
+#define NKB_EPI_GELU_FWD 1  // aux <- (acc+bias) ; C <- gelu(acc+bias)
+#define NKB_EPI_GELU_BWD 2  // C <- acc * gelu'(aux)
+#define NKB_EPI_RELU 3
+
+// ---- gemm_sm100.cu ---------------------------------------------------------
+// C[M,N] = epi(alpha * A[M,K] * B[N,K]^T + bias) + res.  a_mn / b_mn = 1 when the
+// operand is stored with its M / N index contiguous ([K][ld] in memory).
+int nkb_gemm_bf16(const void* A, long long lda, int a_mn, const void* B, long long ldb, int b_mn,
+                  void* C, long long ldc, int c_fp32, int accumulate, int M, int N, int K,
+                  float alpha, const void* bias, const void* res, long long ldres, int epi,
+                  void* aux, long long ldaux, int* status, const int* ready_flags,
+                  int rows_per_flag, int ready_target, int max_ctas, int bn_hint,
+                  const float* alpha_dev, void* stream);
+
+// ---- norm.cu ---------------------------------------------------------------
+// rms = 1: RMSNorm (no mean, no bias).  stats: [rows,2] fp32 (mean, rstd).
+int nkb_norm_fwd(const void* x, const void* w, const void* b, void* y, float* stats, int rows,
+                 int C, float eps, int rms, void* stream);
+int nkb_norm_bwd_dx(const void* dy, const void* x, const void* w, const float* stats, void* dx,
+                    int rows, int C, int rms, void* stream);
+// Column sums over rows: acc[0][c] += sum_r dy[r,c]*xhat[r,c] (if x) ; acc[1][c] += sum_r dy[r,c].
+// `acc` is fp32 [2][C] scratch that must be zero on entry.
+int nkb_colsum(const void* dy, const void* x, const float* stats, float* acc, int rows, int C,
+               long long ld, int rms, void* stream);
+// out_bf16[i] = (accumulate ? out[i] : 0) + acc[i]
+int nkb_f32_to_bf16(const float* src, void* dst, long long n, int accumulate, void* stream);
+
+// ---- loss_embed.cu ---------------------------------------------------------
+// logits [T, ld] bf16 (first V columns valid) are overwritten with
+// dlogits = (softmax - onehot) * grad_scale ; columns >= V get 0 ; losses[t] = -log p[target].
+// Rows with target < 0 are ignored (loss 0, grad 0).
+int nkb_ce_fwd_bwd(void* logits, const long long* targets, float* losses, int T, int V,
+                   long long ld, float grad_scale, void* stream);
+// Two-phase form for a vocabulary split over ranks: local stats [T,3] = (max, sumexp, target logit or 0)
+int nkb_ce_stats(const void* logits, const long long* targets, float* stats, int T, int V,
+                 long long ld, int vocab_start, void* stream);
+// grads from global (max, sumexp) per row: stats_g [T,2]
+int nkb_ce_grad(void* logits, const long long* targets, const float* stats_g, int T, int V,
+                long long ld, int vocab_start, float grad_scale, void* stream);
+int nkb_embed_fwd(const long long* idx, const void* wte, const void* wpe, void* out, int T, int S,
+                  int C, int vocab_start, int vocab_rows, void* stream);
+int nkb_embed_bwd(const long long* idx, const void* dout, void* dwte, void* dwpe, int T, int S,
+                  int C, int vocab_start, int vocab_rows, void* stream);
+
+// ---- optim_quant.cu --------------------------------------------------------
+// Adam / AdamW on flat buffers; master fp32, optional bf16 copy out. grad dtype: 0 bf16, 1 fp32.
+int nkb_adam_flat(float* master, float* m, float* v, const void* grad, int grad_fp32,
+                  void* param_bf16, long long n, float lr, float beta1, float beta2, float eps,
+                  float weight_decay, float bias_c1, float bias_c2, float grad_scale,
+                  void* stream);
+// SGD with momentum on flat buffers (torch.optim.SGD semantics, dampening 0).
+int nkb_sgd_flat(float* master, float* mom, const void* grad, int grad_fp32, void* param_bf16,
+                 long long n, float lr, float momentum, float weight_decay, float grad_scale,
+                 int first_step, void* stream);
+// 2-bit threshold codec with error feedback over a flat fp32/bf16 vector:
+//   a = g[i] + residual[i]; code 01 if a >= thr, 10 if a <= -thr, else 00;
+//   residual[i] = a - decode(code); 16 codes per uint32, element i in bits [2(i%16), 2(i%16)+2).
+int nkb_quant2_flat(const void* g, int g_fp32, float* residual, uint32_t* codes, long long n,
+                    float thr, void* stream);
+int nkb_dequant2_flat(const uint32_t* codes, void* out, int out_fp32, long long n, float thr,
+                      float scale, int accumulate, void* stream);
+// Matrix form with the packing of the reference kernels (16 rows -> one word):
+// codes[x, y] packs A[16x+i, y], i = 0..15.  A, R: fp32 [n, ncol]; codes: [ceil(n/16), ncol].
+int nkb_quant2_matrix(const float* A, uint32_t* codes, float* R, int n, int ncol, float thr,
+                      void* stream);
+int nkb_dequant2_matrix(float* A, const uint32_t* codes, int n, int ncol, float thr, void* stream);
+// flat helpers
+int nkb_scale_cast(const void* src, int src_fp32, void* dst, int dst_fp32, long long n,
+                   float scale, int accumulate, void* stream);
+int nkb_sumsq(const void* src, int src_fp32, long long n, float* out_accum, void* stream);
+
+// ---- attention_sm100.cu ------------------------------------------------------
+// Causal (or full) multi-head attention, head dim 64 or 128.  q,k,v,o: bf16 with
+// element strides (batch, head, seq); the head dim is contiguous.  lse: [B,H,S] fp32.
+int nkb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int H,
+                 int S, int D, long long sb, long long sh, long long ss, long long ob,
+                 long long oh, long long os, float scale, int causal, int* status, void* stream);
+int nkb_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                 const float* lse, void* dq, void* dk, void* dv, float* delta, float* dq_acc,
+                 int B, int H, int S, int D, long long sb, long long sh, long long ss,
+                 long long ob, long long oh, long long os, float scale, int causal, int* status,
+                 void* stream);
+
+// ---- comm.cu -----------------------------------------------------------------
+// Peer-memory collectives.  `peers` is a device array of `world` pointers to the
+// same symmetric buffer on every rank (index = rank in the group); `flags` is a
+// device array of `world` pointers to each rank's flag pad (int32).  `epoch` is a
+// device counter owned by the caller and advanced by the kernels.
+int nkb_barrier(int** flags, int rank, int world, int slot, int* epoch_ctr, int* status,
+                void* stream);
+int nkb_allreduce(void** peers, int** flags, long long offset_bytes, long long n, int dtype_fp32,
+                  int rank, int world, float scale, int* epoch_ctr, int* status, int max_ctas,
+                  void* stream);
+int nkb_allgather(void** peers, int** flags, long long offset_bytes, long long shard_bytes,
+                  int rank, int world, int* epoch_ctr, int* status, int max_ctas, void* stream);
+// 2-bit compressed gradient all-reduce with error feedback (one kernel):
+// quantise g(+residual) into this rank's code buffer, exchange, each rank decodes and
+// sums its shard from all peers, scales, publishes the reduced shard to every peer.
+int nkb_dp_quant_allreduce(const void* g, int g_fp32, float* residual, void** code_peers,
+                           void** out_peers, int** flags, long long n, float thr, float scale,
+                           int out_fp32, int rank, int world, int* epoch_ctr, int* status,
+                           int max_ctas, void* stream);
+// ZeRO: reduce-scatter of bf16 gradients fused with Adam on this rank's shard.
+int nkb_rs_adam(void** grad_peers, int** flags, long long grad_offset_bytes, long long n_total,
+                float* master, float* m, float* v, void* param_shard_bf16, int rank, int world,
+                float lr, float beta1, float beta2, float eps, float weight_decay, float bias_c1,
+                float bias_c2, float grad_scale, int* epoch_ctr, int* status, int max_ctas,
+                void* stream);
+int nkb_rs_sgd(void** grad_peers, int** flags, long long grad_offset_bytes, long long n_total,
+               float* master, float* mom, void* param_shard_bf16, int rank, int world, float lr,
+               float momentum, float weight_decay, float grad_scale, int first_step,
+               int* epoch_ctr, int* status, int max_ctas, void* stream);
+
+int nkb_num_sms(void);
+const char* nkb_build_info(void);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,275 @@
+// LayerNorm / RMSNorm forward and backward for bf16 activations (fp32 math).
+//
+// One warp owns a row and keeps it in registers, so the forward reads x once and
+// writes y once; the backward reads dy and x once and writes dx once.  Weight /
+// bias gradients are column sums produced by nkb_colsum into an fp32 scratch row.
+// These replace torch.nn.LayerNorm / RMSNorm calls in the transformer configs;
+// the reference itself has no norm kernel.
+#include "ptx.cuh"
+#include "nkb_api.h"
+
+namespace nkb {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// NCH chunks of 256 elements (32 lanes x 8 bf16) cover a row of C <= NCH*256.
+template <int NCH>
+__global__ void __launch_bounds__(128)
+norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                const __nv_bfloat16* __restrict__ b, __nv_bfloat16* __restrict__ y,
+                float* __restrict__ stats, int rows, int C, float eps, int rms) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const uint4* xp = reinterpret_cast<const uint4*>(x + (long long)row * C);
+  uint4 xv[NCH];
+  float sum = 0.f;
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int e = c * 256 + lane * 8;
+    if (e < C) {
+      xv[c] = ld_nc_v4(xp + c * 32 + lane);
+      uint32_t u[4] = {xv[c].x, xv[c].y, xv[c].z, xv[c].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f = unpack_bf16x2(u[j]);
+        sum += f.x + f.y;
+      }
+    }
+  }
+  float mean = 0.f;
+  if (!rms) mean = warp_sum(sum) / C;
+  float var = 0.f;
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int e = c * 256 + lane * 8;
+    if (e < C) {
+      uint32_t u[4] = {xv[c].x, xv[c].y, xv[c].z, xv[c].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f = unpack_bf16x2(u[j]);
+        float d0 = f.x - mean, d1 = f.y - mean;
+        var += d0 * d0 + d1 * d1;
+      }
+    }
+  }
+  var = warp_sum(var) / C;
+  const float rstd = rsqrtf(var + eps);
+  if (lane == 0 && stats) {
+    stats[2 * row] = mean;
+    stats[2 * row + 1] = rstd;
+  }
+  uint4* yp = reinterpret_cast<uint4*>(y + (long long)row * C);
+  const uint4* wp = reinterpret_cast<const uint4*>(w);
+  const uint4* bp = reinterpret_cast<const uint4*>(b);
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int e = c * 256 + lane * 8;
+    if (e < C) {
+      uint4 wv = __ldg(wp + c * 32 + lane);
+      uint4 bv = make_uint4(0, 0, 0, 0);
+      if (b) bv = __ldg(bp + c * 32 + lane);
+      uint32_t u[4] = {xv[c].x, xv[c].y, xv[c].z, xv[c].w};
+      uint32_t wu[4] = {wv.x, wv.y, wv.z, wv.w};
+      uint32_t bu[4] = {bv.x, bv.y, bv.z, bv.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f = unpack_bf16x2(u[j]);
+        float2 wf = unpack_bf16x2(wu[j]);
+        float2 bf = unpack_bf16x2(bu[j]);
+        o[j] = pack_bf16x2((f.x - mean) * rstd * wf.x + bf.x, (f.y - mean) * rstd * wf.y + bf.y);
+      }
+      yp[c * 32 + lane] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
+template <int NCH>
+__global__ void __launch_bounds__(128)
+norm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                   const __nv_bfloat16* __restrict__ w, const float* __restrict__ stats,
+                   __nv_bfloat16* __restrict__ dx, int rows, int C, int rms) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const float mean = rms ? 0.f : stats[2 * row];
+  const float rstd = stats[2 * row + 1];
+  const uint4* xp = reinterpret_cast<const uint4*>(x + (long long)row * C);
+  const uint4* gp = reinterpret_cast<const uint4*>(dy + (long long)row * C);
+  const uint4* wp = reinterpret_cast<const uint4*>(w);
+  // dyw (dy*w) and xhat kept as packed bf16? keep fp32-exact by recomputing from
+  // the cached raw bf16 inputs instead.
+  uint4 xv[NCH], gv[NCH];
+  float s1 = 0.f, s2 = 0.f;  // sum(dy*w), sum(dy*w*xhat)
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int e = c * 256 + lane * 8;
+    if (e < C) {
+      xv[c] = ld_nc_v4(xp + c * 32 + lane);
+      gv[c] = ld_nc_v4(gp + c * 32 + lane);
+      uint4 wv = __ldg(wp + c * 32 + lane);
+      uint32_t xu[4] = {xv[c].x, xv[c].y, xv[c].z, xv[c].w};
+      uint32_t gu[4] = {gv[c].x, gv[c].y, gv[c].z, gv[c].w};
+      uint32_t wu[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 xf = unpack_bf16x2(xu[j]), gf = unpack_bf16x2(gu[j]), wf = unpack_bf16x2(wu[j]);
+        float a0 = gf.x * wf.x, a1 = gf.y * wf.y;
+        s1 += a0 + a1;
+        s2 += a0 * (xf.x - mean) * rstd + a1 * (xf.y - mean) * rstd;
+      }
+    }
+  }
+  s1 = rms ? 0.f : warp_sum(s1) / C;
+  s2 = warp_sum(s2) / C;
+  uint4* op = reinterpret_cast<uint4*>(dx + (long long)row * C);
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int e = c * 256 + lane * 8;
+    if (e < C) {
+      uint4 wv = __ldg(wp + c * 32 + lane);
+      uint32_t xu[4] = {xv[c].x, xv[c].y, xv[c].z, xv[c].w};
+      uint32_t gu[4] = {gv[c].x, gv[c].y, gv[c].z, gv[c].w};
+      uint32_t wu[4] = {wv.x, wv.y, wv.z, wv.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 xf = unpack_bf16x2(xu[j]), gf = unpack_bf16x2(gu[j]), wf = unpack_bf16x2(wu[j]);
+        float h0 = (xf.x - mean) * rstd, h1 = (xf.y - mean) * rstd;
+        o[j] = pack_bf16x2(rstd * (gf.x * wf.x - s1 - h0 * s2), rstd * (gf.y * wf.y - s1 - h1 * s2));
+      }
+      op[c * 32 + lane] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
+// Column sums. Block = 32 x 16 threads: x-lane owns 2 adjacent columns, y
+// splits rows. grid = (ceil(C/64), row_splits).
+__global__ void __launch_bounds__(512)
+colsum_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+              const float* __restrict__ stats, float* __restrict__ acc, int rows, int C,
+              long long ld, int rms) {
+  __shared__ float sh[2][16][64];
+  const int col = blockIdx.x * 64 + threadIdx.x * 2;
+  float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+  if (col < C) {
+    for (int r = blockIdx.y * 16 + threadIdx.y; r < rows; r += gridDim.y * 16) {
+      uint32_t gu = *reinterpret_cast<const uint32_t*>(dy + (long long)r * ld + col);
+      float2 gf = unpack_bf16x2(gu);
+      b0 += gf.x;
+      b1 += gf.y;
+      if (x) {
+        uint32_t xu = *reinterpret_cast<const uint32_t*>(x + (long long)r * ld + col);
+        float2 xf = unpack_bf16x2(xu);
+        const float mean = rms ? 0.f : stats[2 * r];
+        const float rstd = stats[2 * r + 1];
+        a0 += gf.x * (xf.x - mean) * rstd;
+        a1 += gf.y * (xf.y - mean) * rstd;
+      }
+    }
+  }
+  sh[0][threadIdx.y][threadIdx.x * 2] = a0;
+  sh[0][threadIdx.y][threadIdx.x * 2 + 1] = a1;
+  sh[1][threadIdx.y][threadIdx.x * 2] = b0;
+  sh[1][threadIdx.y][threadIdx.x * 2 + 1] = b1;
+  __syncthreads();
+  const int tid = threadIdx.y * 32 + threadIdx.x;
+  if (tid < 128) {
+    const int which = tid >> 6, c = tid & 63;
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) s += sh[which][i][c];
+    const int gc = blockIdx.x * 64 + c;
+    if (gc < C && (which == 1 || x)) atomicAdd(&acc[(long long)which * C + gc], s);
+  }
+}
+
+__global__ void f32_to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst,
+                                   long long n, int accumulate) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) {
+    float v = src[i];
+    if (accumulate) v += __bfloat162float(dst[i]);
+    dst[i] = __float2bfloat16(v);
+  }
+}
+
+template <int NCH>
+static int launch_fwd(const void* x, const void* w, const void* b, void* y, float* stats, int rows,
+                      int C, float eps, int rms, cudaStream_t s) {
+  norm_fwd_kernel<NCH><<<(rows + 3) / 4, 128, 0, s>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
+      static_cast<const __nv_bfloat16*>(b), static_cast<__nv_bfloat16*>(y), stats, rows, C, eps,
+      rms);
+  return (int)cudaGetLastError();
+}
+template <int NCH>
+static int launch_bwd(const void* dy, const void* x, const void* w, const float* stats, void* dx,
+                      int rows, int C, int rms, cudaStream_t s) {
+  norm_bwd_dx_kernel<NCH><<<(rows + 3) / 4, 128, 0, s>>>(
+      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
+      static_cast<const __nv_bfloat16*>(w), stats, static_cast<__nv_bfloat16*>(dx), rows, C, rms);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace nkb
+
+using namespace nkb;
+
+#define NKB_NCH_DISPATCH(FN, ...)                          \
+  do {                                                     \
+    const int nch = (C + 255) / 256;                       \
+    if (nch <= 1) return FN<1>(__VA_ARGS__);               \
+    if (nch <= 2) return FN<2>(__VA_ARGS__);               \
+    if (nch <= 4) return FN<4>(__VA_ARGS__);               \
+    if (nch <= 8) return FN<8>(__VA_ARGS__);               \
+    if (nch <= 16) return FN<16>(__VA_ARGS__);             \
+    if (nch <= 20) return FN<20>(__VA_ARGS__);             \
+    if (nch <= 32) return FN<32>(__VA_ARGS__);             \
+    return -4;                                             \
+  } while (0)
+
+extern "C" int nkb_norm_fwd(const void* x, const void* w, const void* b, void* y, float* stats,
+                            int rows, int C, float eps, int rms, void* stream) {
+  if (C % 8) return -3;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  NKB_NCH_DISPATCH(launch_fwd, x, w, b, y, stats, rows, C, eps, rms, s);
+}
+
+extern "C" int nkb_norm_bwd_dx(const void* dy, const void* x, const void* w, const float* stats,
+                               void* dx, int rows, int C, int rms, void* stream) {
+  if (C % 8) return -3;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  NKB_NCH_DISPATCH(launch_bwd, dy, x, w, stats, dx, rows, C, rms, s);
+}
+
+extern "C" int nkb_colsum(const void* dy, const void* x, const float* stats, float* acc, int rows,
+                          int C, long long ld, int rms, void* stream) {
+  if ((C & 1) || (ld & 1)) return -3;
+  dim3 block(32, 16);
+  int gx = (C + 63) / 64;
+  int gy = (4 * 148 + gx - 1) / gx;
+  int max_gy = (rows + 15) / 16;
+  if (gy > max_gy) gy = max_gy;
+  if (gy < 1) gy = 1;
+  colsum_kernel<<<dim3(gx, gy), block, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), stats, acc, rows,
+      C, ld, rms);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int nkb_f32_to_bf16(const float* src, void* dst, long long n, int accumulate,
+                               void* stream) {
+  if (n <= 0) return 0;
+  int blocks = (int)((n + 255) / 256);
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  f32_to_bf16_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      src, static_cast<__nv_bfloat16*>(dst), n, accumulate);
+  return (int)cudaGetLastError();
+}

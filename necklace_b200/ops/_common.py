@@ -1,0 +1,57 @@
+"""Shared helpers for the operator wrappers."""
+from __future__ import annotations
+
+import torch
+
+from .. import _lib
+
+_status: dict[int, torch.Tensor] = {}
+_scratch: dict[tuple, torch.Tensor] = {}
+
+STATUS_TEXT = {
+    0: "ok", 1: "MMA warp timed out waiting for a TMA stage",
+    2: "TMA producer timed out waiting for a free stage",
+    3: "epilogue timed out waiting for an accumulator",
+    4: "MMA warp timed out waiting for a free accumulator",
+    5: "timed out waiting for a readiness/peer flag", 6: "index check failed",
+}
+
+
+def on_gpu(*ts) -> bool:
+    """True when the native path must be used (any CUDA tensor)."""
+    return any(t is not None and t.is_cuda for t in ts)
+
+
+def status_word(device=None) -> torch.Tensor:
+    """Device int32 the kernels write their first error code to."""
+    dev = torch.cuda.current_device() if device is None else torch.device(device).index
+    t = _status.get(dev)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=f"cuda:{dev}")
+        _status[dev] = t
+    return t
+
+
+def check_status(reset: bool = True) -> None:
+    """Synchronise and raise if any kernel since the last check reported an error."""
+    for dev, t in _status.items():
+        code = int(t.item())
+        if code != 0:
+            if reset:
+                t.zero_()
+            raise _lib.NativeLibraryError(
+                f"device-side error {code} on cuda:{dev}: {STATUS_TEXT.get(code, 'unknown')}")
+
+
+def scratch(key: str, numel: int, dtype: torch.dtype, device) -> torch.Tensor:
+    """A cached scratch tensor per (key, device); grown, never shrunk."""
+    k = (key, str(device), dtype)
+    t = _scratch.get(k)
+    if t is None or t.numel() < numel:
+        t = torch.empty(max(numel, 1), dtype=dtype, device=device)
+        _scratch[k] = t
+    return t[:numel]
+
+
+def ptr(t) -> int | None:
+    return None if t is None else t.data_ptr()

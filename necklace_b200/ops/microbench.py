@@ -1,0 +1,132 @@
+"""Micro-benchmarks of the native kernels against the measured device peaks.
+
+``python -m necklace_b200.ops.microbench [gemm|norm|ce|adam|attn|all]`` times each
+kernel with CUDA events (3 warm-up launches, L2 flushed between timed launches by
+writing a 256 MB buffer) and prints achieved TFLOP/s or GB/s, plus the same
+shape through torch (cuBLAS / eager) for comparison.
+"""
+from __future__ import annotations
+
+import json
+import sys
+
+import torch
+
+
+def _time(fn, iters=10, warmup=3, flush=None):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        if flush is not None:
+            flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def bench_gemm(flush):
+    from . import gemm
+    shapes = [  # (M, N, K, a_mn, b_mn, label)
+        (8192, 3072, 1024, False, False, "qkv fwd"),
+        (8192, 1024, 1024, False, False, "proj fwd"),
+        (8192, 4096, 1024, False, False, "fc1 fwd"),
+        (8192, 1024, 4096, False, False, "fc2 fwd"),
+        (8192, 1024, 4096, False, True, "fc1 dgrad"),
+        (4096, 1024, 8192, True, True, "fc1 wgrad"),
+        (8192, 50304, 1024, False, False, "lm head"),
+        (8192, 8192, 8192, False, False, "square 8k"),
+    ]
+    rows = []
+    for M, N, K, a_mn, b_mn, label in shapes:
+        A = torch.randn((K, M) if a_mn else (M, K), device="cuda").bfloat16()
+        B = torch.randn((K, N) if b_mn else (N, K), device="cuda").bfloat16()
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        ms = _time(lambda: gemm(A, B, a_mn=a_mn, b_mn=b_mn, out=out), flush=flush)
+        At = A.t() if a_mn else A
+        Bt = B if b_mn else B.t()
+        ms_t = _time(lambda: torch.matmul(At, Bt, out=out), flush=flush)
+        fl = 2.0 * M * N * K
+        rows.append({"op": "gemm", "label": label, "M": M, "N": N, "K": K, "ms": round(ms, 4),
+                     "tflops": round(fl / ms / 1e9, 1), "torch_ms": round(ms_t, 4),
+                     "torch_tflops": round(fl / ms_t / 1e9, 1)})
+        print(json.dumps(rows[-1]), flush=True)
+    return rows
+
+
+def bench_norm(flush):
+    from .norm import norm_fwd, norm_bwd
+    rows, C = 65536, 1024
+    x = torch.randn(rows, C, device="cuda").bfloat16()
+    w = torch.ones(C, device="cuda").bfloat16()
+    b = torch.zeros(C, device="cuda").bfloat16()
+    ms = _time(lambda: norm_fwd(x, w, b, 1e-5, False), flush=flush)
+    y, st = norm_fwd(x, w, b, 1e-5, False)
+    ms_b = _time(lambda: norm_bwd(x, x, w, st, False), flush=flush)
+    byts = rows * C * 2
+    print(json.dumps({"op": "layernorm_fwd", "ms": round(ms, 4), "GBps": round(2 * byts / ms / 1e6)}))
+    print(json.dumps({"op": "layernorm_bwd(dx+dw+db)", "ms": round(ms_b, 4),
+                      "GBps_min_traffic": round(3 * byts / ms_b / 1e6)}), flush=True)
+
+
+def bench_ce(flush):
+    from . import cross_entropy_fwd_bwd
+    T, V, ld = 8192, 50257, 50304
+    lg = torch.randn(T, ld, device="cuda").bfloat16()
+    tg = torch.randint(0, V, (T,), device="cuda")
+    ms = _time(lambda: cross_entropy_fwd_bwd(lg, tg, V, 1.0 / T), flush=flush)
+    print(json.dumps({"op": "ce_fwd_bwd", "ms": round(ms, 4),
+                      "GBps": round(2 * T * ld * 2 / ms / 1e6)}), flush=True)
+
+
+def bench_adam(flush):
+    from . import adam_step
+    n = 355_000_000
+    master = torch.randn(n, device="cuda")
+    m, v = torch.zeros_like(master), torch.zeros_like(master)
+    g = torch.randn(n, device="cuda").bfloat16()
+    pb = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    ms = _time(lambda: adam_step(master, m, v, g, pb, lr=1e-4, step=2), iters=5)
+    print(json.dumps({"op": "adam_flat", "n": n, "ms": round(ms, 4),
+                      "GBps": round(n * (12 * 2 + 2 + 2) / ms / 1e6)}), flush=True)
+
+
+def bench_attn(flush):
+    from .attention import attn_fwd, attn_bwd
+    for (B, H, S, D) in [(8, 16, 1024, 64), (2, 32, 2048, 128), (1, 40, 4096, 128)]:
+        C = H * D
+        qkv = torch.randn(B, S, 3 * C, device="cuda").bfloat16()
+        ms = _time(lambda: attn_fwd(qkv, H, True), flush=flush)
+        out, lse = attn_fwd(qkv, H, True)
+        do = torch.randn_like(out)
+        ms_b = _time(lambda: attn_bwd(qkv, out, lse, do, H, True), flush=flush)
+        fl = 4.0 * B * H * S * S * D / 2  # causal
+        q, k, v = (t.view(B, S, H, D).transpose(1, 2) for t in qkv.split(C, -1))
+        ms_t = _time(lambda: torch.nn.functional.scaled_dot_product_attention(
+            q, k, v, is_causal=True), flush=flush)
+        print(json.dumps({"op": "attn", "B": B, "H": H, "S": S, "D": D, "fwd_ms": round(ms, 4),
+                          "fwd_tflops": round(fl / ms / 1e9, 1), "bwd_ms": round(ms_b, 4),
+                          "bwd_tflops": round(2.5 * fl / ms_b / 1e9, 1),
+                          "torch_sdpa_fwd_ms": round(ms_t, 4)}), flush=True)
+
+
+def main(argv):
+    which = argv[1] if len(argv) > 1 else "all"
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    table = {"gemm": bench_gemm, "norm": bench_norm, "ce": bench_ce, "adam": bench_adam,
+             "attn": bench_attn}
+    for name, fn in table.items():
+        if which in ("all", name):
+            fn(flush)
+    from . import check_status
+    check_status()
+
+
+if __name__ == "__main__":
+    main(sys.argv)

@@ -1,0 +1,247 @@
+"""Numerics of every native kernel against a plain PyTorch fp32 reference (GPU)."""
+import math
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def _rel_err(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+@pytest.fixture(autouse=True)
+def _status_clean():
+    yield
+    from necklace_b200.ops import check_status
+    check_status()
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (384, 1024, 1024),
+                                   (200, 328, 136), (8192, 1024, 1024), (130, 72, 24)])
+def test_gemm_layouts(a_mn, b_mn, M, N, K):
+    from necklace_b200.ops import gemm
+    torch.manual_seed(0)
+    A = torch.randn(M, K, device=DEV).bfloat16()
+    B = torch.randn(N, K, device=DEV).bfloat16()
+    if (a_mn and M % 8) or (b_mn and N % 8) or ((not a_mn or not b_mn) and K % 8):
+        pass  # repacked inside gemm
+    a_st = A.t().contiguous() if a_mn else A
+    b_st = B.t().contiguous() if b_mn else B
+    out = gemm(a_st, b_st, a_mn=a_mn, b_mn=b_mn)
+    ref = A.float() @ B.float().t()
+    assert _rel_err(out, ref) < 1e-2
+    assert (out.float() - ref).abs().max().item() < 0.05 * math.sqrt(K) + 0.5
+
+
+@pytest.mark.parametrize("bn", [128, 256])
+def test_gemm_epilogues(bn):
+    from necklace_b200.ops import gemm, EPI_GELU_FWD, EPI_GELU_BWD, EPI_RELU
+    torch.manual_seed(1)
+    M, N, K = 512, 768, 320
+    A = (torch.randn(M, K, device=DEV) * 0.5).bfloat16()
+    B = (torch.randn(N, K, device=DEV) * 0.1).bfloat16()
+    bias = torch.randn(N, device=DEV).bfloat16()
+    res = torch.randn(M, N, device=DEV).bfloat16()
+    base = A.float() @ B.float().t()
+    # bias + residual
+    out = gemm(A, B, bias=bias, res=res, bn=bn)
+    assert _rel_err(out, base + bias.float() + res.float()) < 1e-2
+    # gelu forward (saves pre-activation)
+    aux = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    out = gemm(A, B, bias=bias, epi=EPI_GELU_FWD, aux=aux, bn=bn)
+    z = base + bias.float()
+    assert _rel_err(aux, z) < 1e-2
+    assert _rel_err(out, F.gelu(z, approximate="tanh")) < 1e-2
+    # gelu backward
+    zz = aux.float().requires_grad_(True)
+    F.gelu(zz, approximate="tanh").backward(torch.ones_like(zz))
+    out = gemm(A, B, epi=EPI_GELU_BWD, aux=aux, bn=bn)
+    assert _rel_err(out, base * zz.grad) < 2e-2
+    # relu
+    out = gemm(A, B, bias=bias, epi=EPI_RELU, bn=bn)
+    assert _rel_err(out, torch.relu(z)) < 1e-2
+    # fp32 out + accumulate + alpha
+    C = torch.randn(M, N, device=DEV)
+    C0 = C.clone()
+    gemm(A, B, out=C, accumulate=True, alpha=0.5, bn=bn)
+    assert _rel_err(C, C0 + 0.5 * base) < 1e-2
+    # bf16 accumulate
+    Cb = torch.randn(M, N, device=DEV).bfloat16()
+    Cb0 = Cb.clone()
+    gemm(A, B, out=Cb, accumulate=True, bn=bn)
+    assert _rel_err(Cb, Cb0.float() + base) < 1e-2
+    # device-side alpha
+    ad = torch.tensor([0.25], device=DEV)
+    out = gemm(A, B, alpha_dev=ad, bn=bn)
+    assert _rel_err(out, 0.25 * base) < 1e-2
+
+
+def test_gemm_strided_views():
+    from necklace_b200.ops import gemm
+    torch.manual_seed(2)
+    big = torch.randn(256, 3 * 128, device=DEV).bfloat16()
+    A = big[:, 128:256]                      # row pitch 384, offset 128
+    B = torch.randn(64, 128, device=DEV).bfloat16()
+    outbuf = torch.zeros(256, 200, device=DEV, dtype=torch.bfloat16)
+    out = outbuf[:, 8:72]
+    gemm(A, B, out=out)
+    assert _rel_err(out, A.float() @ B.float().t()) < 1e-2
+    assert outbuf[:, :8].abs().sum().item() == 0 and outbuf[:, 72:].abs().sum().item() == 0
+
+
+def test_linear_autograd_matches_torch():
+    from necklace_b200.ops import linear, mlp
+    torch.manual_seed(3)
+    x = torch.randn(4, 64, 256, device=DEV).bfloat16().requires_grad_(True)
+    w1 = (torch.randn(512, 256, device=DEV) * 0.05).bfloat16().requires_grad_(True)
+    b1 = torch.randn(512, device=DEV).bfloat16().requires_grad_(True)
+    w2 = (torch.randn(256, 512, device=DEV) * 0.05).bfloat16().requires_grad_(True)
+    b2 = torch.randn(256, device=DEV).bfloat16().requires_grad_(True)
+    y = mlp(x, w1, b1, w2, b2, residual=x)
+    y2 = linear(y, w1, b1)
+    (y2.float() ** 2).mean().backward()
+    got = [t.grad.clone() for t in (x, w1, b1, w2, b2)]
+    ps = [t.detach().float().requires_grad_(True) for t in (x, w1, b1, w2, b2)]
+    xr, w1r, b1r, w2r, b2r = ps
+    yr = F.linear(F.gelu(F.linear(xr, w1r, b1r), approximate="tanh"), w2r, b2r) + xr
+    y2r = F.linear(yr, w1r, b1r)
+    (y2r ** 2).mean().backward()
+    assert _rel_err(y2, y2r) < 2e-2
+    for g, p in zip(got, ps):
+        assert _rel_err(g, p.grad) < 4e-2
+
+
+@pytest.mark.parametrize("rms", [False, True])
+@pytest.mark.parametrize("C", [64, 1024, 1000, 4096, 5120])
+def test_norm(rms, C):
+    from necklace_b200.ops.norm import NormFn
+    torch.manual_seed(4)
+    rows = 37
+    x = (torch.randn(rows, C, device=DEV) * 2 + 0.3).bfloat16().requires_grad_(True)
+    w = (1 + 0.1 * torch.randn(C, device=DEV)).bfloat16().requires_grad_(True)
+    b = None if rms else (0.1 * torch.randn(C, device=DEV)).bfloat16().requires_grad_(True)
+    dy = torch.randn(rows, C, device=DEV).bfloat16()
+    y = NormFn.apply(x, w, b, 1e-5, rms)
+    y.backward(dy)
+    xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    if rms:
+        yr = xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + 1e-5) * wr
+    else:
+        br = b.detach().float().requires_grad_(True)
+        yr = F.layer_norm(xr, (C,), wr, br, 1e-5)
+    yr.backward(dy.float())
+    assert _rel_err(y, yr) < 1e-2
+    assert _rel_err(x.grad, xr.grad) < 2e-2
+    assert _rel_err(w.grad, wr.grad) < 2e-2
+    if not rms:
+        assert _rel_err(b.grad, br.grad) < 2e-2
+
+
+@pytest.mark.parametrize("V,ld", [(1000, 1000), (50257, 50304), (1003, 1008), (777, 777)])
+def test_cross_entropy(V, ld):
+    from necklace_b200.ops import cross_entropy_fwd_bwd
+    torch.manual_seed(5)
+    T = 33
+    buf = torch.zeros(T, ld, device=DEV, dtype=torch.bfloat16)
+    buf[:, :V] = (torch.randn(T, V, device=DEV) * 3).bfloat16()
+    buf[:, V:] = 77.0  # padding must be ignored
+    tg = torch.randint(0, V, (T,), device=DEV)
+    tg[5] = -100
+    ref_in = buf[:, :V].float().requires_grad_(True)
+    ref = F.cross_entropy(ref_in, tg, ignore_index=-100, reduction="none")
+    ref.sum().backward()
+    losses = cross_entropy_fwd_bwd(buf, tg, V, 1.0)
+    assert torch.allclose(losses, ref, atol=2e-2, rtol=1e-2)
+    assert _rel_err(buf[:, :V], ref_in.grad) < 1e-2
+    assert buf[:, V:].abs().sum().item() == 0
+
+
+def test_embedding():
+    from necklace_b200.ops import Embedding
+    torch.manual_seed(6)
+    emb = Embedding(512, 128, max_pos=64, device=DEV)
+    idx = torch.randint(0, 512, (3, 64), device=DEV)
+    out = emb(idx)
+    ref = emb.wte.float()[idx] + emb.wpe.float()[None, :64]
+    assert _rel_err(out, ref) < 1e-2
+    dy = torch.randn_like(out)
+    out.backward(dy)
+    wte_r = emb.wte.detach().float().requires_grad_(True)
+    wpe_r = emb.wpe.detach().float().requires_grad_(True)
+    (wte_r[idx] + wpe_r[None, :64]).backward(dy.float())
+    assert _rel_err(emb.wte.grad, wte_r.grad) < 3e-2
+    assert _rel_err(emb.wpe.grad, wpe_r.grad) < 3e-2
+
+
+@pytest.mark.parametrize("n", [1024, 1000003])
+@pytest.mark.parametrize("gdt", [torch.bfloat16, torch.float32])
+def test_adam_and_sgd(n, gdt):
+    from necklace_b200.ops import adam_step, sgd_step
+    torch.manual_seed(7)
+    p0 = torch.randn(n, device=DEV)
+    g = torch.randn(n, device=DEV).to(gdt)
+    master, m, v = p0.clone(), torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
+    pb = torch.empty(n, device=DEV, dtype=torch.bfloat16)
+    ref = torch.nn.Parameter(p0.clone())
+    opt = torch.optim.AdamW([ref], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    for step in (1, 2, 3):
+        adam_step(master, m, v, g, pb, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8,
+                  weight_decay=0.1, step=step)
+        ref.grad = g.float()
+        opt.step()
+    assert torch.allclose(master, ref.data, atol=1e-5, rtol=1e-4)
+    assert torch.allclose(pb.float(), master, atol=1e-2, rtol=1e-2)
+    master, mom = p0.clone(), torch.zeros(n, device=DEV)
+    ref = torch.nn.Parameter(p0.clone())
+    opt = torch.optim.SGD([ref], lr=0.01, momentum=0.9, weight_decay=1e-4)
+    for step in (1, 2, 3):
+        sgd_step(master, mom, g, pb, lr=0.01, momentum=0.9, weight_decay=1e-4,
+                 first_step=(step == 1))
+        ref.grad = g.float()
+        opt.step()
+    assert torch.allclose(master, ref.data, atol=1e-5, rtol=1e-4)
+
+
+@pytest.mark.parametrize("n", [16, 1000, 1 << 20])
+def test_quant_flat_matches_cpu_restatement(n):
+    from necklace_b200.ops import quantize_flat, dequantize_flat
+    torch.manual_seed(8)
+    g = torch.randn(n)
+    r = torch.randn(n) * 0.1
+    thr = 0.5
+    r_cpu = r.clone()
+    codes_cpu = quantize_flat(g, r_cpu, thr)
+    g_d, r_d = g.to(DEV), r.to(DEV)
+    codes_d = quantize_flat(g_d, r_d, thr)
+    assert torch.equal(codes_d.cpu(), codes_cpu)
+    assert torch.equal(r_d.cpu(), r_cpu)
+    out = torch.empty(n, device=DEV)
+    dequantize_flat(codes_d, out, thr)
+    ref = torch.empty(n)
+    dequantize_flat(codes_cpu, ref, thr)
+    assert torch.equal(out.cpu(), ref)
+    # decoded + residual reconstructs g + r exactly where |a| < 2*thr
+    assert torch.allclose(ref + r_cpu, g + r, atol=1e-6)
+
+
+def test_quant_matrix_reference_layout():
+    from necklace_b200.ops import matrix_quantize, matrix_dequantize
+    torch.manual_seed(9)
+    A = torch.randn(224, 224)
+    c_cpu, r_cpu = matrix_quantize(A, 0.5)
+    c_d, r_d = matrix_quantize(A.to(DEV), 0.5)
+    assert torch.equal(c_d.cpu(), c_cpu) and torch.equal(r_d.cpu(), r_cpu)
+    back = matrix_dequantize(c_d, 224, 0.5)
+    assert torch.equal(back.cpu(), matrix_dequantize(c_cpu, 224, 0.5))
+    # big, non-square: beyond the reference kernels' fixed 512x512 coverage
+    A = torch.randn(1030, 777, device=DEV)
+    c, r = matrix_quantize(A, 0.3)
+    back = matrix_dequantize(c, 1030, 0.3)
+    assert torch.allclose(back + r, A, atol=1e-6)
