@@ -34,7 +34,8 @@ _SIGS = {
     "nkb_ce_grad": [vp, vp, vp, i32, i32, i64, i32, f32, vp],
     "nkb_embed_fwd": [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp],
     "nkb_embed_bwd": [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp],
-    "nkb_adam_flat": [vp, vp, vp, vp, i32, vp, i64, f32, f32, f32, f32, f32, f32, f32, f32, vp],
+    "nkb_adam_flat": [vp, vp, vp, vp, i32, vp, i64, f32, f32, f32, f32, f32, f32, f32, f32, vp,
+                      vp],
     "nkb_sgd_flat": [vp, vp, vp, i32, vp, i64, f32, f32, f32, f32, i32, vp],
     "nkb_quant2_flat": [vp, i32, vp, vp, i64, f32, vp],
     "nkb_dequant2_flat": [vp, vp, i32, i64, f32, f32, i32, vp],
@@ -46,15 +47,14 @@ _SIGS = {
                      i32, vp, vp],
     "nkb_attn_bwd": [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i64, i64,
                      i64, i64, i64, i64, f32, i32, vp, vp],
-    "nkb_barrier": [vp, i32, i32, i32, vp, vp, vp],
-    "nkb_allreduce": [vp, vp, i64, i64, i32, i32, i32, f32, vp, vp, i32, vp],
-    "nkb_allgather": [vp, vp, i64, i64, i32, i32, vp, vp, i32, vp],
-    "nkb_dp_quant_allreduce": [vp, i32, vp, vp, vp, vp, i64, f32, f32, i32, i32, i32, vp, vp,
-                               i32, vp],
-    "nkb_rs_adam": [vp, vp, i64, i64, vp, vp, vp, vp, i32, i32, f32, f32, f32, f32, f32, f32, f32,
-                    f32, vp, vp, i32, vp],
-    "nkb_rs_sgd": [vp, vp, i64, i64, vp, vp, vp, i32, i32, f32, f32, f32, f32, i32, vp, vp, i32,
-                   vp],
+    "nkb_comm_barrier": [vp, i64, i32, i32, vp, vp, vp],
+    "nkb_comm_allreduce": [vp, i64, i64, i64, i32, f32, i32, i32, vp, vp, i32, vp],
+    "nkb_comm_allgather": [vp, i64, i64, i64, i32, i32, vp, vp, i32, vp],
+    "nkb_comm_dp_quant_allreduce": [vp, i64, vp, i32, vp, i64, i64, vp, i32, i64, f32, f32, i32,
+                                    i32, vp, vp, i32, vp],
+    "nkb_comm_rs_opt_ag": [vp, i64, i64, i64, i64, vp, vp, vp, i32, f32, f32, f32, f32, f32, f32,
+                           f32, f32, i32, vp, i32, i32, vp, vp, i32, vp],
+    "nkb_comm_flag_bytes": [],
     "nkb_num_sms": [],
 }
 

@@ -62,7 +62,7 @@ int nkb_embed_bwd(const long long* idx, const void* dout, void* dwte, void* dwpe
 int nkb_adam_flat(float* master, float* m, float* v, const void* grad, int grad_fp32,
                   void* param_bf16, long long n, float lr, float beta1, float beta2, float eps,
                   float weight_decay, float bias_c1, float bias_c2, float grad_scale,
-                  void* stream);
+                  const float* hyper_dev /* optional device {lr, c1, c2} */, void* stream);
 // SGD with momentum on flat buffers (torch.optim.SGD semantics, dampening 0).
 int nkb_sgd_flat(float* master, float* mom, const void* grad, int grad_fp32, void* param_bf16,
                  long long n, float lr, float momentum, float weight_decay, float grad_scale,
@@ -97,34 +97,37 @@ int nkb_attn_bwd(const void* q, const void* k, const void* v, const void* o, con
                  void* stream);
 
 // ---- comm.cu -----------------------------------------------------------------
-// Peer-memory collectives.  `peers` is a device array of `world` pointers to the
-// same symmetric buffer on every rank (index = rank in the group); `flags` is a
-// device array of `world` pointers to each rank's flag pad (int32).  `epoch` is a
-// device counter owned by the caller and advanced by the kernels.
-int nkb_barrier(int** flags, int rank, int world, int slot, int* epoch_ctr, int* status,
-                void* stream);
-int nkb_allreduce(void** peers, int** flags, long long offset_bytes, long long n, int dtype_fp32,
-                  int rank, int world, float scale, int* epoch_ctr, int* status, int max_ctas,
-                  void* stream);
-int nkb_allgather(void** peers, int** flags, long long offset_bytes, long long shard_bytes,
-                  int rank, int world, int* epoch_ctr, int* status, int max_ctas, void* stream);
-// 2-bit compressed gradient all-reduce with error feedback (one kernel):
-// quantise g(+residual) into this rank's code buffer, exchange, each rank decodes and
-// sums its shard from all peers, scales, publishes the reduced shard to every peer.
-int nkb_dp_quant_allreduce(const void* g, int g_fp32, float* residual, void** code_peers,
-                           void** out_peers, int** flags, long long n, float thr, float scale,
-                           int out_fp32, int rank, int world, int* epoch_ctr, int* status,
-                           int max_ctas, void* stream);
-// ZeRO: reduce-scatter of bf16 gradients fused with Adam on this rank's shard.
-int nkb_rs_adam(void** grad_peers, int** flags, long long grad_offset_bytes, long long n_total,
-                float* master, float* m, float* v, void* param_shard_bf16, int rank, int world,
-                float lr, float beta1, float beta2, float eps, float weight_decay, float bias_c1,
-                float bias_c2, float grad_scale, int* epoch_ctr, int* status, int max_ctas,
-                void* stream);
-int nkb_rs_sgd(void** grad_peers, int** flags, long long grad_offset_bytes, long long n_total,
-               float* master, float* mom, void* param_shard_bf16, int rank, int world, float lr,
-               float momentum, float weight_decay, float grad_scale, int first_step,
-               int* epoch_ctr, int* status, int max_ctas, void* stream);
+// Peer-memory collectives over a symmetric heap.  `heap` is a device array of
+// `world` base pointers (index = rank within the group); buffers are byte offsets
+// into every member's heap.  The flag region (nkb_comm_flag_bytes() bytes, zeroed
+// once) sits at `flag_off`.  `epoch` is a device int[2] (zeroed once) owned by the
+// group: the kernels advance it, so calls can be replayed from a CUDA graph.
+int nkb_comm_flag_bytes(void);
+int nkb_comm_barrier(void** heap, long long flag_off, int rank, int world, int* epoch, int* status,
+                     void* stream);
+// in-place sum (times scale) of n elements at data_off; fp32 = 1 float, 0 bf16
+int nkb_comm_allreduce(void** heap, long long flag_off, long long data_off, long long n, int fp32,
+                       float scale, int rank, int world, int* epoch, int* status, int max_ctas,
+                       void* stream);
+// member r's shard is at data_off + r*shard_bytes; afterwards every member has all shards
+int nkb_comm_allgather(void** heap, long long flag_off, long long data_off, long long shard_bytes,
+                       int rank, int world, int* epoch, int* status, int max_ctas, void* stream);
+// 2-bit compressed gradient all-reduce with error feedback, one kernel:
+// out = scale * thr * sum_ranks sign-code(g + residual); residual updated in place.
+// codes_off: uint32[ceil(n/16)], counts_off: int8[16*ceil(n/16)] in the heap.
+int nkb_comm_dp_quant_allreduce(void** heap, long long flag_off, const void* g, int g_fp32,
+                                float* residual, long long codes_off, long long counts_off,
+                                void* out, int out_fp32, long long n, float thr, float scale,
+                                int rank, int world, int* epoch, int* status, int max_ctas,
+                                void* stream);
+// ZeRO step in one kernel: reduce-scatter of bf16 grads (grad_off) + Adam/SGD on this
+// rank's fp32 shard + all-gather of the new bf16 params (param_off) into every heap.
+// n_total % (8*world) == 0; master/s1/s2 hold n_total/world floats.
+int nkb_comm_rs_opt_ag(void** heap, long long flag_off, long long grad_off, long long param_off,
+                       long long n_total, float* master, float* s1, float* s2, int adam, float lr,
+                       float beta1, float beta2, float eps, float wd, float c1, float c2,
+                       float gscale, int first_step, const float* hyper_dev, int rank, int world,
+                       int* epoch, int* status, int max_ctas, void* stream);
 
 int nkb_num_sms(void);
 const char* nkb_build_info(void);

@@ -23,7 +23,8 @@ __global__ void __launch_bounds__(256)
 adam_flat_kernel(float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
                  const void* __restrict__ grad, int grad_fp32, __nv_bfloat16* __restrict__ pbf,
                  long long n, float lr, float b1, float b2, float eps, float wd, float c1,
-                 float c2, float gscale) {
+                 float c2, float gscale, const float* __restrict__ hyper) {
+  if (hyper) { lr = hyper[0]; c1 = hyper[1]; c2 = hyper[2]; }
   const long long n4 = n >> 2;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
@@ -263,7 +264,7 @@ using namespace nkb;
 extern "C" int nkb_adam_flat(float* master, float* m, float* v, const void* grad, int grad_fp32,
                              void* param_bf16, long long n, float lr, float beta1, float beta2,
                              float eps, float weight_decay, float bias_c1, float bias_c2,
-                             float grad_scale, void* stream) {
+                             float grad_scale, const float* hyper_dev, void* stream) {
   if (n <= 0) return 0;
   // 16-byte accesses need aligned bases
   if ((reinterpret_cast<uintptr_t>(master) | reinterpret_cast<uintptr_t>(m) |
@@ -273,7 +274,7 @@ extern "C" int nkb_adam_flat(float* master, float* m, float* v, const void* grad
   if (param_bf16 && (reinterpret_cast<uintptr_t>(param_bf16) & 7)) return -3;
   adam_flat_kernel<<<grid_for(n / 4 + 1), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       master, m, v, grad, grad_fp32, static_cast<__nv_bfloat16*>(param_bf16), n, lr, beta1, beta2,
-      eps, weight_decay, bias_c1, bias_c2, grad_scale);
+      eps, weight_decay, bias_c1, bias_c2, grad_scale, hyper_dev);
   return (int)cudaGetLastError();
 }
 

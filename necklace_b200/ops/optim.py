@@ -18,12 +18,16 @@ from ._common import on_gpu, ptr
 
 
 def adam_step(master, m, v, grad, param_bf16, *, lr, beta1=0.9, beta2=0.999, eps=1e-8,
-              weight_decay=0.0, step=1, grad_scale=1.0):
-    """One Adam(W) step over flat buffers.  ``step`` is 1-based."""
+              weight_decay=0.0, step=1, grad_scale=1.0, hyper=None):
+    """One Adam(W) step over flat buffers.  ``step`` is 1-based.  ``hyper`` is an optional
+    device tensor ``[lr, 1/(1-b1^t), 1/(1-b2^t)]`` that overrides the host values, so a
+    CUDA graph can be replayed with a changing step count."""
     n = master.numel()
     c1 = 1.0 / (1.0 - beta1 ** step)
     c2 = 1.0 / (1.0 - beta2 ** step)
     if not on_gpu(master):
+        if hyper is not None:
+            lr, c1, c2 = (float(x) for x in hyper[:3])
         g = grad.float() * grad_scale
         m.mul_(beta1).add_(g, alpha=1 - beta1)
         v.mul_(beta2).addcmul_(g, g, value=1 - beta2)
@@ -37,7 +41,7 @@ def adam_step(master, m, v, grad, param_bf16, *, lr, beta1=0.9, beta2=0.999, eps
     _lib.call("nkb_adam_flat", master.data_ptr(), m.data_ptr(), v.data_ptr(), grad.data_ptr(),
               int(grad.dtype == torch.float32), ptr(param_bf16), n, float(lr), float(beta1),
               float(beta2), float(eps), float(weight_decay), float(c1), float(c2),
-              float(grad_scale), _lib.stream_ptr())
+              float(grad_scale), ptr(hyper), _lib.stream_ptr())
     _lib.count_launch()
 
 
