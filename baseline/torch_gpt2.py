@@ -43,6 +43,7 @@ class GPT2(nn.Module):
         self.vocab = c["vocab"]
         vp = (c["vocab"] + 127) // 128 * 128
         self.wte = nn.Embedding(vp, c["d_model"])
+        nn.init.normal_(self.wte.weight, std=0.02)
         self.wpe = nn.Embedding(c["max_seq"], c["d_model"])
         self.blocks = nn.ModuleList(Block(c) for _ in range(c["n_layer"]))
         self.ln_f = nn.LayerNorm(c["d_model"])

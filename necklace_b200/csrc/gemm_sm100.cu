@@ -75,6 +75,94 @@ __device__ __forceinline__ void set_error(int* status, volatile int* abort_flag,
   if (status) atomicCAS(status, 0, code);
 }
 
+// ---- epilogue staging tile: 32 rows x 128 bytes per warp, 16-byte chunks XOR-swizzled
+// by (row & 7) so both the row-per-thread and the 4-rows-per-instruction access
+// patterns are free of bank conflicts.
+constexpr int EPI_STAGE_BYTES = 32 * 128;
+
+__device__ __forceinline__ uint4 stage_get(const uint8_t* stg, int row, int chunk) {
+  return *reinterpret_cast<const uint4*>(stg + row * 128 + ((chunk ^ (row & 7)) << 4));
+}
+__device__ __forceinline__ void stage_set(uint8_t* stg, int row, int chunk, uint4 v) {
+  *reinterpret_cast<uint4*>(stg + row * 128 + ((chunk ^ (row & 7)) << 4)) = v;
+}
+// thread `lane` writes its 64 values as bf16 into row `lane`
+__device__ __forceinline__ void stage_put_bf16(uint8_t* stg, int lane, const float* v) {
+  __syncwarp();
+#pragma unroll
+  for (int q = 0; q < 8; ++q)
+    stage_set(stg, lane, q,
+              make_uint4(pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]), pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]),
+                         pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]), pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7])));
+}
+// Cooperative copies between the staging tile and a [rows_valid x cols_valid]
+// global tile (row pitch ld elements).  ESZ = element size; a row of the tile is
+// 128 bytes = 8 chunks of CH = 16/ESZ elements.  Instruction i moves rows
+// 4i..4i+3, one 16-byte chunk per lane.
+template <typename T>
+__device__ __forceinline__ void stage_store_t(const uint8_t* stg, int lane, T* gptr, long long ld,
+                                              int rows_valid, int cols_valid) {
+  constexpr int CH = 16 / (int)sizeof(T);
+  const bool vec = ((ld * (long long)sizeof(T)) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(gptr) & 15) == 0;
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int row = i * 4 + (lane >> 3), ch = lane & 7;
+    if (row < rows_valid && ch * CH < cols_valid) {
+      const uint4 v = stage_get(stg, row, ch);
+      T* dst = gptr + (long long)row * ld + ch * CH;
+      if (vec && (ch + 1) * CH <= cols_valid) {
+        *reinterpret_cast<uint4*>(dst) = v;
+      } else {
+        const T* e = reinterpret_cast<const T*>(&v);
+        for (int k = 0; k < CH && ch * CH + k < cols_valid; ++k) dst[k] = e[k];
+      }
+    }
+  }
+  __syncwarp();
+}
+template <typename T>
+__device__ __forceinline__ void stage_load_t(uint8_t* stg, int lane, const T* gptr, long long ld,
+                                             int rows_valid, int cols_valid) {
+  constexpr int CH = 16 / (int)sizeof(T);
+  const bool vec = ((ld * (long long)sizeof(T)) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(gptr) & 15) == 0;
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int row = i * 4 + (lane >> 3), ch = lane & 7;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (row < rows_valid && ch * CH < cols_valid) {
+      const T* src = gptr + (long long)row * ld + ch * CH;
+      if (vec && (ch + 1) * CH <= cols_valid) {
+        v = *reinterpret_cast<const uint4*>(src);
+      } else {
+        T* e = reinterpret_cast<T*>(&v);
+        for (int k = 0; k < CH && ch * CH + k < cols_valid; ++k) e[k] = src[k];
+      }
+    }
+    stage_set(stg, row, ch, v);
+  }
+  __syncwarp();
+}
+__device__ __forceinline__ void stage_store_bf16(const uint8_t* stg, int lane, __nv_bfloat16* g,
+                                                 long long ld, int rv, int cv) {
+  stage_store_t<__nv_bfloat16>(stg, lane, g, ld, rv, cv);
+}
+__device__ __forceinline__ void stage_load_bf16(uint8_t* stg, int lane, const __nv_bfloat16* g,
+                                                long long ld, int rv, int cv) {
+  stage_load_t<__nv_bfloat16>(stg, lane, g, ld, rv, cv);
+}
+__device__ __forceinline__ void stage_store_f32(const uint8_t* stg, int lane, float* g,
+                                                long long ld, int rv, int cv) {
+  stage_store_t<float>(stg, lane, g, ld, rv, cv);
+}
+__device__ __forceinline__ void stage_load_f32(uint8_t* stg, int lane, const float* g, long long ld,
+                                               int rv, int cv) {
+  stage_load_t<float>(stg, lane, g, ld, rv, cv);
+}
+
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -88,7 +176,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                               ~uintptr_t(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* full_bar =
+      reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES + 4 * EPI_STAGE_BYTES);
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* acc_full = empty_bar + STAGES;
   uint64_t* acc_empty = acc_full + 2;
@@ -231,22 +320,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   } else {
     // ------------------------------------------------------------ epilogue
+    // Each thread owns one accumulator row (TMEM lane).  Global traffic goes
+    // through a per-warp 32-row x 128-byte staging tile so that every global
+    // load / store instruction of the warp covers whole 128-byte lines.
     const int lane_grp = warp & 3;  // TMEM lanes this warp may touch: 32*lane_grp ..
+    uint8_t* stg = smem + STAGES * STAGE_BYTES + (warp - 2) * EPI_STAGE_BYTES;
     int acc = 0;
     uint32_t acc_phase = 0;
     const float alpha = g.alpha_dev ? g.alpha * __ldg(g.alpha_dev) : g.alpha;
-    const bool vec_ok = ((g.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(g.C) & 15) == 0) &&
-                        (!g.res || (((g.ldres & 7) == 0) &&
-                                    ((reinterpret_cast<uintptr_t>(g.res) & 15) == 0))) &&
-                        (!g.aux_out || (((g.ldaux & 7) == 0) &&
-                                        ((reinterpret_cast<uintptr_t>(g.aux_out) & 15) == 0))) &&
-                        (!g.aux_in || (((g.ldaux & 7) == 0) &&
-                                       ((reinterpret_cast<uintptr_t>(g.aux_in) & 15) == 0))) &&
-                        (!g.bias || ((reinterpret_cast<uintptr_t>(g.bias) & 15) == 0));
+    const bool bias_vec = g.bias && ((reinterpret_cast<uintptr_t>(g.bias) & 15) == 0);
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
       const int mb = t % g.num_m_blocks, nb = t / g.num_m_blocks;
-      const int row = mb * BM + lane_grp * 32 + lane;
+      const int row0 = mb * BM + lane_grp * 32;  // first row of this warp's slab
       const int n0 = nb * BN;
+      int rows_valid = g.M - row0;
+      rows_valid = rows_valid < 0 ? 0 : (rows_valid > 32 ? 32 : rows_valid);
       if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag)) {
         set_error(g.status, abort_flag, NKB_ERR_ACC_WAIT);
         break;
@@ -254,138 +342,122 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_after();
       const uint32_t t_addr = tmem_base + (uint32_t(lane_grp * 32) << 16) + acc * BN;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(t_addr + c * 32, r);
+      for (int cc = 0; cc < BN / 64; ++cc) {
+        uint32_t r[64];
+        tmem_ld_32x32(t_addr + cc * 64, r);
+        tmem_ld_32x32(t_addr + cc * 64 + 32, r + 32);
         tmem_ld_wait();
-        const int col0 = n0 + c * 32;
-        if (row < g.M && col0 < g.N) {
-          float v[32];
+        const int col0 = n0 + cc * 64;
+        if (rows_valid == 0 || col0 >= g.N) continue;  // warp-uniform
+        const int cols_valid = (g.N - col0) < 64 ? (g.N - col0) : 64;
+        float v[64];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * alpha;
-          const bool full = vec_ok && (col0 + 32 <= g.N);
-          if (full) {
-            if (g.bias) {
-              const uint4* bp = reinterpret_cast<const uint4*>(g.bias + col0);
+        for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]) * alpha;
+        if (g.bias) {
+          if (bias_vec && cols_valid == 64 && (col0 & 7) == 0) {
+            const uint4* bp = reinterpret_cast<const uint4*>(g.bias + col0);
 #pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                uint4 b = __ldg(bp + q);
-                uint32_t w[4] = {b.x, b.y, b.z, b.w};
+            for (int q = 0; q < 8; ++q) {
+              uint4 b = __ldg(bp + q);
+              uint32_t w[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  float2 f = unpack_bf16x2(w[j]);
-                  v[q * 8 + 2 * j] += f.x;
-                  v[q * 8 + 2 * j + 1] += f.y;
-                }
-              }
-            }
-            if (g.epi == NKB_EPI_GELU_FWD) {
-              uint4* ap = reinterpret_cast<uint4*>(g.aux_out + (long long)row * g.ldaux + col0);
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                uint4 o;
-                o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
-                o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
-                o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
-                o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
-                ap[q] = o;
-              }
-#pragma unroll
-              for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
-            } else if (g.epi == NKB_EPI_GELU_BWD) {
-              const uint4* ap =
-                  reinterpret_cast<const uint4*>(g.aux_in + (long long)row * g.ldaux + col0);
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                uint4 z = __ldg(ap + q);
-                uint32_t w[4] = {z.x, z.y, z.z, z.w};
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  float2 f = unpack_bf16x2(w[j]);
-                  v[q * 8 + 2 * j] *= gelu_tanh_grad(f.x);
-                  v[q * 8 + 2 * j + 1] *= gelu_tanh_grad(f.y);
-                }
-              }
-            } else if (g.epi == NKB_EPI_RELU) {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) v[i] = fmaxf(v[i], 0.f);
-            }
-            if (g.res) {
-              const uint4* rp =
-                  reinterpret_cast<const uint4*>(g.res + (long long)row * g.ldres + col0);
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                uint4 z = __ldg(rp + q);
-                uint32_t w[4] = {z.x, z.y, z.z, z.w};
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  float2 f = unpack_bf16x2(w[j]);
-                  v[q * 8 + 2 * j] += f.x;
-                  v[q * 8 + 2 * j + 1] += f.y;
-                }
-              }
-            }
-            if (g.c_fp32) {
-              float4* cp = reinterpret_cast<float4*>(reinterpret_cast<float*>(g.C) +
-                                                     (long long)row * g.ldc + col0);
-#pragma unroll
-              for (int q = 0; q < 8; ++q) {
-                float4 o = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
-                if (g.accumulate) {
-                  float4 p = cp[q];
-                  o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
-                }
-                cp[q] = o;
-              }
-            } else {
-              uint4* cp = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(g.C) +
-                                                   (long long)row * g.ldc + col0);
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                if (g.accumulate) {
-                  uint4 p = cp[q];
-                  uint32_t w[4] = {p.x, p.y, p.z, p.w};
-#pragma unroll
-                  for (int j = 0; j < 4; ++j) {
-                    float2 f = unpack_bf16x2(w[j]);
-                    v[q * 8 + 2 * j] += f.x;
-                    v[q * 8 + 2 * j + 1] += f.y;
-                  }
-                }
-                uint4 o;
-                o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
-                o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
-                o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
-                o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
-                cp[q] = o;
+              for (int j = 0; j < 4; ++j) {
+                float2 f = unpack_bf16x2(w[j]);
+                v[q * 8 + 2 * j] += f.x;
+                v[q * 8 + 2 * j + 1] += f.y;
               }
             }
           } else {
-            // ragged edge or unaligned views: scalar path with bounds checks
-            for (int i = 0; i < 32; ++i) {
-              const int col = col0 + i;
-              if (col >= g.N) break;
-              float x = v[i];
-              if (g.bias) x += __bfloat162float(g.bias[col]);
-              if (g.epi == NKB_EPI_GELU_FWD) {
-                g.aux_out[(long long)row * g.ldaux + col] = __float2bfloat16(x);
-                x = gelu_tanh(x);
-              } else if (g.epi == NKB_EPI_GELU_BWD) {
-                x *= gelu_tanh_grad(__bfloat162float(g.aux_in[(long long)row * g.ldaux + col]));
-              } else if (g.epi == NKB_EPI_RELU) {
-                x = fmaxf(x, 0.f);
+#pragma unroll
+            for (int i = 0; i < 64; ++i)
+              if (i < cols_valid) v[i] += __bfloat162float(g.bias[col0 + i]);
+          }
+        }
+        if (g.epi == NKB_EPI_GELU_FWD) {
+          stage_put_bf16(stg, lane, v);
+          stage_store_bf16(stg, lane, g.aux_out + (long long)row0 * g.ldaux + col0, g.ldaux,
+                           rows_valid, cols_valid);
+#pragma unroll
+          for (int i = 0; i < 64; ++i) v[i] = gelu_tanh(v[i]);
+        } else if (g.epi == NKB_EPI_GELU_BWD) {
+          stage_load_bf16(stg, lane, g.aux_in + (long long)row0 * g.ldaux + col0, g.ldaux,
+                          rows_valid, cols_valid);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            uint4 z = stage_get(stg, lane, q);
+            uint32_t w[4] = {z.x, z.y, z.z, z.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              float2 f = unpack_bf16x2(w[j]);
+              v[q * 8 + 2 * j] *= gelu_tanh_grad(f.x);
+              v[q * 8 + 2 * j + 1] *= gelu_tanh_grad(f.y);
+            }
+          }
+        } else if (g.epi == NKB_EPI_RELU) {
+#pragma unroll
+          for (int i = 0; i < 64; ++i) v[i] = fmaxf(v[i], 0.f);
+        }
+        if (g.res) {
+          stage_load_bf16(stg, lane, g.res + (long long)row0 * g.ldres + col0, g.ldres, rows_valid,
+                          cols_valid);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            uint4 z = stage_get(stg, lane, q);
+            uint32_t w[4] = {z.x, z.y, z.z, z.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              float2 f = unpack_bf16x2(w[j]);
+              v[q * 8 + 2 * j] += f.x;
+              v[q * 8 + 2 * j + 1] += f.y;
+            }
+          }
+        }
+        if (g.c_fp32) {
+          float* cbase = reinterpret_cast<float*>(g.C) + (long long)row0 * g.ldc + col0;
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            const int cv = cols_valid - half * 32;
+            if (cv <= 0) break;
+            if (g.accumulate) {
+              stage_load_f32(stg, lane, cbase + half * 32, g.ldc, rows_valid, cv);
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                uint4 z = stage_get(stg, lane, q);
+                v[half * 32 + q * 4 + 0] += __uint_as_float(z.x);
+                v[half * 32 + q * 4 + 1] += __uint_as_float(z.y);
+                v[half * 32 + q * 4 + 2] += __uint_as_float(z.z);
+                v[half * 32 + q * 4 + 3] += __uint_as_float(z.w);
               }
-              if (g.res) x += __bfloat162float(g.res[(long long)row * g.ldres + col]);
-              if (g.c_fp32) {
-                float* cp = reinterpret_cast<float*>(g.C) + (long long)row * g.ldc + col;
-                *cp = g.accumulate ? (*cp + x) : x;
-              } else {
-                __nv_bfloat16* cp =
-                    reinterpret_cast<__nv_bfloat16*>(g.C) + (long long)row * g.ldc + col;
-                *cp = __float2bfloat16(g.accumulate ? (__bfloat162float(*cp) + x) : x);
+            }
+            __syncwarp();
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              stage_set(stg, lane, q,
+                        make_uint4(__float_as_uint(v[half * 32 + q * 4]),
+                                   __float_as_uint(v[half * 32 + q * 4 + 1]),
+                                   __float_as_uint(v[half * 32 + q * 4 + 2]),
+                                   __float_as_uint(v[half * 32 + q * 4 + 3])));
+            stage_store_f32(stg, lane, cbase + half * 32, g.ldc, rows_valid, cv);
+          }
+        } else {
+          __nv_bfloat16* cbase =
+              reinterpret_cast<__nv_bfloat16*>(g.C) + (long long)row0 * g.ldc + col0;
+          if (g.accumulate) {
+            stage_load_bf16(stg, lane, cbase, g.ldc, rows_valid, cols_valid);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              uint4 z = stage_get(stg, lane, q);
+              uint32_t w[4] = {z.x, z.y, z.z, z.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float2 f = unpack_bf16x2(w[j]);
+                v[q * 8 + 2 * j] += f.x;
+                v[q * 8 + 2 * j + 1] += f.y;
               }
             }
           }
+          stage_put_bf16(stg, lane, v);
+          stage_store_bf16(stg, lane, cbase, g.ldc, rows_valid, cols_valid);
         }
       }
       tc_fence_before();
@@ -461,7 +533,8 @@ template <int BN, bool A_MN, bool B_MN>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs& g, int max_ctas,
                        cudaStream_t stream) {
   constexpr int STAGES = (BN == 256) ? 4 : 6;
-  constexpr int smem_bytes = STAGES * (A_STAGE_BYTES + BN * BK * 2) + 1024 + 256;
+  constexpr int smem_bytes =
+      STAGES * (A_STAGE_BYTES + BN * BK * 2) + 4 * EPI_STAGE_BYTES + 1024 + 256;
   static bool configured = false;
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
   if (!configured) {

@@ -116,8 +116,37 @@ def bench_attn(flush):
                           "torch_sdpa_fwd_ms": round(ms_t, 4)}), flush=True)
 
 
+def one_gemm(argv):
+    """``gemm_one M N K [a_mn b_mn]``: a handful of launches of one shape (ncu captures)."""
+    from . import gemm
+    M, N, K = (int(x) for x in argv[2:5])
+    a_mn = len(argv) > 5 and argv[5] == "1"
+    b_mn = len(argv) > 6 and argv[6] == "1"
+    A = torch.randn((K, M) if a_mn else (M, K), device="cuda").bfloat16()
+    B = torch.randn((K, N) if b_mn else (N, K), device="cuda").bfloat16()
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    for _ in range(5):
+        gemm(A, B, a_mn=a_mn, b_mn=b_mn, out=out)
+    torch.cuda.synchronize()
+
+
+def one_attn(argv):
+    """``attn_one B H S D``: a few forward+backward launches of one shape (ncu captures)."""
+    from .attention import attn_fwd, attn_bwd
+    B, H, S, D = (int(x) for x in argv[2:6])
+    qkv = torch.randn(B, S, 3 * H * D, device="cuda").bfloat16()
+    for _ in range(3):
+        out, lse = attn_fwd(qkv, H, True)
+        attn_bwd(qkv, out, lse, out, H, True)
+    torch.cuda.synchronize()
+
+
 def main(argv):
     which = argv[1] if len(argv) > 1 else "all"
+    if which == "gemm_one":
+        return one_gemm(argv)
+    if which == "attn_one":
+        return one_attn(argv)
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
     table = {"gemm": bench_gemm, "norm": bench_norm, "ce": bench_ce, "adam": bench_adam,
              "attn": bench_attn}

@@ -1,0 +1,12 @@
+"""Empty mixin bases kept for user code that subclasses them
+(reference: necklace/rpc/mixinbase.py:4-9)."""
+
+
+class NodeMixin:
+    def __init__(self, ndid=None, cfg=None, *args, **kwargs):
+        self.ndid = ndid
+        self.cfg = cfg or {}
+
+
+class ServiceMixin:
+    pass
