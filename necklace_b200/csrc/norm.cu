@@ -273,3 +273,40 @@ extern "C" int nkb_f32_to_bf16(const float* src, void* dst, long long n, int acc
       src, static_cast<__nv_bfloat16*>(dst), n, accumulate);
   return (int)cudaGetLastError();
 }
+
+// ---------------------------------------------------------------------------
+// Allocation-free column sum (declared in nkb_noalloc.h).  The fp32 accumulator
+// lives in the library image instead of caller-provided scratch.
+#include "nkb_noalloc.h"
+
+static __device__ __align__(256) float g_noalloc_colsum_scratch[2 * NKB_NOALLOC_MAX_COLS];
+
+// Device address of the scratch array per device ordinal.  The array's name is only
+// a host-side handle; kernels must be given the address cudaGetSymbolAddress returns
+// while the owning device is current.
+static float* g_noalloc_scratch_ptr[64] = {nullptr};
+
+extern "C" int nkb_colsum_bf16_noalloc(const void* dy, void* out, int rows, int C, long long ld,
+                                       void* stream) {
+  if (C > NKB_NOALLOC_MAX_COLS) return -4;
+  if (C <= 0 || rows <= 0) return -2;
+  if ((C & 1) || (ld & 1)) return -3;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= 64) return -5;
+  if (!g_noalloc_scratch_ptr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_noalloc_colsum_scratch);
+    if (e != cudaSuccess) return (int)e;
+    g_noalloc_scratch_ptr[dev] = static_cast<float*>(p);
+  }
+  float* acc = g_noalloc_scratch_ptr[dev];
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // only the plain-sum half [C, 2C) is used; it must start at zero for every call
+  e = cudaMemsetAsync(acc + C, 0, sizeof(float) * (size_t)C, s);
+  if (e != cudaSuccess) return (int)e;
+  int rc = nkb_colsum(dy, nullptr, nullptr, acc, rows, C, ld, 0, stream);
+  if (rc) return rc;
+  return nkb_f32_to_bf16(acc + C, out, C, 0, stream);
+}
