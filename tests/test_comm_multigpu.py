@@ -1,0 +1,179 @@
+"""Peer-memory collectives against NCCL results on the same inputs (needs >= 2 GPUs).
+
+Ranks run as child processes, one GPU each.  NCCL is used for bootstrap and as the
+oracle; NVLS is switched off (plain peer loads/stores everywhere)."""
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, fn_name, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                      RANK=str(rank), WORLD_SIZE=str(world))
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world,
+                            device_id=torch.device("cuda", rank))
+    try:
+        from necklace_b200.comm.symm import SymmetricHeap
+        from necklace_b200.ops import check_status
+        heap = SymmetricHeap(256 << 20)
+        grp = heap.peer_group()
+        globals()[fn_name](rank, world, heap, grp)
+        torch.cuda.synchronize()
+        check_status()
+        dist.barrier()
+        q.put((rank, "ok"))
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        q.put((rank, "ERR " + traceback.format_exc()[-1500:]))
+    finally:
+        dist.destroy_process_group()
+
+
+def _run(fn_name, world=None):
+    import torch.multiprocessing as mp
+    world = world or min(torch.cuda.device_count(), 8)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, fn_name, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = []
+    for _ in procs:
+        res.append(q.get(timeout=240))
+    for p in procs:
+        p.join(timeout=60)
+    bad = [r for r in res if r[1] != "ok"]
+    assert not bad, bad
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+def case_allreduce_allgather(rank, world, heap, grp):
+    import torch.distributed as dist
+    for dtype, n in [(torch.float32, 1 << 20), (torch.bfloat16, (1 << 22) + 8 * world),
+                     (torch.float32, 1000)]:
+        t = heap.alloc(n, dtype)
+        for it in range(3):
+            torch.manual_seed(100 * it + rank)
+            src = torch.randn(n, device="cuda").to(dtype)
+            t.copy_(src)
+            ref = src.float().clone()
+            dist.all_reduce(ref)
+            grp.barrier()
+            grp.all_reduce(t, scale=0.5)
+            tol = 1e-5 if dtype == torch.float32 else 2e-2
+            assert _rel(t, ref * 0.5) < tol, (dtype, n, it)
+    shard = 1 << 18
+    full = heap.alloc(shard * world, torch.bfloat16)
+    for it in range(2):
+        full.zero_()
+        mine = torch.full((shard,), float(rank + 1 + it), device="cuda").bfloat16()
+        full.view(world, shard)[rank].copy_(mine)
+        grp.all_gather(full)
+        exp = torch.arange(1 + it, world + 1 + it, device="cuda").float()[:, None].expand(world, shard)
+        assert torch.equal(full.view(world, shard).float(), exp)
+
+
+def case_dp_quant(rank, world, heap, grp):
+    import torch.distributed as dist
+    from necklace_b200.ops.quant import quantize_flat, dequantize_flat
+    n = 3_000_001
+    nw = (n + 15) // 16
+    codes = heap.alloc(nw, torch.int32)
+    counts = heap.alloc(nw * 16, torch.int8)
+    residual = torch.zeros(n, device="cuda")
+    res_ref = torch.zeros(n, device="cuda")
+    thr = 0.4
+    for it in range(3):
+        torch.manual_seed(7 * it + rank)
+        g = torch.randn(n, device="cuda")
+        out = torch.empty(n, device="cuda")
+        grp.dp_quant_allreduce(g, residual, codes, counts, out, thr, 1.0 / world)
+        # oracle: separate codec kernels + NCCL sum of the decoded ternary values
+        c = quantize_flat(g, res_ref, thr)
+        tern = torch.empty(n, device="cuda")
+        dequantize_flat(c, tern, thr)
+        dist.all_reduce(tern)
+        assert torch.allclose(out, tern / world, atol=1e-6), it
+        assert torch.equal(residual, res_ref), it
+
+
+def case_rs_opt_ag(rank, world, heap, grp):
+    import torch.distributed as dist
+    from necklace_b200.ops import adam_step
+    n = 8 * world * 64 * 1000
+    grads = heap.alloc(n, torch.bfloat16)
+    params = heap.alloc(n, torch.bfloat16)
+    torch.manual_seed(1)
+    p0 = torch.randn(n, device="cuda").bfloat16()
+    params.copy_(p0)
+    shard = n // world
+    master = p0[rank * shard:(rank + 1) * shard].float()
+    m, v = torch.zeros_like(master), torch.zeros_like(master)
+    ref_master, ref_m, ref_v = p0.float(), torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    for step in (1, 2, 3):
+        torch.manual_seed(50 * step + rank)
+        g = torch.randn(n, device="cuda").bfloat16()
+        grads.copy_(g)
+        gsum = g.float().clone()
+        dist.all_reduce(gsum)
+        grp.rs_opt_ag(grads, params, master, m, v, adam=True, lr=1e-2, beta1=0.9, beta2=0.95,
+                      eps=1e-8, weight_decay=0.1, step=step, grad_scale=1.0 / world)
+        adam_step(ref_master, ref_m, ref_v, gsum, None, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8,
+                  weight_decay=0.1, step=step, grad_scale=1.0 / world)
+        torch.cuda.synchronize()
+        assert torch.allclose(master, ref_master[rank * shard:(rank + 1) * shard], atol=1e-5,
+                              rtol=1e-4), step
+        assert _rel(params, ref_master) < 1e-2, step
+
+
+def case_engine_zero_matches_single(rank, world, heap, grp):
+    """dp+zr training of a small GPT-2 equals a single-process run on the global batch."""
+    from necklace_b200.models.gpt2 import GPT2, GPT2Config
+    from necklace_b200.parallel.engine import OptimConfig, TrainEngine
+    cfg = GPT2Config(n_layer=2, d_model=128, n_head=2, d_ff=512, vocab=512, max_seq=128)
+    torch.manual_seed(0)
+    model = GPT2(cfg, device="cuda")
+    torch.manual_seed(0)
+    ref_model = GPT2(cfg, device="cuda")
+    opt = OptimConfig("adam", lr=1e-3, beta1=0.9, beta2=0.95)
+    eng = TrainEngine(model, mode="zero", group=grp, heap=heap, optim=opt)
+    ref = TrainEngine(ref_model, mode="local", optim=opt)
+    g = torch.Generator().manual_seed(3)
+    tok = torch.randint(0, cfg.vocab, (world * 2, 129), generator=g).cuda()
+    for _ in range(3):
+        mine = tok[rank * 2:(rank + 1) * 2]
+        l1 = eng.step(mine[:, :-1].contiguous(), mine[:, 1:].contiguous())
+        l2 = ref.step(tok[:, :-1].contiguous(), tok[:, 1:].contiguous())
+    assert _rel(eng.flat.flat[:eng.flat.numel_used], ref.flat.flat[:ref.flat.numel_used]) < 2e-2
+
+
+def test_allreduce_allgather():
+    _run("case_allreduce_allgather")
+
+
+def test_dp_quant_allreduce():
+    _run("case_dp_quant")
+
+
+def test_rs_opt_ag():
+    _run("case_rs_opt_ag")
+
+
+def test_engine_zero_matches_single():
+    _run("case_engine_zero_matches_single")
