@@ -1,0 +1,135 @@
+"""Data-parallel (or single-worker) LeNet on MNIST-shaped data: the canonical example.
+
+Start one scheduler and N workers from this same script, as with the reference
+(examples/dp/mnist/pytorch/train_ngn_mnist_1.py:216-307):
+
+    python train_mnist_dp.py -r scheduler -w 2 -u ipc:///tmp/nk-svr.ipc -e 1
+    python train_mnist_dp.py -r worker -w 2 -k 0 -u ipc:///tmp/nk-w0.ipc -s ipc:///tmp/nk-svr.ipc -t dp
+    python train_mnist_dp.py -r worker -w 2 -k 1 -u ipc:///tmp/nk-w1.ipc -s ipc:///tmp/nk-svr.ipc -t dp
+
+Data is synthetic (uniform [0,1) images, uniform labels) unless ``--data-dir`` points at
+torchvision MNIST files.  ``--no-cuda`` keeps everything on the CPU (gloo collectives).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", ".."))
+
+import torch
+import torch.nn as nn
+
+import necklace_b200
+from necklace_b200.comm import groups as ncclgrp
+from necklace_b200.data.dtldngn import DataLoaderNgnBase
+from necklace_b200.data.dtset import SyntheticDataset
+from necklace_b200.data.sampler import SliceSampler
+from necklace_b200.models.lenet import LeNet
+from necklace_b200.trainer import tndsnc
+from necklace_b200.trainer.tnoppt import TrainerOPPytorch
+from necklace_b200.utils.argutils import attach_nk_args_parser, pg_cfg_from_args
+from necklace_b200.utils.hookbase import NklcHookBase
+from necklace_b200.utils.wrpbase import NklcWrapperBase
+
+
+class WrpDoLoss(NklcWrapperBase):
+    def __init__(self, net, ctx):
+        super().__init__(net, ctx)
+        self.ce = nn.CrossEntropyLoss()
+
+    def __call__(self, output, target):
+        return self.ce(output, target)
+
+
+class HookLogLoss(NklcHookBase):
+    """After every epoch: append the mean training loss of the epoch to a JSON file."""
+
+    def __init__(self, net, ctx, path):
+        super().__init__(net, ctx)
+        self.path, self.losses, self.epochs = path, [], []
+
+    def on_batch(self, trnr, ret=None):
+        if trnr.last_loss is not None and ret == "one_step":
+            self.losses.append(float(trnr.last_loss))
+
+    def __call__(self, trnr, *args, **kwargs):
+        self.epochs.append(sum(self.losses) / max(len(self.losses), 1))
+        self.losses = []
+        if self.path:
+            with open(self.path, "w") as f:
+                json.dump({"rank": trnr.ti, "epoch_loss": self.epochs,
+                           "weights_sum": float(sum(p.double().sum() for p in
+                                                    trnr.net.parameters()))}, f)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    attach_nk_args_parser(ap)
+    ap.add_argument("--batch-size", "-b", type=int, default=100)
+    ap.add_argument("--lr", type=float, default=0.01)
+    ap.add_argument("--momentum", type=float, default=0.0)
+    ap.add_argument("--seed", type=int, default=1)
+    ap.add_argument("--log-interval", type=int, default=100)
+    ap.add_argument("--no-cuda", action="store_true")
+    ap.add_argument("--dataset-len", type=int, default=60000)
+    ap.add_argument("--stepwise", action="store_true",
+                    help="drive every phase of every step by RPC (the reference protocol)")
+    ap.add_argument("--grad-comp-threshold", type=float, default=0.0)
+    ap.add_argument("--out", type=str, default="")
+    args = ap.parse_args()
+
+    tmode = args.tmode or ("dp" if args.world_size > 1 else "no")
+    pg_cfg = pg_cfg_from_args(args)
+    ncclgrp.init_nccl_groups_map(tmode, pg_cfg)
+
+    if args.role == "scheduler":
+        cfg = {"role": "scheduler", "url": args.url, "workers": args.world_size,
+               "wdsz": args.world_size, "rank": 0, "epochs": args.epochs,
+               "nccl_allreduce_typ": "grad", "stepwise": args.stepwise,
+               "nccl_groups_grp_map": ncclgrp.get_nccl_groups_map_grp_dict()}
+        svc = tndsnc.SVCScheduler(cfg)
+        svc.loop()
+        print("scheduler:", svc.exit_status)
+        return 0 if svc.exit_status == "finished" else 1
+
+    use_cuda = torch.cuda.is_available() and not args.no_cuda
+    necklace_b200.init(args.gpu_rank)
+    ctx = torch.device("cuda", int(args.gpu_rank)) if use_cuda else torch.device("cpu")
+    torch.manual_seed(args.seed)
+    net = LeNet()
+    opt = torch.optim.SGD(net.parameters(), lr=args.lr, momentum=args.momentum)
+
+    def dataloader_creator(rank, world):
+        ds = SyntheticDataset(args.dataset_len, (1, 28, 28), classes=10, seed=args.seed)
+        per = len(ds) // world
+        sampler = SliceSampler(indices=list(range(rank * per, (rank + 1) * per)))
+        return DataLoaderNgnBase(ds, batch_size=args.batch_size, sampler=sampler,
+                                 last_batch="discard")
+
+    trainer_cfg = {
+        "kn": args.world_size, "ti": args.rank, "ctx": ctx, "net": net, "opt": opt,
+        "loss": WrpDoLoss(net, ctx), "batch_size": args.batch_size, "epochs": args.epochs,
+        "dataset_len": args.dataset_len, "dataloader_type": "dp",
+        "dataloader_creator": dataloader_creator,
+        "dataloader_creator_args": (args.rank, args.world_size),
+        "log_interval": args.log_interval, "tmode": tmode, "pg_cfg": pg_cfg,
+        "comm_type": "gloo" if not use_cuda else args.comm_type,
+        "grad_comp_cfg": ({"grad_comp_threshold": args.grad_comp_threshold,
+                           "grad_size_threshold": 0} if args.grad_comp_threshold > 0 else None),
+    }
+    cfg = {"role": "worker", "url": args.url, "scheduler_url": args.server_url,
+           "rank": args.rank, "trainer_cls": TrainerOPPytorch, "trainer_cfg": trainer_cfg}
+    svc = tndsnc.SVCWorker(cfg)
+    hook = HookLogLoss(net, ctx, args.out)
+    svc.svr.trnr.register_hook_after_batch(hook.on_batch)
+    svc.svr.trnr.register_hook_after_epoch(hook)
+    svc.loop()
+    print(f"worker {args.rank}:", svc.exit_status)
+    return 0 if svc.exit_status == "stopped" else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())

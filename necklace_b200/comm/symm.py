@@ -22,7 +22,7 @@ import torch.distributed as dist
 from .. import _lib
 from ..ops._common import status_word
 
-_FLAG_REGION = 4096          # bytes reserved per group for epoch flags
+_FLAG_REGION = 8192          # bytes reserved per group for epoch flags (160 CTAs x 8 ranks)
 _MAX_GROUPS = 16
 
 
@@ -92,7 +92,7 @@ class PeerGroup:
         dev = heap.device
         self.ptrs_dev = torch.tensor([heap.ptrs[r] for r in ranks], dtype=torch.int64, device=dev)
         self.epoch = torch.zeros(2, dtype=torch.int32, device=dev)
-        self.max_ctas = 32
+        self.max_ctas = 148
 
     def _ctx(self):
         return (self.ptrs_dev.data_ptr(), self.flag_off)

@@ -22,8 +22,9 @@
 namespace nkb {
 
 constexpr int COMM_THREADS = 512;
-constexpr int COMM_MAX_CTAS = 64;
-constexpr int COMM_MAX_WORLD = 16;
+constexpr int COMM_MAX_CTAS = 160;
+constexpr int COMM_MAX_WORLD = 8;
+constexpr int COMM_MAX_PEER_UNROLL = 8;
 
 struct CommCtx {
   void* const* heap;   // device array [world] of heap base pointers
@@ -345,19 +346,38 @@ rs_opt_ag_kernel(CommCtx c, OptArgs o) {
     const long long s_lo = shard * c.rank;
     long long lo, hi;
     split_range(shard, gridDim.x, blockIdx.x, 8, lo, hi);
-    for (long long i = lo + (long long)threadIdx.x * 8; i < hi; i += COMM_THREADS * 8) {
+    // Peer loads are latency bound (~2-3 us over NVLink): keep two iterations of
+    // `world` 16-byte loads in flight per thread.
+    uint4 nxt[COMM_MAX_PEER_UNROLL];
+    auto load_all = [&](long long i, uint4* v) {
+#pragma unroll
+      for (int p = 0; p < COMM_MAX_PEER_UNROLL; ++p) {
+        if (p < c.world) {
+          const int m = (c.rank + p) % c.world;
+          v[p] = ld_volatile_v4(static_cast<const char*>(c.heap[m]) + o.grad_off + (s_lo + i) * 2);
+        }
+      }
+    };
+    const long long i_first = lo + (long long)threadIdx.x * 8;
+    if (i_first < hi) load_all(i_first, nxt);
+    for (long long i = i_first; i < hi; i += COMM_THREADS * 8) {
+      uint4 cur[COMM_MAX_PEER_UNROLL];
+#pragma unroll
+      for (int p = 0; p < COMM_MAX_PEER_UNROLL; ++p) cur[p] = nxt[p];
+      if (i + COMM_THREADS * 8 < hi) load_all(i + COMM_THREADS * 8, nxt);
       float g[8];
 #pragma unroll
       for (int k = 0; k < 8; ++k) g[k] = 0.f;
-      for (int p = 0; p < c.world; ++p) {
-        const int m = (c.rank + p) % c.world;
-        uint4 v = ld_volatile_v4(static_cast<const char*>(c.heap[m]) + o.grad_off + (s_lo + i) * 2);
-        uint32_t u[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          float2 f = unpack_bf16x2(u[k]);
-          g[2 * k] += f.x;
-          g[2 * k + 1] += f.y;
+      for (int p = 0; p < COMM_MAX_PEER_UNROLL; ++p) {
+        if (p < c.world) {
+          uint32_t u[4] = {cur[p].x, cur[p].y, cur[p].z, cur[p].w};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            float2 f = unpack_bf16x2(u[k]);
+            g[2 * k] += f.x;
+            g[2 * k + 1] += f.y;
+          }
         }
       }
       float4 p0 = reinterpret_cast<float4*>(o.master + i)[0];
@@ -416,7 +436,7 @@ rs_opt_ag_kernel(CommCtx c, OptArgs o) {
 }
 
 static int comm_grid(int max_ctas, long long work_items) {
-  int g = max_ctas > 0 ? max_ctas : 32;
+  int g = max_ctas > 0 ? max_ctas : 148;
   if (g > COMM_MAX_CTAS) g = COMM_MAX_CTAS;
   long long need = (work_items + COMM_THREADS - 1) / COMM_THREADS;
   if (need < 1) need = 1;

@@ -1,0 +1,3 @@
+"""Queue-based multi-process loader under the reference's module name
+(necklace/data/dtqptp.py exports DataLoaderSharedMemory)."""
+from .loaders import QueueDataLoader as DataLoaderSharedMemory  # noqa: F401

@@ -1,0 +1,210 @@
+"""Scheduler + worker processes over ipc:// on CPU (gloo), and host-side failure injection."""
+import json
+import os
+import subprocess
+import sys
+import time
+
+import pytest
+import torch
+import torch.nn as nn
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+EXAMPLE = os.path.join(ROOT, "examples", "dp", "train_mnist_dp.py")
+
+
+def _spawn(args, log):
+    return subprocess.Popen([sys.executable, EXAMPLE, *args], stdout=open(log, "w"),
+                            stderr=subprocess.STDOUT, cwd=ROOT)
+
+
+def _run_job(tmp_path, world, extra_sched=(), extra_worker=(), epochs=1, dataset_len=400,
+             batch=50, timeout=150):
+    svr = f"ipc://{tmp_path}/svr.ipc"
+    procs = [_spawn(["-r", "scheduler", "-w", str(world), "-u", svr, "-e", str(epochs),
+                     *extra_sched], tmp_path / "s.log")]
+    for r in range(world):
+        procs.append(_spawn(["-r", "worker", "-w", str(world), "-k", str(r), "-u",
+                             f"ipc://{tmp_path}/w{r}.ipc", "-s", svr,
+                             "-t", "dp" if world > 1 else "no", "--no-cuda", "-e", str(epochs),
+                             "--dataset-len", str(dataset_len), "-b", str(batch),
+                             "--out", str(tmp_path / f"o{r}.json"), *extra_worker],
+                            tmp_path / f"w{r}.log"))
+    t0 = time.time()
+    codes = []
+    for p in procs:
+        try:
+            codes.append(p.wait(timeout=max(1, timeout - (time.time() - t0))))
+        except subprocess.TimeoutExpired:
+            p.kill()
+            codes.append(-9)
+    outs = []
+    for r in range(world):
+        f = tmp_path / f"o{r}.json"
+        outs.append(json.load(open(f)) if f.exists() else None)
+    return codes, outs
+
+
+def _single_process(world, epochs, dataset_len, batch, lr=0.01, seed=1):
+    """The same training in one process on the global batch (mean of per-rank means)."""
+    sys.path.insert(0, ROOT)
+    from necklace_b200.data.dtset import SyntheticDataset
+    from necklace_b200.models.lenet import LeNet
+    torch.manual_seed(seed)
+    net = LeNet()
+    opt = torch.optim.SGD(net.parameters(), lr=lr)
+    ds = SyntheticDataset(dataset_len, (1, 28, 28), classes=10, seed=seed)
+    per = dataset_len // world
+    ce = nn.CrossEntropyLoss()
+    for _ in range(epochs):
+        for i in range(per // batch):
+            opt.zero_grad()
+            loss = 0
+            for r in range(world):
+                idx = range(r * per + i * batch, r * per + (i + 1) * batch)
+                x = torch.stack([ds[j][0] for j in idx])
+                y = torch.tensor([ds[j][1] for j in idx])
+                loss = loss + ce(net(x), y) / world
+            loss.backward()
+            opt.step()
+    return float(sum(p.double().sum() for p in net.parameters()))
+
+
+@pytest.mark.timeout(200)
+def test_mode_no_single_worker_matches_plain_loop(tmp_path):
+    codes, outs = _run_job(tmp_path, 1, epochs=2)
+    assert codes == [0, 0], open(tmp_path / "w0.log").read()[-2000:]
+    ref = _single_process(1, 2, 400, 50)
+    assert abs(outs[0]["weights_sum"] - ref) < 1e-4
+    assert len(outs[0]["epoch_loss"]) == 2
+
+
+@pytest.mark.timeout(300)
+@pytest.mark.parametrize("stepwise", [False, True])
+def test_dp_two_workers_match_single_process(tmp_path, stepwise):
+    extra = ["--stepwise"] if stepwise else []
+    codes, outs = _run_job(tmp_path, 2, extra_sched=extra)
+    assert codes == [0, 0, 0], open(tmp_path / "w0.log").read()[-2000:]
+    assert abs(outs[0]["weights_sum"] - outs[1]["weights_sum"]) < 1e-9
+    ref = _single_process(2, 1, 400, 50)
+    assert abs(outs[0]["weights_sum"] - ref) < 1e-3
+
+
+@pytest.mark.timeout(300)
+def test_dp_with_2bit_gradient_compression_keeps_ranks_in_sync(tmp_path):
+    codes, outs = _run_job(tmp_path, 2, extra_worker=["--grad-comp-threshold", "0.001"])
+    assert codes == [0, 0, 0], open(tmp_path / "w0.log").read()[-2000:]
+    assert abs(outs[0]["weights_sum"] - outs[1]["weights_sum"]) < 1e-9
+
+
+@pytest.mark.timeout(120)
+def test_scheduler_aborts_when_a_worker_never_registers(tmp_path):
+    sys.path.insert(0, ROOT)
+    from necklace_b200.trainer.service import SVCScheduler
+    svc = SVCScheduler({"url": f"ipc://{tmp_path}/svr.ipc", "workers": 2, "epochs": 1,
+                        "register_timeout": 1.0})
+    t0 = time.time()
+    svc.loop()
+    assert time.time() - t0 < 20
+    assert svc.exit_status.startswith("aborted") and "registered" in svc.exit_status
+
+
+class _StallTrainer:
+    """Fake operator: acknowledges communicator bring-up, then one rank never answers."""
+
+    def __init__(self, cfg):
+        self.cfg = cfg
+        self.ti = cfg["ti"]
+
+    def cre_nccl(self, msg=None):
+        return "ok"
+
+    def cre_nccl_nuid(self, msg=None):
+        return {"master_addr": "127.0.0.1", "master_port": 1}
+
+    def init_nccl_comm(self, msg=None):
+        return "ok"
+
+    def del_nccl_comm(self, msg=None):
+        pass
+
+    def check_msg(self, msg):
+        if self.cfg.get("mode") == "raise" and msg["cmd"] == "run_epoch" and self.ti == 1:
+            raise RuntimeError("injected failure in the training step")
+        if self.cfg.get("mode") == "stall" and msg["cmd"] == "run_epoch" and self.ti == 1:
+            time.sleep(30)
+        return {"ret": {"weights_sync": "weights_synced", "run_epoch": "epoch_end",
+                        "next_epoch": "next_epoch"}[msg["cmd"]]}
+
+    def clear(self):
+        pass
+
+
+def _worker_thread(tmp_path, rank, mode):
+    from necklace_b200.trainer.service import SVCWorker
+    svc = SVCWorker({"url": f"ipc://{tmp_path}/w{rank}.ipc",
+                     "scheduler_url": f"ipc://{tmp_path}/svr.ipc", "rank": rank,
+                     "trainer_cls": _StallTrainer, "trainer_cfg": {"mode": mode},
+                     "heartbeat": 0.2})
+    svc.loop()
+    return svc
+
+
+@pytest.mark.timeout(120)
+@pytest.mark.parametrize("mode,needle", [("raise", "injected failure"), ("stall", "timed out")])
+def test_worker_failure_mid_step_aborts_everyone(tmp_path, mode, needle):
+    """A rank raises inside a step (reported at once) or goes silent (phase deadline):
+    the scheduler broadcasts abort and every survivor leaves its loop."""
+    import threading
+    sys.path.insert(0, ROOT)
+    from necklace_b200.trainer.service import SVCScheduler
+    results = {}
+    ths = [threading.Thread(target=lambda r=r: results.__setitem__(r, _worker_thread(tmp_path, r, mode)),
+                            daemon=True) for r in range(2)]
+    for t in ths:
+        t.start()
+    svc = SVCScheduler({"url": f"ipc://{tmp_path}/svr.ipc", "workers": 2, "epochs": 1,
+                        "phase_timeout": 2.0, "register_timeout": 30})
+    svc.loop()
+    assert svc.exit_status.startswith("aborted") and needle in svc.exit_status, svc.exit_status
+    ths[0].join(timeout=10)
+    assert not ths[0].is_alive()
+    assert results[0].exit_status == "aborted"
+
+
+@pytest.mark.timeout(120)
+def test_protocol_phases_against_fake_trainer(tmp_path):
+    """Stepwise DP protocol: the scheduler issues the reference's phase sequence."""
+    import threading
+    sys.path.insert(0, ROOT)
+    from necklace_b200.trainer.service import SVCScheduler, SVCWorker
+
+    class Fake(_StallTrainer):
+        def __init__(self, cfg):
+            super().__init__(cfg)
+            self.steps = 0
+
+        def check_msg(self, msg):
+            c = msg["cmd"]
+            if c == "one_step":
+                self.steps += 1
+                return {"ret": "one_step" if self.steps <= 2 else "epoch_end"}
+            return {"ret": {"weights_sync": "weights_synced", "nccl_all_reduce": "nccl_all_reduced",
+                            "next_epoch": "next_epoch"}[c]}
+
+    def worker(rank):
+        SVCWorker({"url": f"ipc://{tmp_path}/w{rank}.ipc", "scheduler_url": f"ipc://{tmp_path}/svr.ipc",
+                   "rank": rank, "trainer_cls": Fake, "trainer_cfg": {}, "heartbeat": 0}).loop()
+
+    ths = [threading.Thread(target=worker, args=(r,), daemon=True) for r in range(2)]
+    for t in ths:
+        t.start()
+    svc = SVCScheduler({"url": f"ipc://{tmp_path}/svr.ipc", "workers": 2, "epochs": 1,
+                        "stepwise": True, "phase_timeout": 20})
+    svc.loop()
+    assert svc.exit_status == "finished"
+    seq = [fn for fn, _ in svc.history]
+    assert seq == ["fn_init_nccl_comm", "fn_weights_sync_start", "fn_one_step_start",
+                   "fn_nccl_all_reduce_start", "fn_one_step_start", "fn_nccl_all_reduce_start",
+                   "fn_one_step_start", "fn_next_epoch_start"]
+    assert svc.history[-2][1] == {0: "epoch_end", 1: "epoch_end"}
