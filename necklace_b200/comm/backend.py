@@ -68,6 +68,9 @@ def init_backend(tmode: str, cfg: dict, comm_type: str = "nccl", device=None,
             peer = heap.peer_group(ranks) if heap else None
             if rank in ranks and key in mine:
                 mine[key].attach_comm(GroupComm(pg, ranks, rank, peer))
+    if world > 1 and "pp_group" in G.get_nccl_groups_map_grp_dict():
+        from ..parallel.pipeline import create_channels
+        create_channels(G.get_nccl_groups_map_grp_dict()["pp_group"])
     return heap
 
 

@@ -87,7 +87,8 @@ class PtCudaFltnMemManager:
         self.gpu_weig = md_flatten_1d_mem_create(max_weig_size, dtype, self.device)
         self.gpu_grad = md_flatten_1d_mem_create(max_grad_size, dtype, self.device)
         self.cpu = {}  # id(module) -> (weights, grads, n_w, n_g)
-        self.on_gpu = None
+        self.on_gpu = None      # id of the module currently living in the device buffers
+        self.on_gpu_md = None
 
     def register(self, md):
         nw, ng = md_params_numel_total_size(md), md_grads_numel_total_size(md)
@@ -107,11 +108,15 @@ class PtCudaFltnMemManager:
             md_flatten_1d_mem_copy(self.gpu_grad, g, ng)
             if self.device.type == "cuda":
                 torch.cuda.current_stream().synchronize()
-            self.on_gpu = None
+            self.on_gpu = self.on_gpu_md = None
         md_params_to_flatten_1d_mem(md, w)
         md_grads_to_flatten_1d_mem(md, g)
 
     def md_to_gpu(self, md):
+        if self.on_gpu == id(md):
+            return  # already resident: its device gradients must not be overwritten
+        if self.on_gpu_md is not None:
+            self.md_to_cpu(self.on_gpu_md)  # save the resident module first
         if id(md) not in self.cpu:
             self.register(md)
         w, g, nw, ng = self.cpu[id(md)]
@@ -128,7 +133,7 @@ class PtCudaFltnMemManager:
                 n = p.numel()
                 p.grad = self.gpu_grad.narrow(0, off, n).view(p.data.shape)
                 off += n
-        self.on_gpu = id(md)
+        self.on_gpu, self.on_gpu_md = id(md), md
 
     def weights_flat(self, md):
         return self.gpu_weig[:self.cpu[id(md)][2]]
