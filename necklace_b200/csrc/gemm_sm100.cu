@@ -163,6 +163,133 @@ __device__ __forceinline__ void stage_load_f32(uint8_t* stg, int lane, const flo
   stage_load_t<float>(stg, lane, g, ld, rv, cv);
 }
 
+// Epilogue of one 128 x BN accumulator slab: this warp's 32 rows (TMEM lanes), BN
+// columns starting at global column n0; fused math, then staged coalesced stores.
+template <int BN>
+__device__ __forceinline__ void epilogue_tile(const GemmArgs& g, uint8_t* stg, int lane,
+                                              uint32_t t_addr, int row0, int rows_valid, int n0,
+                                              float alpha, bool bias_vec) {
+#pragma unroll 1
+  for (int cc = 0; cc < BN / 64; ++cc) {
+    uint32_t r[64];
+    tmem_ld_32x32(t_addr + cc * 64, r);
+    tmem_ld_32x32(t_addr + cc * 64 + 32, r + 32);
+    tmem_ld_wait();
+    const int col0 = n0 + cc * 64;
+    if (rows_valid == 0 || col0 >= g.N) continue;  // warp-uniform
+    const int cols_valid = (g.N - col0) < 64 ? (g.N - col0) : 64;
+    float v[64];
+#pragma unroll
+    for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]) * alpha;
+    if (g.bias) {
+      if (bias_vec && cols_valid == 64 && (col0 & 7) == 0) {
+        const uint4* bp = reinterpret_cast<const uint4*>(g.bias + col0);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          uint4 b = __ldg(bp + q);
+          uint32_t w[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float2 f = unpack_bf16x2(w[j]);
+            v[q * 8 + 2 * j] += f.x;
+            v[q * 8 + 2 * j + 1] += f.y;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 64; ++i)
+          if (i < cols_valid) v[i] += __bfloat162float(g.bias[col0 + i]);
+      }
+    }
+    if (g.epi == NKB_EPI_GELU_FWD) {
+      stage_put_bf16(stg, lane, v);
+      stage_store_bf16(stg, lane, g.aux_out + (long long)row0 * g.ldaux + col0, g.ldaux,
+                       rows_valid, cols_valid);
+#pragma unroll
+      for (int i = 0; i < 64; ++i) v[i] = gelu_tanh(v[i]);
+    } else if (g.epi == NKB_EPI_GELU_BWD) {
+      stage_load_bf16(stg, lane, g.aux_in + (long long)row0 * g.ldaux + col0, g.ldaux,
+                      rows_valid, cols_valid);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        uint4 z = stage_get(stg, lane, q);
+        uint32_t w[4] = {z.x, z.y, z.z, z.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 f = unpack_bf16x2(w[j]);
+          v[q * 8 + 2 * j] *= gelu_tanh_grad(f.x);
+          v[q * 8 + 2 * j + 1] *= gelu_tanh_grad(f.y);
+        }
+      }
+    } else if (g.epi == NKB_EPI_RELU) {
+#pragma unroll
+      for (int i = 0; i < 64; ++i) v[i] = fmaxf(v[i], 0.f);
+    }
+    if (g.res) {
+      stage_load_bf16(stg, lane, g.res + (long long)row0 * g.ldres + col0, g.ldres, rows_valid,
+                      cols_valid);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        uint4 z = stage_get(stg, lane, q);
+        uint32_t w[4] = {z.x, z.y, z.z, z.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 f = unpack_bf16x2(w[j]);
+          v[q * 8 + 2 * j] += f.x;
+          v[q * 8 + 2 * j + 1] += f.y;
+        }
+      }
+    }
+    if (g.c_fp32) {
+      float* cbase = reinterpret_cast<float*>(g.C) + (long long)row0 * g.ldc + col0;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int cv = cols_valid - half * 32;
+        if (cv <= 0) break;
+        if (g.accumulate) {
+          stage_load_f32(stg, lane, cbase + half * 32, g.ldc, rows_valid, cv);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            uint4 z = stage_get(stg, lane, q);
+            v[half * 32 + q * 4 + 0] += __uint_as_float(z.x);
+            v[half * 32 + q * 4 + 1] += __uint_as_float(z.y);
+            v[half * 32 + q * 4 + 2] += __uint_as_float(z.z);
+            v[half * 32 + q * 4 + 3] += __uint_as_float(z.w);
+          }
+        }
+        __syncwarp();
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          stage_set(stg, lane, q,
+                    make_uint4(__float_as_uint(v[half * 32 + q * 4]),
+                               __float_as_uint(v[half * 32 + q * 4 + 1]),
+                               __float_as_uint(v[half * 32 + q * 4 + 2]),
+                               __float_as_uint(v[half * 32 + q * 4 + 3])));
+        stage_store_f32(stg, lane, cbase + half * 32, g.ldc, rows_valid, cv);
+      }
+    } else {
+      __nv_bfloat16* cbase =
+          reinterpret_cast<__nv_bfloat16*>(g.C) + (long long)row0 * g.ldc + col0;
+      if (g.accumulate) {
+        stage_load_bf16(stg, lane, cbase, g.ldc, rows_valid, cols_valid);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          uint4 z = stage_get(stg, lane, q);
+          uint32_t w[4] = {z.x, z.y, z.z, z.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float2 f = unpack_bf16x2(w[j]);
+            v[q * 8 + 2 * j] += f.x;
+            v[q * 8 + 2 * j + 1] += f.y;
+          }
+        }
+      }
+      stage_put_bf16(stg, lane, v);
+      stage_store_bf16(stg, lane, cbase, g.ldc, rows_valid, cols_valid);
+    }
+  }
+}
+
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -341,125 +468,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       tc_fence_after();
       const uint32_t t_addr = tmem_base + (uint32_t(lane_grp * 32) << 16) + acc * BN;
-#pragma unroll 1
-      for (int cc = 0; cc < BN / 64; ++cc) {
-        uint32_t r[64];
-        tmem_ld_32x32(t_addr + cc * 64, r);
-        tmem_ld_32x32(t_addr + cc * 64 + 32, r + 32);
-        tmem_ld_wait();
-        const int col0 = n0 + cc * 64;
-        if (rows_valid == 0 || col0 >= g.N) continue;  // warp-uniform
-        const int cols_valid = (g.N - col0) < 64 ? (g.N - col0) : 64;
-        float v[64];
-#pragma unroll
-        for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]) * alpha;
-        if (g.bias) {
-          if (bias_vec && cols_valid == 64 && (col0 & 7) == 0) {
-            const uint4* bp = reinterpret_cast<const uint4*>(g.bias + col0);
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-              uint4 b = __ldg(bp + q);
-              uint32_t w[4] = {b.x, b.y, b.z, b.w};
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                float2 f = unpack_bf16x2(w[j]);
-                v[q * 8 + 2 * j] += f.x;
-                v[q * 8 + 2 * j + 1] += f.y;
-              }
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 64; ++i)
-              if (i < cols_valid) v[i] += __bfloat162float(g.bias[col0 + i]);
-          }
-        }
-        if (g.epi == NKB_EPI_GELU_FWD) {
-          stage_put_bf16(stg, lane, v);
-          stage_store_bf16(stg, lane, g.aux_out + (long long)row0 * g.ldaux + col0, g.ldaux,
-                           rows_valid, cols_valid);
-#pragma unroll
-          for (int i = 0; i < 64; ++i) v[i] = gelu_tanh(v[i]);
-        } else if (g.epi == NKB_EPI_GELU_BWD) {
-          stage_load_bf16(stg, lane, g.aux_in + (long long)row0 * g.ldaux + col0, g.ldaux,
-                          rows_valid, cols_valid);
-#pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            uint4 z = stage_get(stg, lane, q);
-            uint32_t w[4] = {z.x, z.y, z.z, z.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              float2 f = unpack_bf16x2(w[j]);
-              v[q * 8 + 2 * j] *= gelu_tanh_grad(f.x);
-              v[q * 8 + 2 * j + 1] *= gelu_tanh_grad(f.y);
-            }
-          }
-        } else if (g.epi == NKB_EPI_RELU) {
-#pragma unroll
-          for (int i = 0; i < 64; ++i) v[i] = fmaxf(v[i], 0.f);
-        }
-        if (g.res) {
-          stage_load_bf16(stg, lane, g.res + (long long)row0 * g.ldres + col0, g.ldres, rows_valid,
-                          cols_valid);
-#pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            uint4 z = stage_get(stg, lane, q);
-            uint32_t w[4] = {z.x, z.y, z.z, z.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              float2 f = unpack_bf16x2(w[j]);
-              v[q * 8 + 2 * j] += f.x;
-              v[q * 8 + 2 * j + 1] += f.y;
-            }
-          }
-        }
-        if (g.c_fp32) {
-          float* cbase = reinterpret_cast<float*>(g.C) + (long long)row0 * g.ldc + col0;
-#pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            const int cv = cols_valid - half * 32;
-            if (cv <= 0) break;
-            if (g.accumulate) {
-              stage_load_f32(stg, lane, cbase + half * 32, g.ldc, rows_valid, cv);
-#pragma unroll
-              for (int q = 0; q < 8; ++q) {
-                uint4 z = stage_get(stg, lane, q);
-                v[half * 32 + q * 4 + 0] += __uint_as_float(z.x);
-                v[half * 32 + q * 4 + 1] += __uint_as_float(z.y);
-                v[half * 32 + q * 4 + 2] += __uint_as_float(z.z);
-                v[half * 32 + q * 4 + 3] += __uint_as_float(z.w);
-              }
-            }
-            __syncwarp();
-#pragma unroll
-            for (int q = 0; q < 8; ++q)
-              stage_set(stg, lane, q,
-                        make_uint4(__float_as_uint(v[half * 32 + q * 4]),
-                                   __float_as_uint(v[half * 32 + q * 4 + 1]),
-                                   __float_as_uint(v[half * 32 + q * 4 + 2]),
-                                   __float_as_uint(v[half * 32 + q * 4 + 3])));
-            stage_store_f32(stg, lane, cbase + half * 32, g.ldc, rows_valid, cv);
-          }
-        } else {
-          __nv_bfloat16* cbase =
-              reinterpret_cast<__nv_bfloat16*>(g.C) + (long long)row0 * g.ldc + col0;
-          if (g.accumulate) {
-            stage_load_bf16(stg, lane, cbase, g.ldc, rows_valid, cols_valid);
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-              uint4 z = stage_get(stg, lane, q);
-              uint32_t w[4] = {z.x, z.y, z.z, z.w};
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                float2 f = unpack_bf16x2(w[j]);
-                v[q * 8 + 2 * j] += f.x;
-                v[q * 8 + 2 * j + 1] += f.y;
-              }
-            }
-          }
-          stage_put_bf16(stg, lane, v);
-          stage_store_bf16(stg, lane, cbase, g.ldc, rows_valid, cols_valid);
-        }
-      }
+      epilogue_tile<BN>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec);
       tc_fence_before();
       mbar_arrive(&acc_empty[acc]);
       if (++acc == 2) {
@@ -480,6 +489,218 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+
+// ------------------------------------------------------------------ CTA-pair kernel
+// Two CTAs of a cluster compute one 256 x 256 tile with tcgen05.mma.cta_group::2:
+// each CTA loads its own 128 rows of A and its own 128 columns of B (plain per-CTA
+// TMA loads whose bytes are counted on the leader's barrier), the leader CTA issues
+// the MMAs, which read both CTAs' shared memory, and each CTA's TMEM receives its
+// 128 x 256 half of the accumulator.  Operand traffic per FLOP is 2/3 of the
+// single-CTA 128 x 256 tile and a stage is 32 KB, so six stages fit.
+constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_B_BYTES = 128 * BK * 2;
+constexpr int PAIR_STAGE_BYTES = A_STAGE_BYTES + PAIR_B_BYTES;
+
+template <bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
+                      const __grid_constant__ CUtensorMap tmB, const GemmArgs g) {
+  constexpr int BN = 256;
+  constexpr uint32_t TMEM_COLS = 512;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                              ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + PAIR_STAGES * PAIR_STAGE_BYTES +
+                                                   4 * EPI_STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + PAIR_STAGES;
+  uint64_t* acc_full = empty_bar + PAIR_STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+  const int num_m2 = (g.M + 255) / 256;
+  const int num_tiles = num_m2 * g.num_n_blocks;
+  const int KB = (g.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < PAIR_STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 8);  // 4 epilogue warps x 2 CTAs arrive on the leader's copy
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc_2cta(tmem_slot, TMEM_COLS);
+    tmem_relinquish_2cta();
+    tc_fence_before();
+  }
+  __syncthreads();
+  cluster_arrive();  // the peer's barriers must exist before anything signals them
+  cluster_wait();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = pair; t < num_tiles && ok; t += npairs) {
+        const int mb2 = t % num_m2, nb = t / num_m2;
+        const int m0 = mb2 * 256 + (int)rank * 128;
+        const int nB = nb * BN + (int)rank * 128;
+        if (g.ready_flags) {
+          if (m0 < g.M) {
+            int f0 = m0 / g.rows_per_flag;
+            int f1 = (min(m0 + BM, g.M) - 1) / g.rows_per_flag;
+            for (int f = f0; f <= f1 && ok; ++f)
+              if (!wait_flag_ge(g.ready_flags + f, g.ready_target)) {
+                set_error(g.status, abort_flag, NKB_ERR_FLAG_WAIT);
+                ok = false;
+              }
+          }
+          if (!ok) break;
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+        }
+        for (int kb = 0; kb < KB; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
+            set_error(g.status, abort_flag, NKB_ERR_EMPTY_WAIT);
+            ok = false;
+            break;
+          }
+          uint8_t* sA = smem + stage * PAIR_STAGE_BYTES;
+          uint8_t* sB = sA + A_STAGE_BYTES;
+          if (leader) mbar_expect_tx(&full_bar[stage], 2 * PAIR_STAGE_BYTES);
+          const uint32_t bar = mapa_shared(smem_u32(&full_bar[stage]), 0);
+          if constexpr (!A_MN) {
+            tma_load_2d_pair(sA, &tmA, bar, kb * BK, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+              tma_load_2d_pair(sA + j * (64 * BK * 2), &tmA, bar, m0 + j * 64, kb * BK);
+          }
+          if constexpr (!B_MN) {
+            tma_load_2d_pair(sB, &tmB, bar, kb * BK, nB);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+              tma_load_2d_pair(sB + j * (64 * BK * 2), &tmB, bar, nB + j * 64, kb * BK);
+          }
+          if (++stage == PAIR_STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = umma_idesc_bf16(256, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = pair; t < num_tiles && ok; t += npairs) {
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag)) {
+          set_error(g.status, abort_flag, NKB_ERR_ACC_FREE);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < KB; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
+            set_error(g.status, abort_flag, NKB_ERR_TMA_WAIT);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t aA = smem_u32(smem + stage * PAIR_STAGE_BYTES);
+          const uint32_t aB = aA + A_STAGE_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            uint64_t da, db;
+            if constexpr (!A_MN)
+              da = umma_desc_sw128(aA + k * (UMMA_K * 2), 16, 1024);
+            else
+              da = umma_desc_sw128(aA + k * (UMMA_K * 128), 64 * BK * 2, 1024);
+            if constexpr (!B_MN)
+              db = umma_desc_sw128(aB + k * (UMMA_K * 2), 16, 1024);
+            else
+              db = umma_desc_sw128(aB + k * (UMMA_K * 128), 64 * BK * 2, 1024);
+            umma_bf16_ss_2cta(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit_2cta(&empty_bar[stage], 3);  // frees the stage in both CTAs
+          if (++stage == PAIR_STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        umma_commit_2cta(&acc_full[acc], 3);
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+  } else {
+    const int lane_grp = warp & 3;
+    uint8_t* stg = smem + PAIR_STAGES * PAIR_STAGE_BYTES + (warp - 2) * EPI_STAGE_BYTES;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const float alpha = g.alpha_dev ? g.alpha * __ldg(g.alpha_dev) : g.alpha;
+    const bool bias_vec = g.bias && ((reinterpret_cast<uintptr_t>(g.bias) & 15) == 0);
+    for (int t = pair; t < num_tiles; t += npairs) {
+      const int mb2 = t % num_m2, nb = t / num_m2;
+      const int row0 = mb2 * 256 + (int)rank * 128 + lane_grp * 32;
+      const int n0 = nb * BN;
+      int rows_valid = g.M - row0;
+      rows_valid = rows_valid < 0 ? 0 : (rows_valid > 32 ? 32 : rows_valid);
+      if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag)) {
+        set_error(g.status, abort_flag, NKB_ERR_ACC_WAIT);
+        break;
+      }
+      tc_fence_after();
+      const uint32_t t_addr = tmem_base + (uint32_t(lane_grp * 32) << 16) + acc * BN;
+      epilogue_tile<BN>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (leader) mbar_arrive(&acc_empty[acc]);
+        else mbar_arrive_cluster(mapa_shared(smem_u32(&acc_empty[acc]), 0));
+      }
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_arrive();  // neither CTA may leave while the pair's MMAs can still read its smem
+  cluster_wait();
+  if (warp == 1) {
+    if (*abort_flag)
+      for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+    tc_fence_after();
+    tmem_dealloc_2cta(tmem_base, TMEM_COLS);
   }
 }
 
@@ -519,6 +740,7 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* base, long long inner, long 
 }
 
 static int g_num_sms = 0;
+static int g_pair_enabled = 1;  // CTA-pair tiles in the automatic choice
 int num_sms() {
   if (!g_num_sms) {
     int dev = 0;
@@ -553,9 +775,35 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs&
   return (int)cudaGetLastError();
 }
 
+template <bool A_MN, bool B_MN>
+static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs& g,
+                            int max_ctas, cudaStream_t stream) {
+  constexpr int smem_bytes = PAIR_STAGES * PAIR_STAGE_BYTES + 4 * EPI_STAGE_BYTES + 1024 + 256;
+  static bool configured = false;
+  auto kern = gemm_bf16_pair_kernel<A_MN, B_MN>;
+  if (!configured) {
+    cudaError_t e =
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  g.num_m_blocks = (g.M + 255) / 256;
+  g.num_n_blocks = (g.N + 255) / 256;
+  int tiles = g.num_m_blocks * g.num_n_blocks;
+  int ctas = num_sms();
+  if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
+  ctas &= ~1;
+  if (2 * tiles < ctas) ctas = 2 * tiles;
+  if (ctas < 2) ctas = 2;
+  kern<<<ctas, GEMM_THREADS, smem_bytes, stream>>>(tmA, tmB, g);
+  return (int)cudaGetLastError();
+}
+
 }  // namespace nkb
 
 using namespace nkb;
+
+extern "C" void nkb_gemm_set_pair(int enabled) { nkb::g_pair_enabled = enabled; }
 
 extern "C" int nkb_gemm_bf16(const void* A, long long lda, int a_mn, const void* B, long long ldb,
                              int b_mn, void* C, long long ldc, int c_fp32, int accumulate, int M,
@@ -583,31 +831,43 @@ extern "C" int nkb_gemm_bf16(const void* A, long long lda, int a_mn, const void*
   g.rows_per_flag = rows_per_flag > 0 ? rows_per_flag : 1;
   g.ready_target = ready_target;
 
-  // Tile width: 256 unless N is small or the 256-wide grid would leave most SMs idle.
+  // Tile choice.  bn_hint: 0 = automatic, 128 / 256 = single-CTA tile of that width,
+  // 512 = CTA-pair 256 x 256 tile.
   int BN = 256;
+  bool pair = false;
   if (bn_hint == 128 || bn_hint == 256) {
     BN = bn_hint;
+  } else if (bn_hint == 512) {
+    pair = true;
   } else {
+    int sms = num_sms();
     long long mblk = (M + BM - 1) / BM;
     long long t256 = mblk * ((N + 255) / 256);
     long long t128 = mblk * ((N + 127) / 128);
-    int sms = num_sms();
-    // rounds of the persistent loop, in units of a 128-wide tile
+    // rounds of the persistent loop, in units of a 128 x 128 tile's work
     long long r256 = ((t256 + sms - 1) / sms) * 2;
     long long r128 = ((t128 + sms - 1) / sms);
     if (N <= 128 || r128 < r256) BN = 128;
+    long long tp = ((M + 255) / 256) * (long long)((N + 255) / 256);
+    long long rp = ((tp + sms / 2 - 1) / (sms / 2)) * 2;
+    if (g_pair_enabled && M >= 256 && N >= 256 && rp <= (BN == 256 ? r256 : r128)) pair = true;
   }
-
   CUtensorMap tmA, tmB;
   int rc;
   if (!a_mn) rc = make_tmap_bf16_2d(&tmA, A, K, M, lda, BK, BM);
   else rc = make_tmap_bf16_2d(&tmA, A, M, K, lda, 64, BK);
   if (rc) return rc;
-  if (!b_mn) rc = make_tmap_bf16_2d(&tmB, B, K, N, ldb, BK, BN);
+  if (!b_mn) rc = make_tmap_bf16_2d(&tmB, B, K, N, ldb, BK, pair ? 128 : BN);
   else rc = make_tmap_bf16_2d(&tmB, B, N, K, ldb, 64, BK);
   if (rc) return rc;
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (pair) {
+    if (!a_mn && !b_mn) return launch_gemm_pair<false, false>(tmA, tmB, g, max_ctas, s);
+    if (!a_mn && b_mn) return launch_gemm_pair<false, true>(tmA, tmB, g, max_ctas, s);
+    if (a_mn && !b_mn) return launch_gemm_pair<true, false>(tmA, tmB, g, max_ctas, s);
+    return launch_gemm_pair<true, true>(tmA, tmB, g, max_ctas, s);
+  }
 #define NKB_DISPATCH(BN_)                                                              \
   if (!a_mn && !b_mn) return launch_gemm<BN_, false, false>(tmA, tmB, g, max_ctas, s); \
   if (!a_mn && b_mn) return launch_gemm<BN_, false, true>(tmA, tmB, g, max_ctas, s);   \

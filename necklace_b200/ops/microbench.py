@@ -53,9 +53,13 @@ def bench_gemm(flush):
         Bt = B if b_mn else B.t()
         ms_t = _time(lambda: torch.matmul(At, Bt, out=out), flush=flush)
         fl = 2.0 * M * N * K
+        ms_1 = _time(lambda: gemm(A, B, a_mn=a_mn, b_mn=b_mn, out=out, bn=256), flush=flush)
+        ms_2 = _time(lambda: gemm(A, B, a_mn=a_mn, b_mn=b_mn, out=out, bn=512), flush=flush)
         rows.append({"op": "gemm", "label": label, "M": M, "N": N, "K": K, "ms": round(ms, 4),
-                     "tflops": round(fl / ms / 1e9, 1), "torch_ms": round(ms_t, 4),
-                     "torch_tflops": round(fl / ms_t / 1e9, 1)})
+                     "tflops": round(fl / ms / 1e9, 1),
+                     "tflops_1cta_256": round(fl / ms_1 / 1e9, 1),
+                     "tflops_pair_256x256": round(fl / ms_2 / 1e9, 1),
+                     "torch_ms": round(ms_t, 4), "torch_tflops": round(fl / ms_t / 1e9, 1)})
         print(json.dumps(rows[-1]), flush=True)
     return rows
 
