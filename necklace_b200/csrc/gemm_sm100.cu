@@ -840,17 +840,20 @@ extern "C" int nkb_gemm_bf16(const void* A, long long lda, int a_mn, const void*
   } else if (bn_hint == 512) {
     pair = true;
   } else {
+    // cost = rounds of the persistent loop x work per round / measured relative
+    // throughput of the tile kind (pair 1.0, single-CTA 128x256 0.88, 128x128 0.68)
     int sms = num_sms();
     long long mblk = (M + BM - 1) / BM;
     long long t256 = mblk * ((N + 255) / 256);
     long long t128 = mblk * ((N + 127) / 128);
-    // rounds of the persistent loop, in units of a 128 x 128 tile's work
-    long long r256 = ((t256 + sms - 1) / sms) * 2;
-    long long r128 = ((t128 + sms - 1) / sms);
-    if (N <= 128 || r128 < r256) BN = 128;
+    double c256 = (double)((t256 + sms - 1) / sms) * 2.0 / 0.88;
+    double c128 = (double)((t128 + sms - 1) / sms) * 1.0 / 0.68;
+    double best = c256;
+    if (N <= 128 || c128 < c256) { BN = 128; best = c128; }
     long long tp = ((M + 255) / 256) * (long long)((N + 255) / 256);
-    long long rp = ((tp + sms / 2 - 1) / (sms / 2)) * 2;
-    if (g_pair_enabled && M >= 256 && N >= 256 && rp <= (BN == 256 ? r256 : r128)) pair = true;
+    int npair = sms / 2;
+    double cp = (double)((tp + npair - 1) / npair) * 2.0;
+    if (g_pair_enabled && M > 128 && N > 128 && cp <= best) pair = true;
   }
   CUtensorMap tmA, tmB;
   int rc;

@@ -129,6 +129,15 @@ int nkb_comm_rs_opt_ag(void** heap, long long flag_off, long long grad_off, long
                        float gscale, int first_step, const float* hyper_dev, int rank, int world,
                        int* epoch, int* status, int max_ctas, void* stream);
 
+// ---- elementwise.cu ----------------------------------------------------------
+// Rotary embedding in place on q and k of a packed [T, 3*H*D] bf16 buffer
+// (pairs (i, i + D/2), angle = (t % S + pos_offset) * base^(-2i/D)); backward = inverse.
+int nkb_rope(void* qkv, int T, int S, int H, int D, float base, int backward, int pos_offset,
+             void* stream);
+// gu = [T, 2F] (gate | up) ; h = silu(gate) * up ; dgu from dh
+int nkb_swiglu_fwd(const void* gu, void* h, long long T, int F, void* stream);
+int nkb_swiglu_bwd(const void* gu, const void* dh, void* dgu, long long T, int F, void* stream);
+
 int nkb_num_sms(void);
 const char* nkb_build_info(void);
 
