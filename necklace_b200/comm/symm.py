@@ -160,6 +160,33 @@ class PeerGroup:
         _lib.count_launch()
 
 
+    def ag_gemm(self, x_full: torch.Tensor, w: torch.Tensor, *, out=None, bias=None, b_mn=False,
+                ag_ctas: int = 8, bn: int = 0) -> torch.Tensor:
+        """``out = all_gather_rows(x) @ w^T`` in one kernel.  ``x_full`` is a heap tensor
+        ``[world * R, K]`` whose rows ``[rank*R, (rank+1)*R)`` hold this rank's shard; the
+        other rows are filled by the kernel's copy CTAs (peer loads) while its GEMM CTAs
+        already work on the local rows."""
+        from ..ops._common import ptr
+        M, K = x_full.shape
+        R = M // self.world
+        N = w.shape[1] if b_mn else w.shape[0]
+        if out is None:
+            out = torch.empty(M, N, dtype=torch.bfloat16, device=x_full.device)
+        nblk = self.world * ((R + 127) // 128)
+        flags = getattr(self, "_ag_flags", None)
+        if flags is None or flags.numel() < nblk:
+            flags = torch.zeros(max(nblk, 256), dtype=torch.int32, device=x_full.device)
+            self._ag_flags = flags
+        _lib.call("nkb_ag_gemm_bf16", self.ptrs_dev.data_ptr(), self.flag_off,
+                  self.heap.offset_of(x_full), self.rank, self.world, R, self.epoch.data_ptr(),
+                  flags.data_ptr(), int(ag_ctas), x_full.stride(0), w.data_ptr(), w.stride(0),
+                  int(b_mn), out.data_ptr(), out.stride(0), int(out.dtype == torch.float32), N, K,
+                  ptr(bias), None, 0, 0, None, 0, x_full.data_ptr(),
+                  status_word(self.heap.device).data_ptr(), int(bn), _lib.stream_ptr())
+        _lib.count_launch()
+        return out
+
+
 class TorchGroup:
     """Same surface as ``PeerGroup`` on top of ``torch.distributed`` collectives
     (gloo on CPU, NCCL on GPU).  It is the CPU test double and the NCCL baseline."""

@@ -19,6 +19,7 @@
 // `status`, releases its TMEM and returns.
 #include "ptx.cuh"
 #include "nkb_api.h"
+#include "comm_dev.cuh"
 
 namespace nkb {
 
@@ -51,7 +52,60 @@ struct GemmArgs {
   const int* ready_flags;
   int rows_per_flag;
   int ready_target;
+  // All-gather fused in front of the GEMM (optional, ag_ctas > 0): A is the
+  // concatenation of `world` row shards, shard q living at the same offset of rank q's
+  // symmetric heap.  The first ag_ctas CTAs pull the remote shards into this rank's
+  // copy (plain peer loads) and raise one flag per 128-row block; the GEMM CTAs
+  // (which only ever read local memory through TMA) wait on those flags, starting
+  // with the local shard.  ready_flags doubles as the flag array; the target epoch is
+  // *ag_epoch + 1 (advanced by a follow-up kernel).
+  int ag_ctas;
+  CommCtx ag;
+  long long ag_data_off;   // byte offset of A inside every heap
+  int ag_rows_per_rank;
+  long long ag_row_bytes;  // bytes to copy per row (K * 2)
+  long long ag_pitch;      // row pitch in bytes
 };
+
+// Copy role of the fused all-gather (see GemmArgs).  One flag per 128-row block.
+__device__ __noinline__ static void ag_copy_role(const GemmArgs& g) {
+  const CommCtx& c = g.ag;
+  const int e = *reinterpret_cast<volatile int*>(c.epoch) + 1;
+  int* flags = const_cast<int*>(g.ready_flags);
+  const int R = g.ag_rows_per_rank;
+  const int blocks_per_rank = (R + 127) / 128;
+  bool ok = cta_barrier(c, 2 * e - 1);  // every rank's shard is complete
+  if (ok) {
+    // local shard: ready at once
+    for (int b = blockIdx.x * blockDim.x + threadIdx.x; b < blocks_per_rank;
+         b += g.ag_ctas * blockDim.x)
+      st_release_sys(flags + c.rank * blocks_per_rank + b, e);
+    char* mine = static_cast<char*>(c.heap[c.rank]) + g.ag_data_off;
+    const long long v_per_row = g.ag_row_bytes >> 4;
+    for (int p = 1; p < c.world; ++p) {
+      const int q = (c.rank + p) % c.world;
+      const char* theirs = static_cast<const char*>(c.heap[q]) + g.ag_data_off;
+      for (int b = blockIdx.x; b < blocks_per_rank; b += g.ag_ctas) {
+        const int r0 = q * R + b * 128;
+        const int nrows = min(128, R - b * 128);
+        const long long total = (long long)nrows * v_per_row;
+        for (long long i = threadIdx.x; i < total; i += blockDim.x) {
+          const long long row = r0 + i / v_per_row, col = (i % v_per_row) << 4;
+          uint4 v = ld_volatile_v4(theirs + row * g.ag_pitch + col);
+          *reinterpret_cast<uint4*>(mine + row * g.ag_pitch + col) = v;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+          __threadfence();
+          st_release_sys(flags + q * blocks_per_rank + b, e);
+        }
+      }
+    }
+    cta_barrier(c, 2 * e);  // peers may overwrite their shards only after everyone pulled
+  }
+}
+
+__global__ void epoch_bump_kernel(int* epoch) { epoch[0] += 1; }
 
 __device__ __forceinline__ float gelu_tanh(float x) {
   const float k0 = 0.7978845608028654f, k1 = 0.044715f;
@@ -311,6 +365,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
+  if ((int)blockIdx.x < g.ag_ctas) {
+    ag_copy_role(g);
+    return;
+  }
+  const int cta_id = blockIdx.x - g.ag_ctas, n_ctas = gridDim.x - g.ag_ctas;
+  const int ready_target = g.ag_ctas ? *reinterpret_cast<volatile int*>(g.ag.epoch) + 1
+                                     : g.ready_target;
+  // with a fused all-gather the local shard's row blocks come first
+  const int mb_shift = g.ag_ctas ? g.ag.rank * ((g.ag_rows_per_rank + BM - 1) / BM) : 0;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_tiles = g.num_m_blocks * g.num_n_blocks;
@@ -345,15 +408,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        const int mb = t % g.num_m_blocks, nb = t / g.num_m_blocks;
+      for (int t = cta_id; t < num_tiles && ok; t += n_ctas) {
+        const int mb = (t % g.num_m_blocks + mb_shift) % g.num_m_blocks, nb = t / g.num_m_blocks;
         const int m0 = mb * BM, n0 = nb * BN;
         if (g.ready_flags) {
           int f0 = m0 / g.rows_per_flag;
           int m_last = min(m0 + BM, g.M) - 1;
           int f1 = m_last / g.rows_per_flag;
           for (int f = f0; f <= f1 && ok; ++f) {
-            if (!wait_flag_ge(g.ready_flags + f, g.ready_target)) {
+            if (!wait_flag_ge(g.ready_flags + f, ready_target)) {
               set_error(g.status, abort_flag, NKB_ERR_FLAG_WAIT);
               ok = false;
             }
@@ -402,7 +465,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int t = cta_id; t < num_tiles && ok; t += n_ctas) {
         if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag)) {
           set_error(g.status, abort_flag, NKB_ERR_ACC_FREE);
           break;
@@ -456,8 +519,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint32_t acc_phase = 0;
     const float alpha = g.alpha_dev ? g.alpha * __ldg(g.alpha_dev) : g.alpha;
     const bool bias_vec = g.bias && ((reinterpret_cast<uintptr_t>(g.bias) & 15) == 0);
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
-      const int mb = t % g.num_m_blocks, nb = t / g.num_m_blocks;
+    for (int t = cta_id; t < num_tiles; t += n_ctas) {
+      const int mb = (t % g.num_m_blocks + mb_shift) % g.num_m_blocks, nb = t / g.num_m_blocks;
       const int row0 = mb * BM + lane_grp * 32;  // first row of this warp's slab
       const int n0 = nb * BN;
       int rows_valid = g.M - row0;
@@ -521,12 +584,19 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
+  if ((int)blockIdx.x < g.ag_ctas) {  // ag_ctas is even: whole clusters take the copy role
+    ag_copy_role(g);
+    return;
+  }
+  const int ready_target = g.ag_ctas ? *reinterpret_cast<volatile int*>(g.ag.epoch) + 1
+                                     : g.ready_target;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
-  const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+  const int pair = ((int)blockIdx.x - g.ag_ctas) >> 1, npairs = ((int)gridDim.x - g.ag_ctas) >> 1;
   const int num_m2 = (g.M + 255) / 256;
+  const int mb_shift = g.ag_ctas ? g.ag.rank * ((g.ag_rows_per_rank + 255) / 256) : 0;
   const int num_tiles = num_m2 * g.num_n_blocks;
   const int KB = (g.K + BK - 1) / BK;
 
@@ -561,7 +631,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       uint32_t phase = 0;
       bool ok = true;
       for (int t = pair; t < num_tiles && ok; t += npairs) {
-        const int mb2 = t % num_m2, nb = t / num_m2;
+        const int mb2 = (t % num_m2 + mb_shift) % num_m2, nb = t / num_m2;
         const int m0 = mb2 * 256 + (int)rank * 128;
         const int nB = nb * BN + (int)rank * 128;
         if (g.ready_flags) {
@@ -569,7 +639,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
             int f0 = m0 / g.rows_per_flag;
             int f1 = (min(m0 + BM, g.M) - 1) / g.rows_per_flag;
             for (int f = f0; f <= f1 && ok; ++f)
-              if (!wait_flag_ge(g.ready_flags + f, g.ready_target)) {
+              if (!wait_flag_ge(g.ready_flags + f, ready_target)) {
                 set_error(g.status, abort_flag, NKB_ERR_FLAG_WAIT);
                 ok = false;
               }
@@ -667,7 +737,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
     const float alpha = g.alpha_dev ? g.alpha * __ldg(g.alpha_dev) : g.alpha;
     const bool bias_vec = g.bias && ((reinterpret_cast<uintptr_t>(g.bias) & 15) == 0);
     for (int t = pair; t < num_tiles; t += npairs) {
-      const int mb2 = t % num_m2, nb = t / num_m2;
+      const int mb2 = (t % num_m2 + mb_shift) % num_m2, nb = t / num_m2;
       const int row0 = mb2 * 256 + (int)rank * 128 + lane_grp * 32;
       const int n0 = nb * BN;
       int rows_valid = g.M - row0;
@@ -768,10 +838,10 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs&
   g.num_m_blocks = (g.M + BM - 1) / BM;
   g.num_n_blocks = (g.N + BN - 1) / BN;
   int tiles = g.num_m_blocks * g.num_n_blocks;
-  int ctas = num_sms();
+  int ctas = num_sms() - g.ag_ctas;
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
   if (tiles < ctas) ctas = tiles;
-  kern<<<ctas, GEMM_THREADS, smem_bytes, stream>>>(tmA, tmB, g);
+  kern<<<ctas + g.ag_ctas, GEMM_THREADS, smem_bytes, stream>>>(tmA, tmB, g);
   return (int)cudaGetLastError();
 }
 
@@ -790,12 +860,12 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, Gemm
   g.num_m_blocks = (g.M + 255) / 256;
   g.num_n_blocks = (g.N + 255) / 256;
   int tiles = g.num_m_blocks * g.num_n_blocks;
-  int ctas = num_sms();
+  int ctas = num_sms() - g.ag_ctas;
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
   ctas &= ~1;
   if (2 * tiles < ctas) ctas = 2 * tiles;
   if (ctas < 2) ctas = 2;
-  kern<<<ctas, GEMM_THREADS, smem_bytes, stream>>>(tmA, tmB, g);
+  kern<<<ctas + g.ag_ctas, GEMM_THREADS, smem_bytes, stream>>>(tmA, tmB, g);
   return (int)cudaGetLastError();
 }
 
@@ -804,6 +874,60 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, Gemm
 using namespace nkb;
 
 extern "C" void nkb_gemm_set_pair(int enabled) { nkb::g_pair_enabled = enabled; }
+
+static int gemm_run(GemmArgs g, const void* A, long long lda, int a_mn, const void* B,
+                    long long ldb, int b_mn, int max_ctas, int bn_hint, void* stream) {
+  const int M = g.M, N = g.N, K = g.K;
+  // Tile choice.  bn_hint: 0 = automatic, 128 / 256 = single-CTA tile of that width,
+  // 512 = CTA-pair 256 x 256 tile.
+  int BN = 256;
+  bool pair = false;
+  if (bn_hint == 128 || bn_hint == 256) {
+    BN = bn_hint;
+  } else if (bn_hint == 512) {
+    pair = true;
+  } else {
+    // cost = rounds of the persistent loop x work per round / measured relative
+    // throughput of the tile kind (pair 1.0, single-CTA 128x256 0.88, 128x128 0.68)
+    int sms = num_sms();
+    long long mblk = (M + BM - 1) / BM;
+    long long t256 = mblk * ((N + 255) / 256);
+    long long t128 = mblk * ((N + 127) / 128);
+    double c256 = (double)((t256 + sms - 1) / sms) * 2.0 / 0.88;
+    double c128 = (double)((t128 + sms - 1) / sms) * 1.0 / 0.68;
+    double best = c256;
+    if (N <= 128 || c128 < c256) { BN = 128; best = c128; }
+    long long tp = ((M + 255) / 256) * (long long)((N + 255) / 256);
+    int npair = sms / 2;
+    double cp = (double)((tp + npair - 1) / npair) * 2.0;
+    if (g_pair_enabled && M > 128 && N > 128 && cp <= best) pair = true;
+    if (g.ag_ctas && (g.ag_rows_per_rank % 256)) pair = false;
+  }
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (!a_mn) rc = make_tmap_bf16_2d(&tmA, A, K, M, lda, BK, BM);
+  else rc = make_tmap_bf16_2d(&tmA, A, M, K, lda, 64, BK);
+  if (rc) return rc;
+  if (!b_mn) rc = make_tmap_bf16_2d(&tmB, B, K, N, ldb, BK, pair ? 128 : BN);
+  else rc = make_tmap_bf16_2d(&tmB, B, N, K, ldb, 64, BK);
+  if (rc) return rc;
+
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (pair) {
+    if (!a_mn && !b_mn) return launch_gemm_pair<false, false>(tmA, tmB, g, max_ctas, s);
+    if (!a_mn && b_mn) return launch_gemm_pair<false, true>(tmA, tmB, g, max_ctas, s);
+    if (a_mn && !b_mn) return launch_gemm_pair<true, false>(tmA, tmB, g, max_ctas, s);
+    return launch_gemm_pair<true, true>(tmA, tmB, g, max_ctas, s);
+  }
+#define NKB_DISPATCH(BN_)                                                              \
+  if (!a_mn && !b_mn) return launch_gemm<BN_, false, false>(tmA, tmB, g, max_ctas, s); \
+  if (!a_mn && b_mn) return launch_gemm<BN_, false, true>(tmA, tmB, g, max_ctas, s);   \
+  if (a_mn && !b_mn) return launch_gemm<BN_, true, false>(tmA, tmB, g, max_ctas, s);   \
+  return launch_gemm<BN_, true, true>(tmA, tmB, g, max_ctas, s);
+  if (BN == 256) { NKB_DISPATCH(256) }
+  NKB_DISPATCH(128)
+#undef NKB_DISPATCH
+}
 
 extern "C" int nkb_gemm_bf16(const void* A, long long lda, int a_mn, const void* B, long long ldb,
                              int b_mn, void* C, long long ldc, int c_fp32, int accumulate, int M,
@@ -830,53 +954,53 @@ extern "C" int nkb_gemm_bf16(const void* A, long long lda, int a_mn, const void*
   g.ready_flags = ready_flags;
   g.rows_per_flag = rows_per_flag > 0 ? rows_per_flag : 1;
   g.ready_target = ready_target;
+  g.ag_ctas = 0;
+  return gemm_run(g, A, lda, a_mn, B, ldb, b_mn, max_ctas, bn_hint, stream);
+}
 
-  // Tile choice.  bn_hint: 0 = automatic, 128 / 256 = single-CTA tile of that width,
-  // 512 = CTA-pair 256 x 256 tile.
-  int BN = 256;
-  bool pair = false;
-  if (bn_hint == 128 || bn_hint == 256) {
-    BN = bn_hint;
-  } else if (bn_hint == 512) {
-    pair = true;
-  } else {
-    // cost = rounds of the persistent loop x work per round / measured relative
-    // throughput of the tile kind (pair 1.0, single-CTA 128x256 0.88, 128x128 0.68)
-    int sms = num_sms();
-    long long mblk = (M + BM - 1) / BM;
-    long long t256 = mblk * ((N + 255) / 256);
-    long long t128 = mblk * ((N + 127) / 128);
-    double c256 = (double)((t256 + sms - 1) / sms) * 2.0 / 0.88;
-    double c128 = (double)((t128 + sms - 1) / sms) * 1.0 / 0.68;
-    double best = c256;
-    if (N <= 128 || c128 < c256) { BN = 128; best = c128; }
-    long long tp = ((M + 255) / 256) * (long long)((N + 255) / 256);
-    int npair = sms / 2;
-    double cp = (double)((tp + npair - 1) / npair) * 2.0;
-    if (g_pair_enabled && M > 128 && N > 128 && cp <= best) pair = true;
-  }
-  CUtensorMap tmA, tmB;
-  int rc;
-  if (!a_mn) rc = make_tmap_bf16_2d(&tmA, A, K, M, lda, BK, BM);
-  else rc = make_tmap_bf16_2d(&tmA, A, M, K, lda, 64, BK);
-  if (rc) return rc;
-  if (!b_mn) rc = make_tmap_bf16_2d(&tmB, B, K, N, ldb, BK, pair ? 128 : BN);
-  else rc = make_tmap_bf16_2d(&tmB, B, N, K, ldb, 64, BK);
-  if (rc) return rc;
 
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (pair) {
-    if (!a_mn && !b_mn) return launch_gemm_pair<false, false>(tmA, tmB, g, max_ctas, s);
-    if (!a_mn && b_mn) return launch_gemm_pair<false, true>(tmA, tmB, g, max_ctas, s);
-    if (a_mn && !b_mn) return launch_gemm_pair<true, false>(tmA, tmB, g, max_ctas, s);
-    return launch_gemm_pair<true, true>(tmA, tmB, g, max_ctas, s);
+// A = all-gather over the group of per-rank row shards [rows_per_rank, K] that sit at
+// byte offset data_off (row pitch lda) of every member's heap; C = epi(A_full * B^T).
+// The gather runs inside the GEMM kernel (see GemmArgs::ag_ctas).  ready_flags: local
+// int array with one entry per 128-row block of A_full (zeroed once).
+extern "C" int nkb_ag_gemm_bf16(void** heap, long long flag_off, long long data_off, int rank,
+                                int world, int rows_per_rank, int* epoch, int* ready_flags,
+                                int ag_ctas, long long lda, const void* B, long long ldb,
+                                int b_mn, void* C, long long ldc, int c_fp32, int N, int K,
+                                const void* bias, const void* res, long long ldres, int epi,
+                                void* aux, long long ldaux, const void* A_local, int* status,
+                                int bn_hint, void* stream) {
+  if (world > COMM_MAX_WORLD) return -4;
+  if (rows_per_rank % 128) return -5;
+  if ((lda & 7) || (ldb & 7) || (data_off & 15)) return -3;
+  GemmArgs g;
+  g.M = rows_per_rank * world; g.N = N; g.K = K;
+  g.C = C; g.ldc = ldc; g.c_fp32 = c_fp32; g.accumulate = 0; g.alpha = 1.f; g.alpha_dev = nullptr;
+  g.bias = static_cast<const __nv_bfloat16*>(bias);
+  g.res = static_cast<const __nv_bfloat16*>(res);
+  g.ldres = ldres;
+  g.epi = epi;
+  g.aux_out = (epi == NKB_EPI_GELU_FWD) ? static_cast<__nv_bfloat16*>(aux) : nullptr;
+  g.aux_in = (epi == NKB_EPI_GELU_BWD) ? static_cast<const __nv_bfloat16*>(aux) : nullptr;
+  g.ldaux = ldaux;
+  g.status = status;
+  g.ready_flags = ready_flags;
+  g.rows_per_flag = 128;
+  g.ready_target = 0;
+  if (ag_ctas <= 0) ag_ctas = 8;
+  ag_ctas = (ag_ctas + 1) & ~1;
+  g.ag_ctas = world > 1 ? ag_ctas : 0;
+  g.ag.heap = heap; g.ag.flag_off = flag_off; g.ag.rank = rank; g.ag.world = world;
+  g.ag.epoch = epoch; g.ag.status = status;
+  g.ag_data_off = data_off;
+  g.ag_rows_per_rank = rows_per_rank;
+  g.ag_row_bytes = (long long)K * 2;
+  g.ag_pitch = lda * 2;
+  int rc = gemm_run(g, A_local, lda, 0, B, ldb, b_mn, 0, bn_hint, stream);
+  if (rc) return rc;
+  if (world > 1) {
+    epoch_bump_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(epoch);
+    rc = (int)cudaGetLastError();
   }
-#define NKB_DISPATCH(BN_)                                                              \
-  if (!a_mn && !b_mn) return launch_gemm<BN_, false, false>(tmA, tmB, g, max_ctas, s); \
-  if (!a_mn && b_mn) return launch_gemm<BN_, false, true>(tmA, tmB, g, max_ctas, s);   \
-  if (a_mn && !b_mn) return launch_gemm<BN_, true, false>(tmA, tmB, g, max_ctas, s);   \
-  return launch_gemm<BN_, true, true>(tmA, tmB, g, max_ctas, s);
-  if (BN == 256) { NKB_DISPATCH(256) }
-  NKB_DISPATCH(128)
-#undef NKB_DISPATCH
+  return rc;
 }

@@ -163,6 +163,32 @@ def case_engine_zero_matches_single(rank, world, heap, grp):
     assert _rel(eng.flat.flat[:eng.flat.numel_used], ref.flat.flat[:ref.flat.numel_used]) < 2e-2
 
 
+def case_ag_gemm(rank, world, heap, grp):
+    """all-gather -> GEMM in one kernel vs NCCL all-gather + fp32 matmul."""
+    import torch.distributed as dist
+    for (R, K, N, bn) in [(256, 512, 768, 0), (1024, 1024, 4096, 0), (128, 256, 384, 256),
+                          (512, 1024, 1024, 512)]:
+        x_full = heap.alloc(world * R * K, torch.bfloat16).view(world * R, K)
+        for it in range(3):
+            torch.manual_seed(10 * it + rank)
+            mine = torch.randn(R, K, device="cuda").bfloat16()
+            torch.manual_seed(999)
+            w = (torch.randn(N, K, device="cuda") * 0.05).bfloat16()
+            x_full.zero_()
+            x_full[rank * R:(rank + 1) * R].copy_(mine)
+            gathered = torch.empty(world * R, K, device="cuda", dtype=torch.bfloat16)
+            dist.all_gather_into_tensor(gathered, mine)
+            out = grp.ag_gemm(x_full, w, bn=bn)
+            ref = gathered.float() @ w.float().t()
+            assert _rel(out, ref) < 1e-2, (R, K, N, it)
+            assert torch.equal(x_full, gathered)
+            grp.barrier()
+
+
+def test_ag_gemm():
+    _run("case_ag_gemm")
+
+
 def test_allreduce_allgather():
     _run("case_allreduce_allgather")
 
