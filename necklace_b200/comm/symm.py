@@ -187,6 +187,38 @@ class PeerGroup:
         return out
 
 
+    def gemm_rs(self, x: torch.Tensor, w: torch.Tensor, *, out=None, bias=None, res=None,
+                b_mn=False, rs_ctas: int = 16, bn: int = 0) -> torch.Tensor:
+        """``out[R, N]`` = this rank's row block of ``sum_ranks x_r @ w_r^T`` (+ bias + res):
+        GEMM and reduce-scatter in one kernel.  ``x``: ``[M, K_local]`` with ``M = world*R``;
+        partial tiles are stored directly into the owner's staging slab over NVLink and the
+        owner's reduce CTAs sum them as their flags arrive."""
+        from ..ops._common import ptr
+        M, K = x.shape
+        N = w.shape[1] if b_mn else w.shape[0]
+        R = M // self.world
+        key = (R, N)
+        cache = getattr(self, "_rs_cache", None)
+        if cache is None:
+            cache = self._rs_cache = {}
+        if key not in cache:
+            stage = self.heap.alloc(self.world * R * N, torch.bfloat16)
+            tflags = self.heap.alloc(self.world * (R // 128) * ((N + 127) // 128), torch.int32)
+            tflags.zero_()
+            cache[key] = (stage, tflags)
+        stage, tflags = cache[key]
+        if out is None:
+            out = torch.empty(R, N, dtype=torch.bfloat16, device=x.device)
+        _lib.call("nkb_gemm_rs_bf16", self.ptrs_dev.data_ptr(), self.flag_off,
+                  self.heap.offset_of(stage), self.heap.offset_of(tflags), self.rank, self.world,
+                  R, self.epoch.data_ptr(), int(rs_ctas), x.data_ptr(), x.stride(0), w.data_ptr(),
+                  w.stride(0), int(b_mn), out.data_ptr(), out.stride(0), N, K, ptr(bias), ptr(res),
+                  res.stride(0) if res is not None else 0,
+                  status_word(self.heap.device).data_ptr(), int(bn), _lib.stream_ptr())
+        _lib.count_launch()
+        return out
+
+
 class TorchGroup:
     """Same surface as ``PeerGroup`` on top of ``torch.distributed`` collectives
     (gloo on CPU, NCCL on GPU).  It is the CPU test double and the NCCL baseline."""

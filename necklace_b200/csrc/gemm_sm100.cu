@@ -65,7 +65,100 @@ struct GemmArgs {
   int ag_rows_per_rank;
   long long ag_row_bytes;  // bytes to copy per row (K * 2)
   long long ag_pitch;      // row pitch in bytes
+  // Reduce-scatter fused behind the GEMM (optional, rs_ctas > 0): rows of the result are
+  // owned by ranks in contiguous blocks of rs_rows_per_rank.  Each partial 128-row tile
+  // is stored straight into the owner's staging slab [src rank][rows_per_rank][N] (peer
+  // stores) followed by a per-tile flag; the first rs_ctas CTAs of the owner add the
+  // `world` slabs of a tile as soon as its flags are in, apply bias / residual and write
+  // the final [rows_per_rank, N] block.  Remote owners' tiles are computed first.
+  int rs_ctas;
+  CommCtx rs;
+  long long rs_stage_off;  // byte offset of the staging slabs in every heap
+  long long rs_tflag_off;  // byte offset of the tile flags [src][row block][n block]
+  int rs_rows_per_rank;
+  int rs_bn;               // tile width used by the GEMM CTAs
+  __nv_bfloat16* rs_out;   // [rows_per_rank, N] on this rank
+  long long rs_ldout;
 };
+
+// Reduce role of the fused reduce-scatter (see GemmArgs).
+__device__ __noinline__ static void rs_reduce_role(const GemmArgs& g) {
+  const CommCtx& c = g.rs;
+  const int e = *reinterpret_cast<volatile int*>(c.epoch) + 1;
+  const int R = g.rs_rows_per_rank, BNt = g.rs_bn;
+  const int rb = R / 128, nbk = (g.N + BNt - 1) / BNt;
+  const char* stage = static_cast<const char*>(c.heap[c.rank]) + g.rs_stage_off;
+  const int* tflags = reinterpret_cast<const int*>(static_cast<const char*>(c.heap[c.rank]) +
+                                                   g.rs_tflag_off);
+  __shared__ int sh_ok;
+  bool ok = true;
+  for (int u = blockIdx.x; u < rb * nbk && ok; u += g.rs_ctas) {
+    const int lb = u / nbk, nb = u % nbk;
+    if (threadIdx.x == 0) sh_ok = 1;
+    __syncthreads();
+    if (threadIdx.x < c.world) {
+      if (!wait_flag_ge(tflags + ((long long)threadIdx.x * rb + lb) * nbk + nb, e)) {
+        sh_ok = 0;
+        if (c.status) atomicCAS(c.status, 0, NKB_ERR_FLAG_WAIT);
+      }
+    }
+    __syncthreads();
+    ok = sh_ok != 0;
+    if (!ok) break;
+    const int ncols = min(BNt, g.N - nb * BNt);
+    const int v_per_row = ncols >> 3;  // N % 8 == 0 is required
+    for (int i = threadIdx.x; i < 128 * v_per_row; i += blockDim.x) {
+      const int r = lb * 128 + i / v_per_row, col = nb * BNt + (i % v_per_row) * 8;
+      float acc[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+      for (int src = 0; src < c.world; ++src) {
+        uint4 v = ld_volatile_v4(stage + (((long long)src * R + r) * g.N + col) * 2);
+        uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          float2 f = unpack_bf16x2(w[k]);
+          acc[2 * k] += f.x;
+          acc[2 * k + 1] += f.y;
+        }
+      }
+      if (g.bias) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[k] += __bfloat162float(g.bias[col + k]);
+      }
+      if (g.res) {
+        uint4 v = *reinterpret_cast<const uint4*>(g.res + (long long)r * g.ldres + col);
+        uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          float2 f = unpack_bf16x2(w[k]);
+          acc[2 * k] += f.x;
+          acc[2 * k + 1] += f.y;
+        }
+      }
+      *reinterpret_cast<uint4*>(g.rs_out + (long long)r * g.rs_ldout + col) =
+          make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
+                     pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+    }
+  }
+  // a peer may start refilling this rank's staging only after everyone finished reducing
+  if (ok) cta_barrier(c, 2 * e);
+}
+
+// Staging row pointer and flag of the 128-row block that starts at global row `row_blk0`
+// for n-block nb (fused reduce-scatter): returns the staging address of (row_blk0 +
+// lane_grp*32, n0) in the owner's heap.
+__device__ __forceinline__ __nv_bfloat16* rs_tile_dst(const GemmArgs& g, int row_blk0,
+                                                      int lane_grp, int n0, int** flag, int nb,
+                                                      int nbk) {
+  const int R = g.rs_rows_per_rank;
+  const int q = row_blk0 / R, lb = (row_blk0 - q * R) / 128;
+  char* base = static_cast<char*>(g.rs.heap[q]);
+  *flag = reinterpret_cast<int*>(base + g.rs_tflag_off) +
+          ((long long)g.rs.rank * (R / 128) + lb) * nbk + nb;
+  return reinterpret_cast<__nv_bfloat16*>(base + g.rs_stage_off) +
+         ((long long)g.rs.rank * R + lb * 128 + lane_grp * 32) * g.N + n0;
+}
 
 // Copy role of the fused all-gather (see GemmArgs).  One flag per 128-row block.
 __device__ __noinline__ static void ag_copy_role(const GemmArgs& g) {
@@ -222,7 +315,9 @@ __device__ __forceinline__ void stage_load_f32(uint8_t* stg, int lane, const flo
 template <int BN>
 __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, uint8_t* stg, int lane,
                                               uint32_t t_addr, int row0, int rows_valid, int n0,
-                                              float alpha, bool bias_vec) {
+                                              float alpha, bool bias_vec,
+                                              __nv_bfloat16* rs_dst = nullptr,
+                                              long long rs_ld = 0) {
 #pragma unroll 1
   for (int cc = 0; cc < BN / 64; ++cc) {
     uint32_t r[64];
@@ -235,6 +330,13 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, uint8_t* stg, i
     float v[64];
 #pragma unroll
     for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]) * alpha;
+    if (rs_dst) {
+      // fused reduce-scatter: the raw partial sums go to the owner's staging slab;
+      // bias / residual are applied by the owner after the cross-rank sum
+      stage_put_bf16(stg, lane, v);
+      stage_store_bf16(stg, lane, rs_dst + cc * 64, rs_ld, rows_valid, cols_valid);
+      continue;
+    }
     if (g.bias) {
       if (bias_vec && cols_valid == 64 && (col0 & 7) == 0) {
         const uint4* bp = reinterpret_cast<const uint4*>(g.bias + col0);
@@ -369,11 +471,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     ag_copy_role(g);
     return;
   }
-  const int cta_id = blockIdx.x - g.ag_ctas, n_ctas = gridDim.x - g.ag_ctas;
+  if ((int)blockIdx.x < g.rs_ctas) {
+    rs_reduce_role(g);
+    return;
+  }
+  const int pre = g.ag_ctas + g.rs_ctas;  // at most one of the two is non-zero
+  const int cta_id = blockIdx.x - pre, n_ctas = gridDim.x - pre;
+  const int rs_epoch = g.rs_ctas ? *reinterpret_cast<volatile int*>(g.rs.epoch) + 1 : 0;
   const int ready_target = g.ag_ctas ? *reinterpret_cast<volatile int*>(g.ag.epoch) + 1
                                      : g.ready_target;
   // with a fused all-gather the local shard's row blocks come first
-  const int mb_shift = g.ag_ctas ? g.ag.rank * ((g.ag_rows_per_rank + BM - 1) / BM) : 0;
+  // ... and with a fused reduce-scatter the rows owned by the other ranks
+  const int mb_shift = g.ag_ctas ? g.ag.rank * ((g.ag_rows_per_rank + BM - 1) / BM)
+                     : g.rs_ctas ? ((g.rs.rank + 1) % g.rs.world) * (g.rs_rows_per_rank / BM) : 0;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_tiles = g.num_m_blocks * g.num_n_blocks;
@@ -531,7 +641,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       tc_fence_after();
       const uint32_t t_addr = tmem_base + (uint32_t(lane_grp * 32) << 16) + acc * BN;
-      epilogue_tile<BN>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec);
+      if (g.rs_ctas) {
+        int* tflag;
+        __nv_bfloat16* dst = rs_tile_dst(g, mb * BM, lane_grp, n0, &tflag, nb, g.num_n_blocks);
+        epilogue_tile<BN>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec, dst, g.N);
+        __threadfence_system();
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
+        if (warp == 2 && lane == 0) st_release_sys(tflag, rs_epoch);
+      } else {
+        epilogue_tile<BN>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec);
+      }
       tc_fence_before();
       mbar_arrive(&acc_empty[acc]);
       if (++acc == 2) {
@@ -588,15 +707,22 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
     ag_copy_role(g);
     return;
   }
+  if ((int)blockIdx.x < g.rs_ctas) {
+    rs_reduce_role(g);
+    return;
+  }
+  const int rs_epoch = g.rs_ctas ? *reinterpret_cast<volatile int*>(g.rs.epoch) + 1 : 0;
   const int ready_target = g.ag_ctas ? *reinterpret_cast<volatile int*>(g.ag.epoch) + 1
                                      : g.ready_target;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
-  const int pair = ((int)blockIdx.x - g.ag_ctas) >> 1, npairs = ((int)gridDim.x - g.ag_ctas) >> 1;
+  const int pre = g.ag_ctas + g.rs_ctas;
+  const int pair = ((int)blockIdx.x - pre) >> 1, npairs = ((int)gridDim.x - pre) >> 1;
   const int num_m2 = (g.M + 255) / 256;
-  const int mb_shift = g.ag_ctas ? g.ag.rank * ((g.ag_rows_per_rank + 255) / 256) : 0;
+  const int mb_shift = g.ag_ctas ? g.ag.rank * ((g.ag_rows_per_rank + 255) / 256)
+                     : g.rs_ctas ? ((g.rs.rank + 1) % g.rs.world) * (g.rs_rows_per_rank / 256) : 0;
   const int num_tiles = num_m2 * g.num_n_blocks;
   const int KB = (g.K + BK - 1) / BK;
 
@@ -748,7 +874,17 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       }
       tc_fence_after();
       const uint32_t t_addr = tmem_base + (uint32_t(lane_grp * 32) << 16) + acc * BN;
-      epilogue_tile<BN>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec);
+      if (g.rs_ctas) {
+        int* tflag;
+        __nv_bfloat16* dst = rs_tile_dst(g, mb2 * 256 + (int)rank * 128, lane_grp, n0, &tflag, nb,
+                                         g.num_n_blocks);
+        epilogue_tile<BN>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec, dst, g.N);
+        __threadfence_system();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (warp == 2 && lane == 0) st_release_sys(tflag, rs_epoch);
+      } else {
+        epilogue_tile<BN>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec);
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {
@@ -838,10 +974,11 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs&
   g.num_m_blocks = (g.M + BM - 1) / BM;
   g.num_n_blocks = (g.N + BN - 1) / BN;
   int tiles = g.num_m_blocks * g.num_n_blocks;
-  int ctas = num_sms() - g.ag_ctas;
+  int ctas = num_sms() - g.ag_ctas - g.rs_ctas;
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
   if (tiles < ctas) ctas = tiles;
-  kern<<<ctas + g.ag_ctas, GEMM_THREADS, smem_bytes, stream>>>(tmA, tmB, g);
+  g.rs_bn = BN;
+  kern<<<ctas + g.ag_ctas + g.rs_ctas, GEMM_THREADS, smem_bytes, stream>>>(tmA, tmB, g);
   return (int)cudaGetLastError();
 }
 
@@ -860,12 +997,13 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, Gemm
   g.num_m_blocks = (g.M + 255) / 256;
   g.num_n_blocks = (g.N + 255) / 256;
   int tiles = g.num_m_blocks * g.num_n_blocks;
-  int ctas = num_sms() - g.ag_ctas;
+  int ctas = num_sms() - g.ag_ctas - g.rs_ctas;
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
   ctas &= ~1;
   if (2 * tiles < ctas) ctas = 2 * tiles;
   if (ctas < 2) ctas = 2;
-  kern<<<ctas + g.ag_ctas, GEMM_THREADS, smem_bytes, stream>>>(tmA, tmB, g);
+  g.rs_bn = 256;
+  kern<<<ctas + g.ag_ctas + g.rs_ctas, GEMM_THREADS, smem_bytes, stream>>>(tmA, tmB, g);
   return (int)cudaGetLastError();
 }
 
@@ -955,6 +1093,7 @@ extern "C" int nkb_gemm_bf16(const void* A, long long lda, int a_mn, const void*
   g.rows_per_flag = rows_per_flag > 0 ? rows_per_flag : 1;
   g.ready_target = ready_target;
   g.ag_ctas = 0;
+  g.rs_ctas = 0;
   return gemm_run(g, A, lda, a_mn, B, ldb, b_mn, max_ctas, bn_hint, stream);
 }
 
@@ -990,6 +1129,7 @@ extern "C" int nkb_ag_gemm_bf16(void** heap, long long flag_off, long long data_
   if (ag_ctas <= 0) ag_ctas = 8;
   ag_ctas = (ag_ctas + 1) & ~1;
   g.ag_ctas = world > 1 ? ag_ctas : 0;
+  g.rs_ctas = 0;
   g.ag.heap = heap; g.ag.flag_off = flag_off; g.ag.rank = rank; g.ag.world = world;
   g.ag.epoch = epoch; g.ag.status = status;
   g.ag_data_off = data_off;
@@ -1003,4 +1143,46 @@ extern "C" int nkb_ag_gemm_bf16(void** heap, long long flag_off, long long data_
     rc = (int)cudaGetLastError();
   }
   return rc;
+}
+
+// out[rows_per_rank, N] on every rank = rows [rank*rows_per_rank, ...) of
+// sum over ranks of A_r[M, K_r] * B_r[N, K_r]^T (+ bias + res): GEMM and reduce-scatter in
+// one kernel (see GemmArgs::rs_ctas).  stage_off: bf16 [world][rows_per_rank][N] in every
+// heap; tflag_off: int [world][rows_per_rank/128][ceil(N/128)] in every heap (zeroed once).
+extern "C" int nkb_gemm_rs_bf16(void** heap, long long flag_off, long long stage_off,
+                                long long tflag_off, int rank, int world, int rows_per_rank,
+                                int* epoch, int rs_ctas, const void* A, long long lda,
+                                const void* B, long long ldb, int b_mn, void* out,
+                                long long ldout, int N, int K, const void* bias, const void* res,
+                                long long ldres, int* status, int bn_hint, void* stream) {
+  if (world > COMM_MAX_WORLD) return -4;
+  if ((rows_per_rank % 128) || (N % 8)) return -5;
+  if ((lda & 7) || (ldb & 7) || (stage_off & 15) || (tflag_off & 3)) return -3;
+  GemmArgs g;
+  g.M = rows_per_rank * world; g.N = N; g.K = K;
+  g.C = nullptr; g.ldc = 0; g.c_fp32 = 0; g.accumulate = 0; g.alpha = 1.f; g.alpha_dev = nullptr;
+  g.bias = static_cast<const __nv_bfloat16*>(bias);
+  g.res = static_cast<const __nv_bfloat16*>(res);
+  g.ldres = ldres;
+  g.epi = NKB_EPI_NONE;
+  g.aux_out = nullptr; g.aux_in = nullptr; g.ldaux = 0;
+  g.status = status;
+  g.ready_flags = nullptr; g.rows_per_flag = 1; g.ready_target = 0;
+  g.ag_ctas = 0;
+  if (rs_ctas <= 0) rs_ctas = 16;
+  rs_ctas = (rs_ctas + 1) & ~1;
+  g.rs_ctas = rs_ctas;
+  g.rs.heap = heap; g.rs.flag_off = flag_off; g.rs.rank = rank; g.rs.world = world;
+  g.rs.epoch = epoch; g.rs.status = status;
+  g.rs_stage_off = stage_off; g.rs_tflag_off = tflag_off;
+  g.rs_rows_per_rank = rows_per_rank;
+  g.rs_out = static_cast<__nv_bfloat16*>(out);
+  g.rs_ldout = ldout;
+  // the tile-flag layout depends on the tile width: fix it (pair tiles when shards are
+  // multiples of 256 rows, else single-CTA 128 x 256)
+  if (bn_hint == 0) bn_hint = (rows_per_rank % 256 == 0 && g_pair_enabled) ? 512 : 256;
+  int rc = gemm_run(g, A, lda, 0, B, ldb, b_mn, 0, bn_hint, stream);
+  if (rc) return rc;
+  epoch_bump_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(epoch);
+  return (int)cudaGetLastError();
 }

@@ -185,6 +185,32 @@ def case_ag_gemm(rank, world, heap, grp):
             grp.barrier()
 
 
+def case_gemm_rs(rank, world, heap, grp):
+    """GEMM -> reduce-scatter in one kernel vs fp32 matmul + NCCL reduce_scatter."""
+    import torch.distributed as dist
+    for (R, K, N, bn) in [(128, 256, 256, 256), (256, 512, 768, 0), (512, 1024, 4096, 0),
+                          (384, 320, 520, 256)]:
+        M = R * world
+        for it in range(3):
+            torch.manual_seed(10 * it + rank)
+            x = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+            w = (torch.randn(N, K, device="cuda") * 0.1).bfloat16()
+            torch.manual_seed(5)
+            bias = torch.randn(N, device="cuda").bfloat16()
+            res = torch.randn(R, N, device="cuda").bfloat16()
+            part = x.float() @ w.float().t()
+            ref = torch.empty(R, N, device="cuda")
+            dist.reduce_scatter_tensor(ref, part)
+            ref = ref + bias.float() + res.float()
+            out = grp.gemm_rs(x, w, bias=bias, res=res, bn=bn)
+            assert _rel(out, ref) < 1.5e-2, (R, K, N, it, _rel(out, ref))
+            grp.barrier()
+
+
+def test_gemm_rs():
+    _run("case_gemm_rs")
+
+
 def test_ag_gemm():
     _run("case_ag_gemm")
 
