@@ -1,0 +1,140 @@
+"""Checkpoint / resume.
+
+The reference only has helpers (``torch.save(state, 'checkpoint.pth.tar')`` plus a best
+copy, ``module.``-prefix stripping, whole-model assembly for ZeRO / pipeline parts;
+necklace/frmwrk/pytorch/callback.py:16-19, ptutils.py:21-35, mdwrp.py:148-155) and no resume
+logic.  Here a checkpoint is one ``torch.save`` file holding
+
+    {"state_dict": un-sharded parameter tensors by their ordinary names (fp32 master values),
+     "optim": {"kind", "step", "s1", "s2"  (flat fp32, un-sharded)},
+     "meta": {"epoch", "step", "rng", "layout"}}
+
+so it loads into a plain ``nn.Module`` with ``load_state_dict`` and re-shards onto any
+number of ZeRO ranks.  Tensor-parallel parameters (``model_parallel`` attribute with a
+``partition_dim``) are concatenated on save and re-split on load; pipeline / ZeRO parts are
+assembled under the reference's ``whole_md.<i>...`` keys.
+"""
+from __future__ import annotations
+
+import os
+import shutil
+from collections import OrderedDict
+
+import torch
+import torch.distributed as dist
+
+
+# ----------------------------------------------------------------------- engine (dp / zero)
+def _gather_flat(t: torch.Tensor, sharded: bool, world: int, group=None) -> torch.Tensor:
+    if not sharded or world == 1:
+        return t.detach().float().cpu()
+    parts = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(parts, t.contiguous(), group=group)
+    return torch.cat(parts).float().cpu()
+
+
+def engine_state(engine, epoch: int = 0, extra: dict | None = None) -> dict:
+    """Consolidated state of a ``TrainEngine`` (collective when the engine is sharded)."""
+    f = engine.flat
+    pg = getattr(getattr(engine.group, "heap", None), "group", None) if engine.sharded else None
+    master = _gather_flat(engine.master, engine.sharded, engine.world, pg)
+    sd = OrderedDict()
+    for name, p, off in zip(f.names, f.params, f.offsets):
+        sd[name] = master[off:off + p.numel()].view(p.shape).clone()
+    optim = {"kind": engine.optim.kind, "step": engine.step_count}
+    for key in ("s1", "s2"):
+        t = getattr(engine, key)
+        optim[key] = None if t is None else _gather_flat(t, engine.sharded, engine.world, pg)
+    meta = {"epoch": epoch, "step": engine.step_count, "rng": torch.get_rng_state(),
+            "layout": {"names": f.names, "offsets": f.offsets, "numel": f.numel,
+                       "world": engine.world, "mode": engine.mode}}
+    if extra:
+        meta.update(extra)
+    return {"state_dict": sd, "optim": optim, "meta": meta}
+
+
+def load_engine_state(engine, state: dict) -> dict:
+    """Load a consolidated state into an engine of any world size (re-shards)."""
+    f = engine.flat
+    full = torch.zeros(f.numel, dtype=torch.float32)
+    for name, p, off in zip(f.names, f.params, f.offsets):
+        full[off:off + p.numel()] = state["state_dict"][name].reshape(-1).float()
+    n = engine.master.numel()
+    lo = engine.rank * n if engine.sharded else 0
+    dev = engine.master.device
+    engine.master.copy_(full[lo:lo + n].to(dev))
+    f.flat.copy_(full.to(dev).to(f.flat.dtype))
+    old = state["meta"]["layout"]
+    for key in ("s1", "s2"):
+        src, dst = state["optim"].get(key), getattr(engine, key)
+        if src is None or dst is None:
+            continue
+        buf = torch.zeros(f.numel, dtype=torch.float32)
+        if old["names"] == f.names and old["offsets"] == f.offsets:
+            buf[:min(f.numel, src.numel())] = src[:min(f.numel, src.numel())]
+        else:  # different padding / order: move slice by slice
+            o_off = dict(zip(old["names"], old["offsets"]))
+            for name, p, off in zip(f.names, f.params, f.offsets):
+                buf[off:off + p.numel()] = src[o_off[name]:o_off[name] + p.numel()]
+        dst.copy_(buf[lo:lo + n].to(dev))
+    engine.step_count = int(state["optim"].get("step", 0))
+    if state["meta"].get("rng") is not None:
+        torch.set_rng_state(state["meta"]["rng"])
+    return state["meta"]
+
+
+def save(state: dict, filename: str = "checkpoint.pth.tar", is_best: bool = False,
+         best: str = "model_best.pth.tar", rank: int = 0) -> None:
+    """Written by one rank, atomically (temp file + rename)."""
+    if rank != 0:
+        return
+    tmp = filename + ".tmp"
+    torch.save(state, tmp)
+    os.replace(tmp, filename)
+    if is_best:
+        shutil.copyfile(filename, best)
+
+
+def load(filename: str) -> dict:
+    return torch.load(filename, map_location="cpu", weights_only=False)
+
+
+# ------------------------------------------------------------------ tensor-parallel modules
+def gather_tp_state_dict(module: torch.nn.Module, mp_group=None) -> OrderedDict:
+    """Un-sharded state dict of a tensor-parallel module (collective over the mp group)."""
+    from .comm import fns
+    ws = mp_group.world_size if mp_group is not None else 1
+    out = OrderedDict()
+    for name, p in module.named_parameters():
+        t = p.detach()
+        if ws > 1 and getattr(p, "model_parallel", False):
+            dim = getattr(p, "partition_dim", 0)
+            buf = torch.empty((ws,) + tuple(t.shape), dtype=t.dtype, device=t.device)
+            fns.all_gather(buf, t.contiguous(), group=mp_group)
+            t = torch.cat(list(buf.unbind(0)), dim=dim)
+        out[name] = t.float().cpu()
+    for name, b in module.named_buffers():
+        out[name] = b.detach().cpu()
+    return out
+
+
+def load_tp_state_dict(module: torch.nn.Module, full: dict, mp_group=None) -> None:
+    ws = mp_group.world_size if mp_group is not None else 1
+    rank = mp_group.rank if mp_group is not None else 0
+    with torch.no_grad():
+        for name, p in module.named_parameters():
+            t = full[name]
+            if ws > 1 and getattr(p, "model_parallel", False):
+                t = t.chunk(ws, dim=getattr(p, "partition_dim", 0))[rank]
+            p.copy_(t.to(p.dtype).to(p.device))
+
+
+# ---------------------------------------------------------------- pipeline / ZeRO parts
+def whole_state_dict(parts) -> OrderedDict:
+    """State dict of all parts under the reference's ``whole_md.<i>.`` keys."""
+    from .frmwrk.pytorch.mdwrp import MdWrpWholeNet
+    return MdWrpWholeNet(list(parts)).state_dict()
+
+
+def strip_module_prefix(sd: dict) -> OrderedDict:
+    return OrderedDict((k[7:] if k.startswith("module.") else k, v) for k, v in sd.items())

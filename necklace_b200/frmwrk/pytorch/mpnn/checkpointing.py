@@ -204,9 +204,6 @@ class CheckpointFunction(torch.autograd.Function):
                 torch.cuda.current_stream().wait_stream(side)
             else:
                 inputs = get_full_inputs(inputs, ctx.shapes)
-        for t, req in zip(inputs, ctx.requires):
-            if isinstance(t, torch.Tensor):
-                t.requires_grad = False
         bwd_cpu_rng, bwd_dev_rng = torch.get_rng_state(), _get_rng_state()
         bwd_tracker = get_cuda_rng_tracker().get_states()
         torch.set_rng_state(ctx.fwd_cpu_rng)

@@ -1,0 +1,175 @@
+"""Checkpoint round trips (incl. re-sharding over gloo ranks), data loaders, samplers,
+flat-memory manager, activation checkpointing, hooks (CPU)."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.nn as nn
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _tiny():
+    from necklace_b200.models.gpt2 import GPT2, GPT2Config
+    torch.manual_seed(0)
+    return GPT2(GPT2Config(n_layer=1, d_model=32, n_head=2, d_ff=64, vocab=50, max_seq=16,
+                           dtype=torch.float32))
+
+
+def test_engine_checkpoint_resume_is_bit_identical(tmp_path):
+    from necklace_b200 import checkpoint as ck
+    from necklace_b200.parallel.engine import OptimConfig, TrainEngine
+    tok = torch.randint(0, 50, (4, 17), generator=torch.Generator().manual_seed(1))
+    x, y = tok[:, :-1], tok[:, 1:]
+    a = TrainEngine(_tiny(), optim=OptimConfig("adam", lr=1e-2))
+    for _ in range(3):
+        a.step(x, y)
+    ck.save(ck.engine_state(a, epoch=2), str(tmp_path / "c.pt"))
+    la = [float(a.step(x, y)) for _ in range(2)]
+    b = TrainEngine(_tiny(), optim=OptimConfig("adam", lr=1e-2))
+    meta = ck.load_engine_state(b, ck.load(str(tmp_path / "c.pt")))
+    assert meta["epoch"] == 2 and b.step_count == 3
+    lb = [float(b.step(x, y)) for _ in range(2)]
+    assert la == lb
+    # the state dict loads into a plain module
+    plain = _tiny()
+    plain.load_state_dict(ck.load(str(tmp_path / "c.pt"))["state_dict"], strict=False)
+
+
+def _reshard_worker(rank, world, port, path, q):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from necklace_b200 import checkpoint as ck
+    from necklace_b200.comm.symm import TorchGroup
+    from necklace_b200.parallel.engine import OptimConfig, TrainEngine
+    eng = TrainEngine(_tiny(), mode="zero", group=TorchGroup(), optim=OptimConfig("adam", lr=1e-2))
+    ck.load_engine_state(eng, ck.load(path))
+    tok = torch.randint(0, 50, (4, 17), generator=torch.Generator().manual_seed(1))
+    mine = tok[rank * 2:(rank + 1) * 2]
+    eng.step(mine[:, :-1], mine[:, 1:])
+    st = ck.engine_state(eng)
+    if rank == 0:
+        q.put({k: v.clone() for k, v in st["state_dict"].items()})
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_checkpoint_reshards_from_1_to_2_zero_ranks(tmp_path):
+    import torch.multiprocessing as mp
+    from necklace_b200 import checkpoint as ck
+    from necklace_b200.parallel.engine import OptimConfig, TrainEngine
+    tok = torch.randint(0, 50, (4, 17), generator=torch.Generator().manual_seed(1))
+    a = TrainEngine(_tiny(), optim=OptimConfig("adam", lr=1e-2))
+    a.step(tok[:, :-1], tok[:, 1:])
+    path = str(tmp_path / "c.pt")
+    ck.save(ck.engine_state(a), path)
+    a.step(tok[:, :-1], tok[:, 1:])  # single-process continuation on the global batch
+    ref = ck.engine_state(a)["state_dict"]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    ps = [ctx.Process(target=_reshard_worker, args=(r, 2, port, path, q)) for r in range(2)]
+    for p in ps:
+        p.start()
+    got = q.get(timeout=120)
+    for p in ps:
+        p.join(timeout=60)
+    for k in ref:
+        assert torch.allclose(got[k], ref[k], atol=1e-5), k
+
+
+def test_samplers_and_slices():
+    from necklace_b200.data.sampler import (BatchSampler, SequentialSampler, SliceBatchSampler,
+                                            SliceSampler)
+    assert list(BatchSampler(SequentialSampler(7), 3, "keep")) == [[0, 1, 2], [3, 4, 5], [6]]
+    assert list(BatchSampler(SequentialSampler(7), 3, "discard")) == [[0, 1, 2], [3, 4, 5]]
+    bs = BatchSampler(SequentialSampler(7), 3, "rollover")
+    assert list(bs) == [[0, 1, 2], [3, 4, 5]] and list(bs)[0] == [6, 0, 1]
+    s = SliceSampler(10)
+    assert list(s[2:5]) == [2, 3, 4] and len(s[5:]) == 5
+    s2 = SliceSampler(100, shuffle=True, seed=3)
+    assert sorted(s2) == list(range(100)) and list(s2) != list(range(100))
+    sb = SliceBatchSampler(SliceSampler(12), 4, "keep")
+    assert list(sb[1:]) == [[4, 5, 6, 7], [8, 9, 10, 11]]
+
+
+@pytest.mark.timeout(180)
+@pytest.mark.parametrize("kind", ["queue", "ring"])
+def test_multiprocess_loaders_deliver_every_batch_in_order(kind):
+    from necklace_b200.data.dtset import SyntheticDataset
+    from necklace_b200.data.loaders import QueueDataLoader, ShmRingDataLoader
+    ds = SyntheticDataset(50, (3, 4), classes=5, seed=2)
+    cls = QueueDataLoader if kind == "queue" else ShmRingDataLoader
+    dl = cls(ds, batch_size=8, num_workers=2, part_num=2, last_batch="keep")
+    try:
+        for _ in range(2):  # two epochs on the same workers
+            got = list(dl)
+            assert len(got) == 7 and sum(b[0].shape[0] for b in got) == 50
+            x0 = torch.stack([ds[i][0] for i in range(8)])
+            assert torch.equal(got[0][0], x0)
+            x5 = torch.stack([ds[i][0] for i in range(40, 48)])
+            assert torch.equal(got[5][0], x5)
+            assert got[6][0].shape[0] == 2
+    finally:
+        dl.clear()
+
+
+def test_flat_memory_manager_roundtrip():
+    from necklace_b200.frmwrk.pytorch.tsmem import PtCudaFltnMemManager
+    a, b = nn.Linear(4, 3), nn.Linear(3, 5)
+    wa = a.weight.detach().clone()
+    mm = PtCudaFltnMemManager(32, 32, "cpu")
+    mm.register(a)
+    mm.register(b)
+    mm.md_to_gpu(a)
+    assert torch.equal(a.weight, wa) and a.weight.data_ptr() == mm.gpu_weig.data_ptr()
+    a(torch.randn(2, 4)).sum().backward()
+    ga = a.weight.grad.clone()
+    assert ga.abs().sum() > 0
+    mm.md_to_gpu(b)          # implicitly parks `a`, keeping its gradients
+    mm.md_to_cpu(b)
+    mm.md_to_gpu(a)
+    assert torch.equal(a.weight.grad, ga) and torch.equal(a.weight, wa)
+
+
+def test_activation_checkpoint_matches_plain_backward():
+    from necklace_b200.frmwrk.pytorch.mpnn.checkpointing import (checkpoint,
+                                                                 model_parallel_cuda_manual_seed)
+    model_parallel_cuda_manual_seed(123)
+    net = nn.Sequential(nn.Linear(8, 16), nn.Dropout(0.5), nn.Tanh(), nn.Linear(16, 4))
+    x = torch.randn(5, 8, requires_grad=True)
+    st = torch.get_rng_state()
+    y = checkpoint(net, x)
+    y.pow(2).sum().backward()
+    g1, gw1 = x.grad.clone(), net[0].weight.grad.clone()
+    x.grad = None
+    net.zero_grad()
+    torch.set_rng_state(st)
+    net(x).pow(2).sum().backward()
+    assert torch.allclose(g1, x.grad, atol=1e-6) and torch.allclose(gw1, net[0].weight.grad, atol=1e-6)
+
+
+def test_hook_order_and_return_override():
+    from necklace_b200.trainer.tnopbs import ModelWrapperHooks
+    calls = []
+
+    class T(ModelWrapperHooks):
+        def _one_step(self, rank=0):
+            calls.append("step")
+            return "one_step"
+
+    t = T({})
+    t.register_hook_before_batch(lambda trnr: calls.append("b1"))
+    t.register_hook_before_batch(lambda trnr: calls.append("b2"))
+    t.register_hook_after_batch(lambda trnr, r: calls.append(("a1", r)))
+    assert t.one_step() == "one_step" and calls == ["b1", "b2", "step", ("a1", "one_step")]
+    t.register_hook_after_batch(lambda trnr, r: "overridden")
+    assert t.one_step() == "overridden"
+    for ev in ("train", "epoch", "data_batch", "batch", "do_a_batch_grads", "do_a_train_step"):
+        assert hasattr(t, f"register_hook_before_{ev}") and hasattr(t, f"register_hook_after_{ev}")

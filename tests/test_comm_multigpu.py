@@ -207,6 +207,40 @@ def case_gemm_rs(rank, world, heap, grp):
             grp.barrier()
 
 
+def case_sp_tp_mlp(rank, world, heap, grp):
+    """Sequence-parallel tensor-parallel MLP (fused AG->GEMM, GEMM->RS, both directions)
+    against the unsharded fp32 computation."""
+    import torch.distributed as dist
+    import torch.nn.functional as F
+    from necklace_b200.parallel.tensor import SPColumnParallelLinear, SPRowParallelLinear
+    C, Fh, R = 256, 1024, 256
+    M = R * world
+    up = SPColumnParallelLinear(C, Fh, grp, device="cuda", seed=11, std=0.05)
+    down = SPRowParallelLinear(Fh, C, grp, device="cuda", seed=12, std=0.05)
+    torch.manual_seed(3)
+    x_full = torch.randn(M, C, device="cuda").bfloat16()
+    dy_full = torch.randn(M, C, device="cuda").bfloat16()
+    xs = x_full[rank * R:(rank + 1) * R].clone().requires_grad_(True)
+    y = down(F.gelu(up(xs), approximate="tanh"), residual=xs)
+    y.backward(dy_full[rank * R:(rank + 1) * R])
+    # reference with the full weights
+    g1, g2 = torch.Generator().manual_seed(11), torch.Generator().manual_seed(12)
+    w1 = (torch.randn(Fh, C, generator=g1) * 0.05).bfloat16().float().cuda().requires_grad_(True)
+    w2 = (torch.randn(C, Fh, generator=g2) * 0.05).bfloat16().float().cuda().requires_grad_(True)
+    xr = x_full.float().requires_grad_(True)
+    yr = F.linear(F.gelu(F.linear(xr, w1), approximate="tanh"), w2) + xr
+    yr.backward(dy_full.float())
+    sl = slice(rank * R, (rank + 1) * R)
+    assert _rel(y, yr[sl]) < 2e-2
+    assert _rel(xs.grad, xr.grad[sl]) < 3e-2
+    assert _rel(up.weight.grad, w1.grad.chunk(world, 0)[rank]) < 3e-2
+    assert _rel(down.weight.grad, w2.grad.chunk(world, 1)[rank]) < 3e-2
+
+
+def test_sp_tp_mlp():
+    _run("case_sp_tp_mlp")
+
+
 def test_gemm_rs():
     _run("case_gemm_rs")
 
