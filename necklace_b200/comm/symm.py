@@ -204,7 +204,9 @@ class PeerGroup:
         if key not in cache:
             stage = self.heap.alloc(self.world * R * N, torch.bfloat16)
             tflags = self.heap.alloc(self.world * (R // 128) * ((N + 127) // 128), torch.int32)
-            tflags.zero_()
+            # No zeroing here: the heap is zero-filled before it is mapped and the bump
+            # allocator never hands a range out twice.  Zeroing now would race with a
+            # faster peer whose kernel is already raising flags in this rank's array.
             cache[key] = (stage, tflags)
         stage, tflags = cache[key]
         if out is None:

@@ -46,14 +46,21 @@ __device__ __forceinline__ uint32_t sw128_off(int r, int chunk) {
   return uint32_t(r) * 128u + (uint32_t(chunk ^ (r & 7)) << 4);
 }
 
-template <int D>
+// EXPM selects how probabilities are computed: 0 = fp32 exp2 (one MUFU op per element,
+// row sums in registers), 1 = packed half exp2 (two per MUFU op) converted to bf16,
+// 2 = packed bf16 exp2.  In modes 1 and 2 the row sums come from an extra MMA of P
+// against a tile of ones (16 accumulator columns, one used).  The kernel is bound by the
+// exponential unit (128 x 128 exps per key block vs 512 tensor-core cycles), which is
+// why halving the MUFU work matters.
+template <int D, int EXPM>
 __global__ void __launch_bounds__(ATT_THREADS, (D == 64 ? 2 : 1))
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const AttnFwdArgs a) {
   constexpr int TILE = 128 * D * 2;          // bytes of a 128 x D bf16 tile
   constexpr int NKD = D / 64;                // 64-wide sub-tiles along the head dim
-  constexpr uint32_t TMEM_COLS = 256;
+  constexpr uint32_t TMEM_COLS = (D == 64) ? 256 : 512;
   constexpr uint32_t O_COL = 128;
+  constexpr uint32_t L_COL = 128 + D;  // row sums (modes 1, 2)
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                               ~uintptr_t(1023));
@@ -61,7 +68,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint8_t* sK = sQ + TILE;       // two stages
   uint8_t* sV = sK + 2 * TILE;   // one stage
   uint8_t* sP = sV + TILE;       // 128 x 128 bf16
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 32768);
+  uint8_t* sOnes = sP + 32768;   // 16 x 128 bf16 ones (K-major B operand of the row-sum MMA)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sOnes + 4096);
   uint64_t* q_full = bars + 0;
   uint64_t* k_full = bars + 1;  // [2]
   uint64_t* v_full = bars + 3;
@@ -90,6 +98,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     *abort_flag = 0;
     mbar_fence_init();
   }
+  if (EXPM != 0) {
+    for (int i = threadIdx.x; i < 4096 / 4; i += ATT_THREADS)
+      reinterpret_cast<uint32_t*>(sOnes)[i] = 0x3F803F80u;  // bf16 1.0 pairs
+    fence_proxy_async_smem();
+  }
   if (warp == 4) {
     tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
@@ -103,6 +116,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (lane == 0) {
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);
       constexpr uint32_t idesc_o = umma_idesc_bf16(128, D, 0, 1);
+      constexpr uint32_t idesc_l = umma_idesc_bf16(128, 16, 0, 0);
       auto load_tile = [&](uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, int row0) {
         mbar_expect_tx(bar, TILE);
 #pragma unroll
@@ -144,6 +158,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             umma_bf16_ss(tmem_base + O_COL,
                          umma_desc_sw128(ap + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024),
                          umma_desc_sw128(av + k * 2048, 16384, 1024), idesc_o, k > 0 ? 1u : 0u);
+          if (EXPM != 0) {
+            const uint32_t ao = smem_u32(sOnes);
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+              umma_bf16_ss(tmem_base + L_COL,
+                           umma_desc_sw128(ap + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024),
+                           umma_desc_sw128(ao + (k >> 2) * 2048 + (k & 3) * 32, 16, 1024),
+                           idesc_l, k > 0 ? 1u : 0u);
+          }
           umma_commit(o_full);
         }
         if (j + 1 < nkv) {
@@ -217,6 +240,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
           for (int i = 0; i < 32; ++i) O[c * 32 + i] = (O[c * 32 + i] + __uint_as_float(pv[i])) * alpha;
         }
+        if (EXPM != 0) {
+          const float rs = __uint_as_float(tmem_ld_32x1(t_lane + L_COL));
+          tmem_ld_wait();
+          l = (l + rs) * alpha;
+        }
       }
       // pass 2: probabilities -> shared memory (swizzled K-major A operand)
       float rowsum = 0.f;
@@ -229,16 +257,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float x0 = __uint_as_float(s[i]), x1 = __uint_as_float(s[i + 1]);
-          float p0 = exp2f(fmaf(x0, a.scale_log2, mneg));
-          float p1 = exp2f(fmaf(x1, a.scale_log2, mneg));
+          float x0 = fmaf(__uint_as_float(s[i]), a.scale_log2, mneg);
+          float x1 = fmaf(__uint_as_float(s[i + 1]), a.scale_log2, mneg);
           if (need_mask) {
             const int kv = kv0 + c * 32 + i;
-            if (kv >= a.S || (a.causal && kv > qi)) p0 = 0.f;
-            if (kv + 1 >= a.S || (a.causal && kv + 1 > qi)) p1 = 0.f;
+            if (kv >= a.S || (a.causal && kv > qi)) x0 = -INFINITY;
+            if (kv + 1 >= a.S || (a.causal && kv + 1 > qi)) x1 = -INFINITY;
           }
-          rowsum += p0 + p1;
-          pk[i >> 1] = pack_bf16x2(p0, p1);
+          if (EXPM == 0) {
+            const float p0 = exp2f(x0), p1 = exp2f(x1);
+            rowsum += p0 + p1;
+            pk[i >> 1] = pack_bf16x2(p0, p1);
+          } else if (EXPM == 1) {
+            pk[i >> 1] = f16x2_to_bf16x2(ex2_f16x2(x0, x1));
+          } else {
+            pk[i >> 1] = ex2_bf16x2(x0, x1);
+          }
         }
         uint8_t* base = sP + (c >> 1) * 16384;
 #pragma unroll
@@ -246,7 +280,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           *reinterpret_cast<uint4*>(base + sw128_off(r, (c & 1) * 4 + q)) =
               make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
       }
-      l = l * alpha + rowsum;
+      if (EXPM == 0) l = l * alpha + rowsum;
       m = m_new;
       fence_proxy_async_smem();
       tc_fence_before();
@@ -254,6 +288,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
     if (ok && mbar_wait(o_full, (nkv - 1) & 1, abort_flag)) {
       tc_fence_after();
+      if (EXPM != 0) {
+        l += __uint_as_float(tmem_ld_32x1(t_lane + L_COL));
+        tmem_ld_wait();
+      }
       const float inv = 1.f / l;
       __nv_bfloat16* orow = a.o + (long long)b * a.ob + (long long)h * a.oh + (long long)qi * a.os;
 #pragma unroll
@@ -657,20 +695,30 @@ static int make_tmap_bshd(CUtensorMap* out, const void* base, int B, int H, int 
   return r == CUDA_SUCCESS ? 0 : -(int)r - 1000;
 }
 
-template <int D>
+static int g_attn_exp_mode = 1;
+
+template <int D, int EXPM>
 static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                       const AttnFwdArgs& a, cudaStream_t s) {
-  constexpr int smem = 4 * (128 * D * 2) + 32768 + 1024 + 128;
+  constexpr int smem = 4 * (128 * D * 2) + 32768 + 4096 + 1024 + 128;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel<D>,
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel<D, EXPM>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   dim3 grid(a.B * a.H, (a.S + 127) / 128);
-  attn_fwd_kernel<D><<<grid, ATT_THREADS, smem, s>>>(tq, tk, tv, a);
+  attn_fwd_kernel<D, EXPM><<<grid, ATT_THREADS, smem, s>>>(tq, tk, tv, a);
   return (int)cudaGetLastError();
+}
+
+template <int D>
+static int launch_fwd_mode(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                           const AttnFwdArgs& a, cudaStream_t s) {
+  if (g_attn_exp_mode == 0) return launch_fwd<D, 0>(tq, tk, tv, a, s);
+  if (g_attn_exp_mode == 2) return launch_fwd<D, 2>(tq, tk, tv, a, s);
+  return launch_fwd<D, 1>(tq, tk, tv, a, s);
 }
 
 template <int D>
@@ -694,6 +742,9 @@ static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
 
 using namespace nkb;
 
+// 0 = fp32 exponentials, 1 = packed half (default), 2 = packed bf16
+extern "C" void nkb_attn_set_exp_mode(int mode) { nkb::g_attn_exp_mode = mode; }
+
 extern "C" int nkb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
                             int B, int H, int S, int D, long long sb, long long sh, long long ss,
                             long long ob, long long oh, long long os, float scale, int causal,
@@ -715,7 +766,7 @@ extern "C" int nkb_attn_fwd(const void* q, const void* k, const void* v, void* o
   a.causal = causal;
   a.status = status;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  return D == 64 ? launch_fwd<64>(tq, tk, tv, a, s) : launch_fwd<128>(tq, tk, tv, a, s);
+  return D == 64 ? launch_fwd_mode<64>(tq, tk, tv, a, s) : launch_fwd_mode<128>(tq, tk, tv, a, s);
 }
 
 extern "C" int nkb_attn_bwd(const void* q, const void* k, const void* v, const void* o,

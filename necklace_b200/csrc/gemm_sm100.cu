@@ -79,6 +79,13 @@ struct GemmArgs {
   int rs_bn;               // tile width used by the GEMM CTAs
   __nv_bfloat16* rs_out;   // [rows_per_rank, N] on this rank
   long long rs_ldout;
+  // Split-K (optional, split_k > 1): the K range is cut into split_k slices that are
+  // scheduled as independent work units, so weight-gradient shapes (few output tiles,
+  // very long K) still fill the machine.  Slice s stores its raw fp32 partial tile into
+  // splitk_ws[s][M][N]; a small follow-up kernel adds the slices and applies alpha /
+  // accumulate / output type.
+  int split_k;
+  float* splitk_ws;
 };
 
 // Reduce role of the fused reduce-scatter (see GemmArgs).
@@ -200,6 +207,39 @@ __device__ __noinline__ static void ag_copy_role(const GemmArgs& g) {
 
 __global__ void epoch_bump_kernel(int* epoch) { epoch[0] += 1; }
 
+// out = (accumulate ? out : 0) + alpha * sum_s ws[s]; 4 elements per thread-iteration
+// (N % 4 == 0 and 16-byte aligned rows are guaranteed by the caller).
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float* __restrict__ ws, int S, long long MN, int N, void* out,
+                     long long ldc, int c_fp32, int accumulate, float alpha,
+                     const float* __restrict__ alpha_dev) {
+  if (alpha_dev) alpha *= *alpha_dev;
+  const long long n4 = MN >> 2;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4;
+       i += (long long)gridDim.x * blockDim.x) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < S; ++s) {
+      float4 v = reinterpret_cast<const float4*>(ws + (long long)s * MN)[i];
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    const long long e = i << 2, row = e / N, col = e % N;
+    acc.x *= alpha; acc.y *= alpha; acc.z *= alpha; acc.w *= alpha;
+    if (c_fp32) {
+      float4* o = reinterpret_cast<float4*>(static_cast<float*>(out) + row * ldc + col);
+      if (accumulate) { float4 p = *o; acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w; }
+      *o = acc;
+    } else {
+      uint2* o = reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(out) + row * ldc + col);
+      if (accumulate) {
+        uint2 p = *o;
+        float2 a = unpack_bf16x2(p.x), b = unpack_bf16x2(p.y);
+        acc.x += a.x; acc.y += a.y; acc.z += b.x; acc.w += b.y;
+      }
+      *o = make_uint2(pack_bf16x2(acc.x, acc.y), pack_bf16x2(acc.z, acc.w));
+    }
+  }
+}
+
 __device__ __forceinline__ float gelu_tanh(float x) {
   const float k0 = 0.7978845608028654f, k1 = 0.044715f;
   float u = k0 * (x + k1 * x * x * x);
@@ -317,7 +357,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, uint8_t* stg, i
                                               uint32_t t_addr, int row0, int rows_valid, int n0,
                                               float alpha, bool bias_vec,
                                               __nv_bfloat16* rs_dst = nullptr,
-                                              long long rs_ld = 0) {
+                                              long long rs_ld = 0, float* raw_dst = nullptr) {
 #pragma unroll 1
   for (int cc = 0; cc < BN / 64; ++cc) {
     uint32_t r[64];
@@ -330,6 +370,22 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, uint8_t* stg, i
     float v[64];
 #pragma unroll
     for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]) * alpha;
+    if (raw_dst) {
+      // split-K: raw fp32 partial sums into this slice's workspace slab (pitch N)
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int cv = cols_valid - half * 32;
+        if (cv <= 0) break;
+        __syncwarp();
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          stage_set(stg, lane, q,
+                    make_uint4(r[half * 32 + q * 4], r[half * 32 + q * 4 + 1],
+                               r[half * 32 + q * 4 + 2], r[half * 32 + q * 4 + 3]));
+        stage_store_f32(stg, lane, raw_dst + cc * 64 + half * 32, g.N, rows_valid, cv);
+      }
+      continue;
+    }
     if (rs_dst) {
       // fused reduce-scatter: the raw partial sums go to the owner's staging slab;
       // bias / residual are applied by the owner after the cross-rank sum
@@ -488,6 +544,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int lane = threadIdx.x & 31;
   const int num_tiles = g.num_m_blocks * g.num_n_blocks;
   const int KB = (g.K + BK - 1) / BK;
+  const int num_units = num_tiles * g.split_k;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -518,7 +575,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = cta_id; t < num_tiles && ok; t += n_ctas) {
+      for (int u = cta_id; u < num_units && ok; u += n_ctas) {
+        const int t = u % num_tiles, ks = u / num_tiles;
+        const int kb_lo = ks * KB / g.split_k, kb_hi = (ks + 1) * KB / g.split_k;
         const int mb = (t % g.num_m_blocks + mb_shift) % g.num_m_blocks, nb = t / g.num_m_blocks;
         const int m0 = mb * BM, n0 = nb * BN;
         if (g.ready_flags) {
@@ -536,7 +595,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           // it through the async proxy
           asm volatile("fence.proxy.async.global;" ::: "memory");
         }
-        for (int kb = 0; kb < KB; ++kb) {
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
             set_error(g.status, abort_flag, NKB_ERR_EMPTY_WAIT);
             ok = false;
@@ -575,14 +634,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int t = cta_id; t < num_tiles && ok; t += n_ctas) {
+      for (int u = cta_id; u < num_units && ok; u += n_ctas) {
+        const int ks = u / num_tiles;
+        const int kb_lo = ks * KB / g.split_k, kb_hi = (ks + 1) * KB / g.split_k;
         if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag)) {
           set_error(g.status, abort_flag, NKB_ERR_ACC_FREE);
           break;
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < KB; ++kb) {
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
             set_error(g.status, abort_flag, NKB_ERR_TMA_WAIT);
             ok = false;
@@ -602,7 +663,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               db = umma_desc_sw128(aB + k * (UMMA_K * 2), 16, 1024);
             else
               db = umma_desc_sw128(aB + k * (UMMA_K * 128), 64 * BK * 2, 1024);
-            umma_bf16_ss(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            umma_bf16_ss(d_tmem, da, db, idesc, (kb > kb_lo || k > 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);  // frees the stage when these MMAs retire
           if (++stage == STAGES) {
@@ -629,7 +690,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint32_t acc_phase = 0;
     const float alpha = g.alpha_dev ? g.alpha * __ldg(g.alpha_dev) : g.alpha;
     const bool bias_vec = g.bias && ((reinterpret_cast<uintptr_t>(g.bias) & 15) == 0);
-    for (int t = cta_id; t < num_tiles; t += n_ctas) {
+    for (int u = cta_id; u < num_units; u += n_ctas) {
+      const int t = u % num_tiles, ks = u / num_tiles;
       const int mb = (t % g.num_m_blocks + mb_shift) % g.num_m_blocks, nb = t / g.num_m_blocks;
       const int row0 = mb * BM + lane_grp * 32;  // first row of this warp's slab
       const int n0 = nb * BN;
@@ -649,7 +711,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
         if (warp == 2 && lane == 0) st_release_sys(tflag, rs_epoch);
       } else {
-        epilogue_tile<BN>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec);
+        float* raw = g.split_k > 1
+                         ? g.splitk_ws + ((long long)ks * g.M + row0) * g.N + n0 : nullptr;
+        epilogue_tile<BN>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec, nullptr, 0,
+                          raw);
       }
       tc_fence_before();
       mbar_arrive(&acc_empty[acc]);
@@ -725,6 +790,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
                      : g.rs_ctas ? ((g.rs.rank + 1) % g.rs.world) * (g.rs_rows_per_rank / 256) : 0;
   const int num_tiles = num_m2 * g.num_n_blocks;
   const int KB = (g.K + BK - 1) / BK;
+  const int num_units = num_tiles * g.split_k;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < PAIR_STAGES; ++s) {
@@ -756,7 +822,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = pair; t < num_tiles && ok; t += npairs) {
+      for (int u = pair; u < num_units && ok; u += npairs) {
+        const int t = u % num_tiles, ks = u / num_tiles;
+        const int kb_lo = ks * KB / g.split_k, kb_hi = (ks + 1) * KB / g.split_k;
         const int mb2 = (t % num_m2 + mb_shift) % num_m2, nb = t / num_m2;
         const int m0 = mb2 * 256 + (int)rank * 128;
         const int nB = nb * BN + (int)rank * 128;
@@ -773,7 +841,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
           if (!ok) break;
           asm volatile("fence.proxy.async.global;" ::: "memory");
         }
-        for (int kb = 0; kb < KB; ++kb) {
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
             set_error(g.status, abort_flag, NKB_ERR_EMPTY_WAIT);
             ok = false;
@@ -812,14 +880,16 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int t = pair; t < num_tiles && ok; t += npairs) {
+      for (int u = pair; u < num_units && ok; u += npairs) {
+        const int ks = u / num_tiles;
+        const int kb_lo = ks * KB / g.split_k, kb_hi = (ks + 1) * KB / g.split_k;
         if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag)) {
           set_error(g.status, abort_flag, NKB_ERR_ACC_FREE);
           break;
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < KB; ++kb) {
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
             set_error(g.status, abort_flag, NKB_ERR_TMA_WAIT);
             ok = false;
@@ -839,7 +909,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
               db = umma_desc_sw128(aB + k * (UMMA_K * 2), 16, 1024);
             else
               db = umma_desc_sw128(aB + k * (UMMA_K * 128), 64 * BK * 2, 1024);
-            umma_bf16_ss_2cta(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            umma_bf16_ss_2cta(d_tmem, da, db, idesc, (kb > kb_lo || k > 0) ? 1u : 0u);
           }
           umma_commit_2cta(&empty_bar[stage], 3);  // frees the stage in both CTAs
           if (++stage == PAIR_STAGES) {
@@ -862,7 +932,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
     uint32_t acc_phase = 0;
     const float alpha = g.alpha_dev ? g.alpha * __ldg(g.alpha_dev) : g.alpha;
     const bool bias_vec = g.bias && ((reinterpret_cast<uintptr_t>(g.bias) & 15) == 0);
-    for (int t = pair; t < num_tiles; t += npairs) {
+    for (int u = pair; u < num_units; u += npairs) {
+      const int t = u % num_tiles, ks = u / num_tiles;
       const int mb2 = (t % num_m2 + mb_shift) % num_m2, nb = t / num_m2;
       const int row0 = mb2 * 256 + (int)rank * 128 + lane_grp * 32;
       const int n0 = nb * BN;
@@ -883,7 +954,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (warp == 2 && lane == 0) st_release_sys(tflag, rs_epoch);
       } else {
-        epilogue_tile<BN>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec);
+        float* raw = g.split_k > 1
+                         ? g.splitk_ws + ((long long)ks * g.M + row0) * g.N + n0 : nullptr;
+        epilogue_tile<BN>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec, nullptr, 0,
+                          raw);
       }
       tc_fence_before();
       __syncwarp();
@@ -946,7 +1020,10 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* base, long long inner, long 
 }
 
 static int g_num_sms = 0;
-static int g_pair_enabled = 1;  // CTA-pair tiles in the automatic choice
+static int g_pair_enabled = 1;
+static int g_splitk_enabled = 1;
+static float* g_splitk_ws = nullptr;      // caller-provided workspace (see nkb_gemm_set_workspace)
+static long long g_splitk_ws_floats = 0;  // CTA-pair tiles in the automatic choice
 int num_sms() {
   if (!g_num_sms) {
     int dev = 0;
@@ -973,7 +1050,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs&
   }
   g.num_m_blocks = (g.M + BM - 1) / BM;
   g.num_n_blocks = (g.N + BN - 1) / BN;
-  int tiles = g.num_m_blocks * g.num_n_blocks;
+  int tiles = g.num_m_blocks * g.num_n_blocks * g.split_k;
   int ctas = num_sms() - g.ag_ctas - g.rs_ctas;
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
   if (tiles < ctas) ctas = tiles;
@@ -996,7 +1073,7 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, Gemm
   }
   g.num_m_blocks = (g.M + 255) / 256;
   g.num_n_blocks = (g.N + 255) / 256;
-  int tiles = g.num_m_blocks * g.num_n_blocks;
+  int tiles = g.num_m_blocks * g.num_n_blocks * g.split_k;
   int ctas = num_sms() - g.ag_ctas - g.rs_ctas;
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
   ctas &= ~1;
@@ -1012,6 +1089,41 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, Gemm
 using namespace nkb;
 
 extern "C" void nkb_gemm_set_pair(int enabled) { nkb::g_pair_enabled = enabled; }
+extern "C" void nkb_gemm_set_splitk(int enabled) { nkb::g_splitk_enabled = enabled; }
+// Caller-owned fp32 workspace for split-K partial tiles (the library never allocates);
+// without one, split-K is not used.
+extern "C" void nkb_gemm_set_workspace(float* ws, long long n_floats) {
+  nkb::g_splitk_ws = ws;
+  nkb::g_splitk_ws_floats = n_floats;
+}
+
+static int gemm_run_splitk(GemmArgs g, const CUtensorMap& tmA, const CUtensorMap& tmB, int a_mn,
+                           int b_mn, bool pair, int BN, int max_ctas, cudaStream_t s) {
+  int rc;
+  if (pair) {
+    rc = (!a_mn && !b_mn) ? launch_gemm_pair<false, false>(tmA, tmB, g, max_ctas, s)
+         : (!a_mn && b_mn) ? launch_gemm_pair<false, true>(tmA, tmB, g, max_ctas, s)
+         : (a_mn && !b_mn) ? launch_gemm_pair<true, false>(tmA, tmB, g, max_ctas, s)
+                           : launch_gemm_pair<true, true>(tmA, tmB, g, max_ctas, s);
+  } else if (BN == 256) {
+    rc = (!a_mn && !b_mn) ? launch_gemm<256, false, false>(tmA, tmB, g, max_ctas, s)
+         : (!a_mn && b_mn) ? launch_gemm<256, false, true>(tmA, tmB, g, max_ctas, s)
+         : (a_mn && !b_mn) ? launch_gemm<256, true, false>(tmA, tmB, g, max_ctas, s)
+                           : launch_gemm<256, true, true>(tmA, tmB, g, max_ctas, s);
+  } else {
+    rc = (!a_mn && !b_mn) ? launch_gemm<128, false, false>(tmA, tmB, g, max_ctas, s)
+         : (!a_mn && b_mn) ? launch_gemm<128, false, true>(tmA, tmB, g, max_ctas, s)
+         : (a_mn && !b_mn) ? launch_gemm<128, true, false>(tmA, tmB, g, max_ctas, s)
+                           : launch_gemm<128, true, true>(tmA, tmB, g, max_ctas, s);
+  }
+  if (rc) return rc;
+  const long long MN = (long long)g.M * g.N;
+  int blocks = (int)((MN / 4 + 255) / 256);
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  splitk_reduce_kernel<<<blocks, 256, 0, s>>>(g.splitk_ws, g.split_k, MN, g.N, g.C, g.ldc, g.c_fp32,
+                                              g.accumulate, g.alpha, g.alpha_dev);
+  return (int)cudaGetLastError();
+}
 
 static int gemm_run(GemmArgs g, const void* A, long long lda, int a_mn, const void* B,
                     long long ldb, int b_mn, int max_ctas, int bn_hint, void* stream) {
@@ -1041,6 +1153,22 @@ static int gemm_run(GemmArgs g, const void* A, long long lda, int a_mn, const vo
     if (g_pair_enabled && M > 128 && N > 128 && cp <= best) pair = true;
     if (g.ag_ctas && (g.ag_rows_per_rank % 256)) pair = false;
   }
+  // split-K when the output has too few tiles to occupy the machine and K is long
+  g.split_k = 1;
+  g.splitk_ws = nullptr;
+  if (g_splitk_enabled && g_splitk_ws && !g.ag_ctas && !g.rs_ctas && g.epi == NKB_EPI_NONE &&
+      !g.bias && !g.res && (N % 4) == 0 && (g.ldc % 4) == 0 && K >= 2048) {
+    long long slots = pair ? num_sms() / 2 : num_sms();
+    long long tl = pair ? ((M + 255) / 256) * (long long)((N + 255) / 256)
+                        : ((M + BM - 1) / BM) * (long long)((N + BN - 1) / BN);
+    int S = (int)(slots / tl);
+    if (S > 8) S = 8;
+    while (S > 1 && (K / BK) / S < 8) --S;
+    if (S > 1 && tl * 10 <= slots * 7 && (long long)S * M * N <= g_splitk_ws_floats) {
+      g.split_k = S;
+      g.splitk_ws = g_splitk_ws;
+    }
+  }
   CUtensorMap tmA, tmB;
   int rc;
   if (!a_mn) rc = make_tmap_bf16_2d(&tmA, A, K, M, lda, BK, BM);
@@ -1051,6 +1179,7 @@ static int gemm_run(GemmArgs g, const void* A, long long lda, int a_mn, const vo
   if (rc) return rc;
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (g.split_k > 1) return gemm_run_splitk(g, tmA, tmB, a_mn, b_mn, pair, BN, max_ctas, s);
   if (pair) {
     if (!a_mn && !b_mn) return launch_gemm_pair<false, false>(tmA, tmB, g, max_ctas, s);
     if (!a_mn && b_mn) return launch_gemm_pair<false, true>(tmA, tmB, g, max_ctas, s);

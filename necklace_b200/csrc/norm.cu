@@ -148,44 +148,70 @@ norm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   }
 }
 
-// Column sums. Block = 32 x 16 threads: x-lane owns 2 adjacent columns, y
-// splits rows. grid = (ceil(C/64), row_splits).
-__global__ void __launch_bounds__(512)
+// Column sums.  Block = 32 x 8 threads: a lane owns 8 adjacent columns (one 16-byte
+// load per row), the 8 warps take interleaved rows; grid = (ceil(C/256), row_splits).
+// Two rows are in flight per thread to cover memory latency.
+__global__ void __launch_bounds__(256)
 colsum_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
               const float* __restrict__ stats, float* __restrict__ acc, int rows, int C,
               long long ld, int rms) {
-  __shared__ float sh[2][16][64];
-  const int col = blockIdx.x * 64 + threadIdx.x * 2;
-  float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+  __shared__ float sh[8][256 + 8];
+  const int lane = threadIdx.x & 31, wy = threadIdx.x >> 5;
+  const int col = blockIdx.x * 256 + lane * 8;
+  float a[8], b[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) a[k] = b[k] = 0.f;
+  const bool vec = (col + 8 <= C) && ((ld & 7) == 0);
+  const int stride = gridDim.y * 8;
   if (col < C) {
-    for (int r = blockIdx.y * 16 + threadIdx.y; r < rows; r += gridDim.y * 16) {
-      uint32_t gu = *reinterpret_cast<const uint32_t*>(dy + (long long)r * ld + col);
-      float2 gf = unpack_bf16x2(gu);
-      b0 += gf.x;
-      b1 += gf.y;
+    for (int r = blockIdx.y * 8 + wy; r < rows; r += stride) {
+      float g[8], xv[8];
+      if (vec) {
+        uint4 gu = ld_nc_v4(dy + (long long)r * ld + col);
+        uint32_t w[4] = {gu.x, gu.y, gu.z, gu.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 f = unpack_bf16x2(w[j]);
+          g[2 * j] = f.x; g[2 * j + 1] = f.y;
+        }
+        if (x) {
+          uint4 xu = ld_nc_v4(x + (long long)r * ld + col);
+          uint32_t v[4] = {xu.x, xu.y, xu.z, xu.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float2 f = unpack_bf16x2(v[j]);
+            xv[2 * j] = f.x; xv[2 * j + 1] = f.y;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          g[k] = (col + k < C) ? __bfloat162float(dy[(long long)r * ld + col + k]) : 0.f;
+          xv[k] = (x && col + k < C) ? __bfloat162float(x[(long long)r * ld + col + k]) : 0.f;
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) b[k] += g[k];
       if (x) {
-        uint32_t xu = *reinterpret_cast<const uint32_t*>(x + (long long)r * ld + col);
-        float2 xf = unpack_bf16x2(xu);
         const float mean = rms ? 0.f : stats[2 * r];
         const float rstd = stats[2 * r + 1];
-        a0 += gf.x * (xf.x - mean) * rstd;
-        a1 += gf.y * (xf.y - mean) * rstd;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) a[k] += g[k] * (xv[k] - mean) * rstd;
       }
     }
   }
-  sh[0][threadIdx.y][threadIdx.x * 2] = a0;
-  sh[0][threadIdx.y][threadIdx.x * 2 + 1] = a1;
-  sh[1][threadIdx.y][threadIdx.x * 2] = b0;
-  sh[1][threadIdx.y][threadIdx.x * 2 + 1] = b1;
-  __syncthreads();
-  const int tid = threadIdx.y * 32 + threadIdx.x;
-  if (tid < 128) {
-    const int which = tid >> 6, c = tid & 63;
+  for (int which = 0; which < 2; ++which) {
+    if (which == 0 && !x) continue;
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 8; ++k) sh[wy][lane * 8 + k] = which == 0 ? a[k] : b[k];
+    __syncthreads();
+    const int c = threadIdx.x;
     float s = 0.f;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) s += sh[which][i][c];
-    const int gc = blockIdx.x * 64 + c;
-    if (gc < C && (which == 1 || x)) atomicAdd(&acc[(long long)which * C + gc], s);
+    for (int i = 0; i < 8; ++i) s += sh[i][c];
+    const int gc = blockIdx.x * 256 + c;
+    if (gc < C) atomicAdd(&acc[(long long)which * C + gc], s);
   }
 }
 
@@ -252,13 +278,12 @@ extern "C" int nkb_norm_bwd_dx(const void* dy, const void* x, const void* w, con
 extern "C" int nkb_colsum(const void* dy, const void* x, const float* stats, float* acc, int rows,
                           int C, long long ld, int rms, void* stream) {
   if ((C & 1) || (ld & 1)) return -3;
-  dim3 block(32, 16);
-  int gx = (C + 63) / 64;
-  int gy = (4 * 148 + gx - 1) / gx;
-  int max_gy = (rows + 15) / 16;
+  int gx = (C + 255) / 256;
+  int gy = (8 * 148 + gx - 1) / gx;
+  int max_gy = (rows + 7) / 8;
   if (gy > max_gy) gy = max_gy;
   if (gy < 1) gy = 1;
-  colsum_kernel<<<dim3(gx, gy), block, 0, static_cast<cudaStream_t>(stream)>>>(
+  colsum_kernel<<<dim3(gx, gy), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), stats, acc, rows,
       C, ld, rms);
   return (int)cudaGetLastError();

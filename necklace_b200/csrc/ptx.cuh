@@ -273,6 +273,33 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t* r) {
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ uint32_t tmem_ld_32x1(uint32_t taddr) {
+  uint32_t r;
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr)
+               : "memory");
+  return r;
+}
+// two exponentials per MUFU op: packed half / bfloat16 inputs and outputs
+__device__ __forceinline__ uint32_t ex2_f16x2(float x0, float x1) {
+  uint32_t h, e;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(h) : "f"(x1), "f"(x0));
+  asm("ex2.approx.f16x2 %0, %1;" : "=r"(e) : "r"(h));
+  return e;
+}
+__device__ __forceinline__ uint32_t ex2_bf16x2(float x0, float x1) {
+  uint32_t h, e;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(h) : "f"(x1), "f"(x0));
+  asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(e) : "r"(h));
+  return e;
+}
+__device__ __forceinline__ uint32_t f16x2_to_bf16x2(uint32_t h) {
+  float lo, hi;
+  uint32_t o;
+  asm("{\n\t.reg .f16 a, b;\n\tmov.b32 {a, b}, %2;\n\tcvt.f32.f16 %0, a;\n\tcvt.f32.f16 %1, b;\n\t}"
+      : "=f"(lo), "=f"(hi) : "r"(h));
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o) : "f"(hi), "f"(lo));
+  return o;
+}
 __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t* r) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 "

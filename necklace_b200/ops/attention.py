@@ -17,6 +17,15 @@ from .. import _lib
 from ._common import on_gpu, status_word
 
 
+def set_exp_mode(mode: int) -> None:
+    """Forward kernel variant: 0 = fp32 exponentials, 1 = packed half exponentials (default),
+    2 = packed bf16 exponentials (fastest, ~1% relative error on small probabilities)."""
+    lib = _lib.load()
+    lib.nkb_attn_set_exp_mode.argtypes = [_lib.i32]
+    lib.nkb_attn_set_exp_mode.restype = None
+    lib.nkb_attn_set_exp_mode(int(mode))
+
+
 def _ref_attention(q, k, v, causal, scale):
     # q,k,v: [B,H,S,D] fp32
     s = (q @ k.transpose(-1, -2)) * scale

@@ -83,6 +83,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         a = _repack(a)
     if b.stride(0) % 8 or b.data_ptr() % 16:
         b = _repack(b)
+    _ensure_workspace(a.device)
     _lib.call("nkb_gemm_bf16", a.data_ptr(), a.stride(0), int(a_mn), b.data_ptr(), b.stride(0),
               int(b_mn), out.data_ptr(), out.stride(0), int(out.dtype == torch.float32),
               int(accumulate), M, N, K, float(alpha), ptr(bias), ptr(res),
@@ -92,6 +93,32 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
               ptr(alpha_dev), _lib.stream_ptr())
     _lib.count_launch()
     return out
+
+
+_WORKSPACE: dict = {}
+SPLITK_WORKSPACE_FLOATS = 32 * 1024 * 1024  # 128 MB: 8 slices of a 1024 x 4096 fp32 tile set
+
+
+def _ensure_workspace(device) -> None:
+    """Hand the library its split-K workspace (the library itself never allocates).  One
+    buffer per device, owned here for the life of the process; weight-gradient GEMMs with
+    few output tiles and a long K use it to spread their K range over all SMs."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx in _WORKSPACE:
+        return
+    ws = torch.empty(SPLITK_WORKSPACE_FLOATS, dtype=torch.float32, device=device)
+    _WORKSPACE[idx] = ws
+    lib = _lib.load()
+    lib.nkb_gemm_set_workspace.argtypes = [_lib.vp, _lib.i64]
+    lib.nkb_gemm_set_workspace.restype = None
+    lib.nkb_gemm_set_workspace(ws.data_ptr(), ws.numel())
+
+
+def set_splitk(enabled: bool) -> None:
+    lib = _lib.load()
+    lib.nkb_gemm_set_splitk.argtypes = [_lib.i32]
+    lib.nkb_gemm_set_splitk.restype = None
+    lib.nkb_gemm_set_splitk(int(enabled))
 
 
 def _repack(t: torch.Tensor) -> torch.Tensor:

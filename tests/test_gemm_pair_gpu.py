@@ -59,3 +59,22 @@ def test_pair_epilogues():
     C0 = C.clone()
     gemm(A, B, out=C, accumulate=True, alpha=0.5, bn=512)
     assert _rel_err(C, C0 + 0.5 * base) < 1e-2
+
+
+@pytest.mark.parametrize("bn", [0, 256, 512])
+@pytest.mark.parametrize("M,N,K,acc", [(1024, 1024, 8192, False), (3072, 1024, 4096, True),
+                                       (256, 512, 2048, False), (1024, 4096, 8192, False)])
+def test_split_k_weight_gradient_shapes(bn, M, N, K, acc):
+    """Few output tiles and a long K: the split-K path (slices + reduce kernel)."""
+    from necklace_b200.ops import gemm
+    torch.manual_seed(2)
+    At = (torch.randn(K, M, device=DEV) * 0.1).bfloat16()   # MN-major operands (wgrad layout)
+    Bt = (torch.randn(K, N, device=DEV) * 0.1).bfloat16()
+    ref = At.float().t() @ Bt.float()
+    out = torch.randn(M, N, device=DEV).bfloat16() if acc else None
+    base = out.float().clone() if acc else 0
+    got = gemm(At, Bt, a_mn=True, b_mn=True, out=out, accumulate=acc, alpha=0.5, bn=bn)
+    assert _rel_err(got, base + 0.5 * ref) < 1e-2
+    c32 = torch.zeros(M, N, device=DEV)
+    gemm(At, Bt, a_mn=True, b_mn=True, out=c32, bn=bn)
+    assert _rel_err(c32, ref) < 5e-3
