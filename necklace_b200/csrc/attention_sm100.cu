@@ -329,6 +329,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 }
 
+#include "attention_fwd_pp.cuh"
+
 // ------------------------------------------------------------------ backward
 struct AttnBwdArgs {
   const float* lse;
@@ -695,7 +697,9 @@ static int make_tmap_bshd(CUtensorMap* out, const void* base, int B, int H, int 
   return r == CUDA_SUCCESS ? 0 : -(int)r - 1000;
 }
 
-static int g_attn_exp_mode = 1;
+// 0: fp32 exp (default; the packed forms measured no faster: the softmax warps are not
+// bound by the exponential alone), 1: packed f16x2, 2: packed bf16x2
+static int g_attn_exp_mode = 0;
 
 template <int D, int EXPM>
 static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
@@ -713,9 +717,32 @@ static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
   return (int)cudaGetLastError();
 }
 
+// 1: ping-pong kernel (two query tiles per CTA, P through TMEM), 0: one query tile per CTA
+static int g_attn_fwd_impl = 1;
+
+template <int D, int EXPM>
+static int launch_fwd_pp(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                         const AttnFwdArgs& a, cudaStream_t s) {
+  constexpr int smem = 6 * (128 * D * 2) + 1024 + 256;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_pp_kernel<D, EXPM>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid(a.B * a.H, (a.S + 255) / 256);
+  attn_fwd_pp_kernel<D, EXPM><<<grid, ATT2_THREADS, smem, s>>>(tq, tk, tv, a);
+  return (int)cudaGetLastError();
+}
+
 template <int D>
 static int launch_fwd_mode(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                            const AttnFwdArgs& a, cudaStream_t s) {
+  if (g_attn_fwd_impl == 1) {
+    if (g_attn_exp_mode == 0) return launch_fwd_pp<D, 0>(tq, tk, tv, a, s);
+    return launch_fwd_pp<D, 1>(tq, tk, tv, a, s);
+  }
   if (g_attn_exp_mode == 0) return launch_fwd<D, 0>(tq, tk, tv, a, s);
   if (g_attn_exp_mode == 2) return launch_fwd<D, 2>(tq, tk, tv, a, s);
   return launch_fwd<D, 1>(tq, tk, tv, a, s);
@@ -742,8 +769,10 @@ static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
 
 using namespace nkb;
 
-// 0 = fp32 exponentials, 1 = packed half (default), 2 = packed bf16
+// 0 = fp32 exponentials (default), 1 = packed half, 2 = packed bf16 (one-tile kernel only)
 extern "C" void nkb_attn_set_exp_mode(int mode) { nkb::g_attn_exp_mode = mode; }
+// 1 = ping-pong forward kernel (default), 0 = one query tile per CTA
+extern "C" void nkb_attn_set_fwd_impl(int impl) { nkb::g_attn_fwd_impl = impl; }
 
 extern "C" int nkb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
                             int B, int H, int S, int D, long long sb, long long sh, long long ss,

@@ -352,7 +352,9 @@ __device__ __forceinline__ void stage_load_f32(uint8_t* stg, int lane, const flo
 
 // Epilogue of one 128 x BN accumulator slab: this warp's 32 rows (TMEM lanes), BN
 // columns starting at global column n0; fused math, then staged coalesced stores.
-template <int BN>
+// MODE 0: plain epilogue; 1: kernel fused with a collective (rs_dst set: raw partial
+// sums to the owner's staging slab); 2: split-K (raw fp32 partial sums to raw_dst).
+template <int BN, int MODE>
 __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, uint8_t* stg, int lane,
                                               uint32_t t_addr, int row0, int rows_valid, int n0,
                                               float alpha, bool bias_vec,
@@ -370,28 +372,31 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, uint8_t* stg, i
     float v[64];
 #pragma unroll
     for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]) * alpha;
-    if (raw_dst) {
+    if constexpr (MODE == 2) {
       // split-K: raw fp32 partial sums into this slice's workspace slab (pitch N)
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         const int cv = cols_valid - half * 32;
-        if (cv <= 0) break;
-        __syncwarp();
+        if (cv > 0) {
+          __syncwarp();
 #pragma unroll
-        for (int q = 0; q < 8; ++q)
-          stage_set(stg, lane, q,
-                    make_uint4(r[half * 32 + q * 4], r[half * 32 + q * 4 + 1],
-                               r[half * 32 + q * 4 + 2], r[half * 32 + q * 4 + 3]));
-        stage_store_f32(stg, lane, raw_dst + cc * 64 + half * 32, g.N, rows_valid, cv);
+          for (int q = 0; q < 8; ++q)
+            stage_set(stg, lane, q,
+                      make_uint4(r[half * 32 + q * 4], r[half * 32 + q * 4 + 1],
+                                 r[half * 32 + q * 4 + 2], r[half * 32 + q * 4 + 3]));
+          stage_store_f32(stg, lane, raw_dst + cc * 64 + half * 32, g.N, rows_valid, cv);
+        }
       }
       continue;
     }
-    if (rs_dst) {
-      // fused reduce-scatter: the raw partial sums go to the owner's staging slab;
-      // bias / residual are applied by the owner after the cross-rank sum
-      stage_put_bf16(stg, lane, v);
-      stage_store_bf16(stg, lane, rs_dst + cc * 64, rs_ld, rows_valid, cols_valid);
-      continue;
+    if constexpr (MODE == 1) {
+      if (rs_dst) {
+        // fused reduce-scatter: the raw partial sums go to the owner's staging slab;
+        // bias / residual are applied by the owner after the cross-rank sum
+        stage_put_bf16(stg, lane, v);
+        stage_store_bf16(stg, lane, rs_dst + cc * 64, rs_ld, rows_valid, cols_valid);
+        continue;
+      }
     }
     if (g.bias) {
       if (bias_vec && cols_valid == 64 && (col0 & 7) == 0) {
@@ -457,7 +462,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, uint8_t* stg, i
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         const int cv = cols_valid - half * 32;
-        if (cv <= 0) break;
+        if (cv <= 0) continue;
         if (g.accumulate) {
           stage_load_f32(stg, lane, cbase + half * 32, g.ldc, rows_valid, cv);
 #pragma unroll
@@ -502,7 +507,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, uint8_t* stg, i
   }
 }
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, int MODE>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const GemmArgs g) {
@@ -523,28 +528,33 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-  if ((int)blockIdx.x < g.ag_ctas) {
-    ag_copy_role(g);
-    return;
+  constexpr bool COMM = MODE == 1;
+  const int ag_ctas = COMM ? g.ag_ctas : 0, rs_ctas = COMM ? g.rs_ctas : 0;
+  const int split_k = MODE == 2 ? g.split_k : 1;
+  if constexpr (COMM) {
+    if ((int)blockIdx.x < ag_ctas) {
+      ag_copy_role(g);
+      return;
+    }
+    if ((int)blockIdx.x < rs_ctas) {
+      rs_reduce_role(g);
+      return;
+    }
   }
-  if ((int)blockIdx.x < g.rs_ctas) {
-    rs_reduce_role(g);
-    return;
-  }
-  const int pre = g.ag_ctas + g.rs_ctas;  // at most one of the two is non-zero
+  const int pre = ag_ctas + rs_ctas;  // at most one of the two is non-zero
   const int cta_id = blockIdx.x - pre, n_ctas = gridDim.x - pre;
-  const int rs_epoch = g.rs_ctas ? *reinterpret_cast<volatile int*>(g.rs.epoch) + 1 : 0;
-  const int ready_target = g.ag_ctas ? *reinterpret_cast<volatile int*>(g.ag.epoch) + 1
-                                     : g.ready_target;
+  const int rs_epoch = rs_ctas ? *reinterpret_cast<volatile int*>(g.rs.epoch) + 1 : 0;
+  const int ready_target = ag_ctas ? *reinterpret_cast<volatile int*>(g.ag.epoch) + 1
+                                   : g.ready_target;
   // with a fused all-gather the local shard's row blocks come first
   // ... and with a fused reduce-scatter the rows owned by the other ranks
-  const int mb_shift = g.ag_ctas ? g.ag.rank * ((g.ag_rows_per_rank + BM - 1) / BM)
-                     : g.rs_ctas ? ((g.rs.rank + 1) % g.rs.world) * (g.rs_rows_per_rank / BM) : 0;
+  const int mb_shift = ag_ctas ? g.ag.rank * ((g.ag_rows_per_rank + BM - 1) / BM)
+                     : rs_ctas ? ((g.rs.rank + 1) % g.rs.world) * (g.rs_rows_per_rank / BM) : 0;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_tiles = g.num_m_blocks * g.num_n_blocks;
   const int KB = (g.K + BK - 1) / BK;
-  const int num_units = num_tiles * g.split_k;
+  const int num_units = num_tiles * split_k;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -577,7 +587,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       bool ok = true;
       for (int u = cta_id; u < num_units && ok; u += n_ctas) {
         const int t = u % num_tiles, ks = u / num_tiles;
-        const int kb_lo = ks * KB / g.split_k, kb_hi = (ks + 1) * KB / g.split_k;
+        const int kb_lo = ks * KB / split_k, kb_hi = (ks + 1) * KB / split_k;
         const int mb = (t % g.num_m_blocks + mb_shift) % g.num_m_blocks, nb = t / g.num_m_blocks;
         const int m0 = mb * BM, n0 = nb * BN;
         if (g.ready_flags) {
@@ -636,7 +646,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       bool ok = true;
       for (int u = cta_id; u < num_units && ok; u += n_ctas) {
         const int ks = u / num_tiles;
-        const int kb_lo = ks * KB / g.split_k, kb_hi = (ks + 1) * KB / g.split_k;
+        const int kb_lo = ks * KB / split_k, kb_hi = (ks + 1) * KB / split_k;
         if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag)) {
           set_error(g.status, abort_flag, NKB_ERR_ACC_FREE);
           break;
@@ -703,18 +713,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       tc_fence_after();
       const uint32_t t_addr = tmem_base + (uint32_t(lane_grp * 32) << 16) + acc * BN;
-      if (g.rs_ctas) {
+      if (rs_ctas) {
         int* tflag;
         __nv_bfloat16* dst = rs_tile_dst(g, mb * BM, lane_grp, n0, &tflag, nb, g.num_n_blocks);
-        epilogue_tile<BN>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec, dst, g.N);
+        epilogue_tile<BN, MODE>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec, dst,
+                                g.N);
         __threadfence_system();
         asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
         if (warp == 2 && lane == 0) st_release_sys(tflag, rs_epoch);
       } else {
-        float* raw = g.split_k > 1
-                         ? g.splitk_ws + ((long long)ks * g.M + row0) * g.N + n0 : nullptr;
-        epilogue_tile<BN>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec, nullptr, 0,
-                          raw);
+        float* raw = MODE == 2 ? g.splitk_ws + ((long long)ks * g.M + row0) * g.N + n0 : nullptr;
+        epilogue_tile<BN, MODE>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec,
+                                nullptr, 0, raw);
       }
       tc_fence_before();
       mbar_arrive(&acc_empty[acc]);
@@ -751,7 +761,7 @@ constexpr int PAIR_STAGES = 6;
 constexpr int PAIR_B_BYTES = 128 * BK * 2;
 constexpr int PAIR_STAGE_BYTES = A_STAGE_BYTES + PAIR_B_BYTES;
 
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, int MODE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
                       const __grid_constant__ CUtensorMap tmB, const GemmArgs g) {
@@ -768,29 +778,34 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-  if ((int)blockIdx.x < g.ag_ctas) {  // ag_ctas is even: whole clusters take the copy role
-    ag_copy_role(g);
-    return;
+  constexpr bool COMM = MODE == 1;
+  const int ag_ctas = COMM ? g.ag_ctas : 0, rs_ctas = COMM ? g.rs_ctas : 0;
+  const int split_k = MODE == 2 ? g.split_k : 1;
+  if constexpr (COMM) {
+    if ((int)blockIdx.x < ag_ctas) {  // ag_ctas is even: whole clusters take the copy role
+      ag_copy_role(g);
+      return;
+    }
+    if ((int)blockIdx.x < rs_ctas) {
+      rs_reduce_role(g);
+      return;
+    }
   }
-  if ((int)blockIdx.x < g.rs_ctas) {
-    rs_reduce_role(g);
-    return;
-  }
-  const int rs_epoch = g.rs_ctas ? *reinterpret_cast<volatile int*>(g.rs.epoch) + 1 : 0;
-  const int ready_target = g.ag_ctas ? *reinterpret_cast<volatile int*>(g.ag.epoch) + 1
-                                     : g.ready_target;
+  const int rs_epoch = rs_ctas ? *reinterpret_cast<volatile int*>(g.rs.epoch) + 1 : 0;
+  const int ready_target = ag_ctas ? *reinterpret_cast<volatile int*>(g.ag.epoch) + 1
+                                   : g.ready_target;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
-  const int pre = g.ag_ctas + g.rs_ctas;
+  const int pre = ag_ctas + rs_ctas;
   const int pair = ((int)blockIdx.x - pre) >> 1, npairs = ((int)gridDim.x - pre) >> 1;
   const int num_m2 = (g.M + 255) / 256;
-  const int mb_shift = g.ag_ctas ? g.ag.rank * ((g.ag_rows_per_rank + 255) / 256)
-                     : g.rs_ctas ? ((g.rs.rank + 1) % g.rs.world) * (g.rs_rows_per_rank / 256) : 0;
+  const int mb_shift = ag_ctas ? g.ag.rank * ((g.ag_rows_per_rank + 255) / 256)
+                     : rs_ctas ? ((g.rs.rank + 1) % g.rs.world) * (g.rs_rows_per_rank / 256) : 0;
   const int num_tiles = num_m2 * g.num_n_blocks;
   const int KB = (g.K + BK - 1) / BK;
-  const int num_units = num_tiles * g.split_k;
+  const int num_units = num_tiles * split_k;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < PAIR_STAGES; ++s) {
@@ -824,7 +839,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       bool ok = true;
       for (int u = pair; u < num_units && ok; u += npairs) {
         const int t = u % num_tiles, ks = u / num_tiles;
-        const int kb_lo = ks * KB / g.split_k, kb_hi = (ks + 1) * KB / g.split_k;
+        const int kb_lo = ks * KB / split_k, kb_hi = (ks + 1) * KB / split_k;
         const int mb2 = (t % num_m2 + mb_shift) % num_m2, nb = t / num_m2;
         const int m0 = mb2 * 256 + (int)rank * 128;
         const int nB = nb * BN + (int)rank * 128;
@@ -882,7 +897,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       bool ok = true;
       for (int u = pair; u < num_units && ok; u += npairs) {
         const int ks = u / num_tiles;
-        const int kb_lo = ks * KB / g.split_k, kb_hi = (ks + 1) * KB / g.split_k;
+        const int kb_lo = ks * KB / split_k, kb_hi = (ks + 1) * KB / split_k;
         if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag)) {
           set_error(g.status, abort_flag, NKB_ERR_ACC_FREE);
           break;
@@ -945,19 +960,19 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       }
       tc_fence_after();
       const uint32_t t_addr = tmem_base + (uint32_t(lane_grp * 32) << 16) + acc * BN;
-      if (g.rs_ctas) {
+      if (rs_ctas) {
         int* tflag;
         __nv_bfloat16* dst = rs_tile_dst(g, mb2 * 256 + (int)rank * 128, lane_grp, n0, &tflag, nb,
                                          g.num_n_blocks);
-        epilogue_tile<BN>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec, dst, g.N);
+        epilogue_tile<BN, MODE>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec, dst,
+                                g.N);
         __threadfence_system();
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (warp == 2 && lane == 0) st_release_sys(tflag, rs_epoch);
       } else {
-        float* raw = g.split_k > 1
-                         ? g.splitk_ws + ((long long)ks * g.M + row0) * g.N + n0 : nullptr;
-        epilogue_tile<BN>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec, nullptr, 0,
-                          raw);
+        float* raw = MODE == 2 ? g.splitk_ws + ((long long)ks * g.M + row0) * g.N + n0 : nullptr;
+        epilogue_tile<BN, MODE>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec,
+                                nullptr, 0, raw);
       }
       tc_fence_before();
       __syncwarp();
@@ -1034,14 +1049,14 @@ int num_sms() {
   return g_num_sms;
 }
 
-template <int BN, bool A_MN, bool B_MN>
-static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs& g, int max_ctas,
-                       cudaStream_t stream) {
+template <int BN, bool A_MN, bool B_MN, int MODE>
+static int launch_gemm_mode(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs& g,
+                            int max_ctas, cudaStream_t stream) {
   constexpr int STAGES = (BN == 256) ? 4 : 6;
   constexpr int smem_bytes =
       STAGES * (A_STAGE_BYTES + BN * BK * 2) + 4 * EPI_STAGE_BYTES + 1024 + 256;
   static bool configured = false;
-  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, MODE>;
   if (!configured) {
     cudaError_t e =
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
@@ -1059,12 +1074,22 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs&
   return (int)cudaGetLastError();
 }
 
-template <bool A_MN, bool B_MN>
-static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs& g,
-                            int max_ctas, cudaStream_t stream) {
+// MODE: 0 plain, 1 fused with a collective, 2 split-K (separate instantiations keep the
+// plain kernel free of the other paths' registers and branches)
+template <int BN, bool A_MN, bool B_MN>
+static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs& g, int max_ctas,
+                       cudaStream_t stream) {
+  if (g.ag_ctas || g.rs_ctas) return launch_gemm_mode<BN, A_MN, B_MN, 1>(tmA, tmB, g, max_ctas, stream);
+  if (g.split_k > 1) return launch_gemm_mode<BN, A_MN, B_MN, 2>(tmA, tmB, g, max_ctas, stream);
+  return launch_gemm_mode<BN, A_MN, B_MN, 0>(tmA, tmB, g, max_ctas, stream);
+}
+
+template <bool A_MN, bool B_MN, int MODE>
+static int launch_gemm_pair_mode(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs& g,
+                                 int max_ctas, cudaStream_t stream) {
   constexpr int smem_bytes = PAIR_STAGES * PAIR_STAGE_BYTES + 4 * EPI_STAGE_BYTES + 1024 + 256;
   static bool configured = false;
-  auto kern = gemm_bf16_pair_kernel<A_MN, B_MN>;
+  auto kern = gemm_bf16_pair_kernel<A_MN, B_MN, MODE>;
   if (!configured) {
     cudaError_t e =
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
@@ -1082,6 +1107,14 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, Gemm
   g.rs_bn = 256;
   kern<<<ctas + g.ag_ctas + g.rs_ctas, GEMM_THREADS, smem_bytes, stream>>>(tmA, tmB, g);
   return (int)cudaGetLastError();
+}
+
+template <bool A_MN, bool B_MN>
+static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs& g,
+                            int max_ctas, cudaStream_t stream) {
+  if (g.ag_ctas || g.rs_ctas) return launch_gemm_pair_mode<A_MN, B_MN, 1>(tmA, tmB, g, max_ctas, stream);
+  if (g.split_k > 1) return launch_gemm_pair_mode<A_MN, B_MN, 2>(tmA, tmB, g, max_ctas, stream);
+  return launch_gemm_pair_mode<A_MN, B_MN, 0>(tmA, tmB, g, max_ctas, stream);
 }
 
 }  // namespace nkb

@@ -300,6 +300,22 @@ __device__ __forceinline__ uint32_t f16x2_to_bf16x2(uint32_t h) {
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o) : "f"(hi), "f"(lo));
   return o;
 }
+// one MUFU op, flush-to-zero, no range fix-up (inputs here are <= small positive values)
+__device__ __forceinline__ float ex2_f32(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// three-input maximum (one instruction on sm_100)
+__device__ __forceinline__ float max3_f32(float a, float b, float c) {
+  float y;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+  return y;
+}
+__device__ __forceinline__ void unpack_f16x2(uint32_t h, float& lo, float& hi) {
+  asm("{\n\t.reg .f16 a, b;\n\tmov.b32 {a, b}, %2;\n\tcvt.f32.f16 %0, a;\n\tcvt.f32.f16 %1, b;\n\t}"
+      : "=f"(lo), "=f"(hi) : "r"(h));
+}
 __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t* r) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 "

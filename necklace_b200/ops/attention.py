@@ -18,12 +18,21 @@ from ._common import on_gpu, status_word
 
 
 def set_exp_mode(mode: int) -> None:
-    """Forward kernel variant: 0 = fp32 exponentials, 1 = packed half exponentials (default),
-    2 = packed bf16 exponentials (fastest, ~1% relative error on small probabilities)."""
+    """Forward exponentials: 0 = fp32 (default), 1 = packed half (two per MUFU op),
+    2 = packed bf16 (one-tile kernel only)."""
     lib = _lib.load()
     lib.nkb_attn_set_exp_mode.argtypes = [_lib.i32]
     lib.nkb_attn_set_exp_mode.restype = None
     lib.nkb_attn_set_exp_mode(int(mode))
+
+
+def set_fwd_impl(impl: int) -> None:
+    """Forward kernel: 1 = ping-pong (two query tiles per CTA, P through TMEM; default),
+    0 = one query tile per CTA."""
+    lib = _lib.load()
+    lib.nkb_attn_set_fwd_impl.argtypes = [_lib.i32]
+    lib.nkb_attn_set_fwd_impl.restype = None
+    lib.nkb_attn_set_fwd_impl(int(impl))
 
 
 def _ref_attention(q, k, v, causal, scale):

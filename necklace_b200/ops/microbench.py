@@ -106,17 +106,18 @@ def bench_attn(flush):
     for (B, H, S, D) in [(8, 16, 1024, 64), (2, 32, 2048, 128), (1, 40, 4096, 128)]:
         C = H * D
         qkv = torch.randn(B, S, 3 * C, device="cuda").bfloat16()
-        from .attention import set_exp_mode
+        from .attention import set_exp_mode, set_fwd_impl
         q_, k_, v_ = (t.view(B, S, H, D).transpose(1, 2).float() for t in qkv.split(C, -1))
         ref = torch.nn.functional.scaled_dot_product_attention(q_, k_, v_, is_causal=True)
         ref = ref.transpose(1, 2).reshape(B, S, C)
         modes = {}
-        for mode in (0, 2, 1):
+        for impl, mode in ((0, 0), (0, 1), (1, 1), (1, 0)):
+            set_fwd_impl(impl)
             set_exp_mode(mode)
             t_ms = _time(lambda: attn_fwd(qkv, H, True), flush=flush)
             o_, _ = attn_fwd(qkv, H, True)
             err = ((o_.float() - ref).norm() / ref.norm()).item()
-            modes[f"mode{mode}"] = {"ms": round(t_ms, 4), "rel_err": round(err, 5)}
+            modes[f"impl{impl}_exp{mode}"] = {"ms": round(t_ms, 4), "rel_err": round(err, 5)}
         print(json.dumps({"op": "attn_fwd_exp_modes", "B": B, "H": H, "S": S, "D": D, **modes}),
               flush=True)
         ms = _time(lambda: attn_fwd(qkv, H, True), flush=flush)

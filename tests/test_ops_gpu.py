@@ -275,3 +275,33 @@ def test_attention_fwd_bwd(causal, B, H, S, D):
     for name, sl in (("dq", slice(0, C1)), ("dk", slice(C1, 2 * C1)), ("dv", slice(2 * C1, 3 * C1))):
         err = _rel_err(qkv.grad[..., sl], ref_in.grad[..., sl])
         assert err < 3e-2, (name, err)
+
+
+@pytest.mark.parametrize("impl,mode", [(1, 0), (1, 1), (0, 0), (0, 1)])
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("B,H,S,D", [(1, 2, 128, 64), (2, 2, 300, 64), (1, 3, 1024, 64),
+                                     (1, 2, 640, 128), (1, 1, 129, 128), (2, 1, 257, 64)])
+def test_attention_forward_variants(impl, mode, causal, B, H, S, D):
+    """Both forward kernels and both exponential forms against fp32 softmax attention,
+    with a large score spread so that the running maximum moves between key blocks."""
+    from necklace_b200.ops.attention import attn_fwd, set_exp_mode, set_fwd_impl
+    torch.manual_seed(11)
+    C = H * D
+    qkv = torch.randn(B, S, 3 * C, device=DEV)
+    qkv[:, S // 2:, :C] *= 3.0          # later queries: sharper rows
+    qkv[:, 2 * S // 3:, C:2 * C] *= 2.0  # later keys: larger scores -> rescale path
+    qkv = qkv.bfloat16()
+    set_fwd_impl(impl)
+    set_exp_mode(mode)
+    try:
+        out, lse = attn_fwd(qkv, H, causal)
+    finally:
+        set_fwd_impl(1)
+        set_exp_mode(0)
+    q, k, v = (t.view(B, S, H, D).transpose(1, 2).float() for t in qkv.split(C, -1))
+    s = (q @ k.transpose(-1, -2)) / math.sqrt(D)
+    if causal:
+        s = s.masked_fill(~torch.ones(S, S, dtype=torch.bool, device=DEV).tril(), float("-inf"))
+    ref = (torch.softmax(s, -1) @ v).transpose(1, 2).reshape(B, S, C)
+    assert _rel_err(out, ref) < 2e-2
+    assert (lse - torch.logsumexp(s, -1)).abs().max().item() < 2e-2
