@@ -8,10 +8,15 @@
 // exponential unit, not the dependency chain S -> softmax -> PV, sets the pace.
 //
 //   TMEM columns: S_a [0,128)  S_b [128,256)  O_a [256,256+D)  O_b [256+D,256+2D)
+//                 and for D = 64: P_a [384,448)  P_b [448,512)
 //   * S = Q K^T lands in TMEM; a thread owns one query row (TMEM lane) and reads all
 //     128 scores of the key block at once.
-//   * P (bf16 pairs) is written back over the first 64 columns of its own S buffer and
-//     is the A operand of the P V MMA straight from TMEM: no shared-memory staging.
+//   * P (bf16 pairs) goes back to TMEM and is the A operand of the P V MMA straight from
+//     there: no shared-memory staging.  With D = 64 it has columns of its own, so the
+//     next S of a warpgroup is issued as soon as the warpgroup has read the current one
+//     and is ready before the softmax of the current block ends; with D = 128 TMEM is
+//     full, P overwrites the first 64 columns of its S buffer and the next S follows
+//     the P V MMA.
 //   * O accumulates in TMEM across key blocks.  The running maximum is only moved (and
 //     O rescaled through tcgen05.ld / st) when it grew by more than 2^8 since the last
 //     move; until then probabilities are taken against the older maximum, which keeps
@@ -32,6 +37,8 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   constexpr int NKD = D / 64;        // 64-wide sub-tiles along the head dim
   constexpr uint32_t TMEM_COLS = 512;
   constexpr uint32_t O_COL = 256;
+  constexpr bool PSEP = (D == 64);  // P has TMEM columns of its own
+  constexpr uint32_t P_COL = 384;
   constexpr float RESCALE_LOG2 = 8.f;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -47,8 +54,9 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint64_t* v_empty = bars + 7;   // [2]
   uint64_t* s_full = bars + 9;    // [2] one per warpgroup
   uint64_t* p_full = bars + 11;   // [2]
-  uint64_t* o_full = bars + 13;   // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  uint64_t* p_free = bars + 13;   // [2] P V of a block retired: O stable, P columns free
+  uint64_t* s_free = bars + 15;   // [2] S read into registers (D = 64)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -72,7 +80,8 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
       mbar_init(&p_full[i], 4);  // one arrival per softmax warp
-      mbar_init(&o_full[i], 1);
+      mbar_init(&p_free[i], 1);
+      mbar_init(&s_free[i], 4);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -131,11 +140,13 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       };
       auto issue_pv = [&](int x, int stage, bool first) {
         const uint32_t av = smem_u32(sV + stage * TILE);
+        const uint32_t tp = tmem_base + (PSEP ? P_COL + x * 64 : x * 128);
 #pragma unroll
         for (int k = 0; k < 8; ++k)  // 16 keys per MMA: 8 TMEM columns of bf16 pairs
-          umma_bf16_ts(tmem_base + O_COL + x * D, tmem_base + x * 128 + k * 8,
+          umma_bf16_ts(tmem_base + O_COL + x * D, tp + k * 8,
                        umma_desc_sw128(av + k * 2048, 16384, 1024), idesc_o,
                        (!first || k > 0) ? 1u : 0u);
+        umma_commit(&p_free[x]);
       };
       bool ok = mbar_wait(q_full, 0, abort_flag) && mbar_wait(&k_full[0], 0, abort_flag);
       if (!ok) att_error(a.status, abort_flag, NKB_ERR_TMA_WAIT);
@@ -145,41 +156,43 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (n1 > 0) issue_s(1, 0);
         umma_commit(&k_empty[0]);
       }
-      for (int j = 0; j < nmax && ok; ++j) {
-        const int st = j & 1;
-        if (!mbar_wait(&v_full[st], (j >> 1) & 1, abort_flag)) {
-          att_error(a.status, abort_flag, NKB_ERR_TMA_WAIT);
-          break;
-        }
-        bool k_next_ready = false;
-        // P V of block j for one half, then that half's S of block j+1 (or the final commit)
-        auto half_step = [&](int x, int nx) -> bool {
-          if (j >= nx) return true;
-          if (!mbar_wait(&p_full[x], j & 1, abort_flag)) {
-            att_error(a.status, abort_flag, NKB_ERR_ACC_WAIT);
-            return false;
-          }
-          tc_fence_after();
-          issue_pv(x, st, j == 0);
-          if (j + 1 < nx) {
-            if (!k_next_ready) {
-              if (!mbar_wait(&k_full[st ^ 1], ((j + 1) >> 1) & 1, abort_flag)) {
-                att_error(a.status, abort_flag, NKB_ERR_TMA_WAIT);
-                return false;
-              }
+      // Event-driven issue: per half, js = next S block to issue, jp = next P V block.
+      int js[2] = {1, 1}, jp[2] = {0, 0};
+      const int nn[2] = {n0, n1};
+      long long t_last = clock64();
+      while (ok && (jp[0] < n0 || jp[1] < n1)) {
+        bool progress = false;
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          const int y = x ^ 1;
+          if (js[x] < nn[x]) {
+            const int j = js[x];
+            const bool s_ok = PSEP ? mbar_test_wait(&s_free[x], (j - 1) & 1) : (jp[x] >= j);
+            if (s_ok && mbar_test_wait(&k_full[j & 1], (j >> 1) & 1)) {
               tc_fence_after();
-              k_next_ready = true;
+              issue_s(x, j & 1);
+              if (j >= nn[y] || js[y] > j) umma_commit(&k_empty[j & 1]);
+              ++js[x];
+              progress = true;
             }
-            issue_s(x, st ^ 1);
-          } else {
-            umma_commit(&o_full[x]);
           }
-          return true;
-        };
-        ok = half_step(0, n0) && half_step(1, n1);
-        if (!ok) break;
-        umma_commit(&v_empty[st]);
-        if (k_next_ready) umma_commit(&k_empty[st ^ 1]);
+          if (jp[x] < nn[x]) {
+            const int j = jp[x];
+            if (mbar_test_wait(&p_full[x], j & 1) && mbar_test_wait(&v_full[j & 1], (j >> 1) & 1)) {
+              tc_fence_after();
+              issue_pv(x, j & 1, j == 0);
+              if (j >= nn[y] || jp[y] > j) umma_commit(&v_empty[j & 1]);
+              ++jp[x];
+              progress = true;
+            }
+          }
+        }
+        if (progress) {
+          t_last = clock64();
+        } else if (*abort_flag || clock64() - t_last > NKB_WAIT_CYCLES) {
+          att_error(a.status, abort_flag, NKB_ERR_ACC_WAIT);
+          ok = false;
+        }
       }
     }
   } else {
@@ -190,6 +203,7 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const uint32_t t_lane = tmem_base + (uint32_t((warp & 3) * 32) << 16);
     const uint32_t t_s = t_lane + x * 128;
     const uint32_t t_o = t_lane + O_COL + x * D;
+    const uint32_t t_p = PSEP ? t_lane + P_COL + x * 64 : t_s;
     const int nkv = x ? n1 : n0;
     float m_ref = 0.f, l = 0.f;
     bool ok = true;
@@ -204,6 +218,11 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld_32x32(t_s + c * 32, s + c * 32);
       tmem_ld_wait();
+      if (PSEP) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s_free[x]);
+      }
       const int kv0 = j * 128;
       const bool need_mask = (a.causal && kv0 + 127 > m0 + x * 128) || (kv0 + 128 > a.S);
       if (need_mask) {
@@ -223,9 +242,15 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       if (j == 0) {
         m_ref = (mx == -INFINITY) ? 0.f : mx;
       } else {
+        // P V of block j-1 must have retired before O is rescaled or P overwritten
+        if (!mbar_wait(&p_free[x], (j - 1) & 1, abort_flag)) {
+          att_error(a.status, abort_flag, NKB_ERR_ACC_WAIT);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
         const bool grow = (mx - m_ref) * a.scale_log2 > RESCALE_LOG2;
         if (__any_sync(0xffffffffu, grow)) {
-          // s_full(j) is committed after P V of block j-1, so O is complete here
           const float alpha = grow ? ex2_f32((m_ref - mx) * a.scale_log2) : 1.f;
           l *= alpha;
 #pragma unroll
@@ -261,7 +286,7 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           sum1 += p1;
           pk[i >> 1] = pack_bf16x2(p0, p1);
         }
-        tmem_st_32x16(t_s + c * 16, pk);
+        tmem_st_32x16(t_p + c * 16, pk);
       }
       l += sum0 + sum1;
       tmem_st_wait();
@@ -270,7 +295,7 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       if (lane == 0) mbar_arrive(&p_full[x]);
     }
     if (nkv > 0) {
-      if (ok && mbar_wait(&o_full[x], 0, abort_flag)) {
+      if (ok && mbar_wait(&p_free[x], (nkv - 1) & 1, abort_flag)) {
         tc_fence_after();
         const float inv = 1.f / l;
         __nv_bfloat16* orow =

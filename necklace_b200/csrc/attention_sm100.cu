@@ -612,6 +612,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 }
 
+#include "attention_bwd_pp.cuh"
+
 // delta[b,h,s] = sum_d o * do ; 8 lanes per row
 __global__ void __launch_bounds__(256)
 attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
@@ -765,9 +767,45 @@ static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
   return (int)cudaGetLastError();
 }
 
+// fp32 dQ accumulator [B*H, S, D] as a 3-D map; box = 32 (d) x 128 (s) x 1, 128B swizzle
+static int make_tmap_dq(CUtensorMap* out, float* base, int BH, int S, int D) {
+  EncodeTiledFn fn = att_encode_fn();
+  if (!fn) return -1;
+  if (reinterpret_cast<uintptr_t>(base) & 15) return -3;
+  cuuint64_t gdim[3] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)BH};
+  cuuint64_t gstride[2] = {(cuuint64_t)D * 4, (cuuint64_t)S * D * 4};
+  cuuint32_t box[3] = {32, 128, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, base, gdim, gstride, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -(int)r - 1000;
+}
+
+// 1: warp-specialised kernel (head dim 64), 0: serial kernel
+static int g_attn_bwd_impl = 1;
+
+static int launch_bwd_pp(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                         const CUtensorMap& tdo, const CUtensorMap& tdq, const AttnBwdArgs& a,
+                         cudaStream_t s) {
+  constexpr int smem = AttnBwd2Smem::BYTES;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_bwd_pp_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid(a.B * a.H, (a.S + 127) / 128);
+  attn_bwd_pp_kernel<<<grid, BWD2_THREADS, smem, s>>>(tq, tk, tv, tdo, tdq, a);
+  return (int)cudaGetLastError();
+}
+
 }  // namespace nkb
 
 using namespace nkb;
+
+extern "C" void nkb_attn_set_bwd_impl(int impl) { nkb::g_attn_bwd_impl = impl; }
 
 // 0 = fp32 exponentials (default), 1 = packed half, 2 = packed bf16 (one-tile kernel only)
 extern "C" void nkb_attn_set_exp_mode(int mode) { nkb::g_attn_exp_mode = mode; }
@@ -825,7 +863,13 @@ extern "C" int nkb_attn_bwd(const void* q, const void* k, const void* v, const v
   a.scale_log2 = scale * LOG2E;
   a.causal = causal;
   a.status = status;
-  rc = D == 64 ? launch_bwd<64>(tq, tk, tv, tdo, a, s) : launch_bwd<128>(tq, tk, tv, tdo, a, s);
+  if (D == 64 && g_attn_bwd_impl == 1) {
+    CUtensorMap tdq;
+    if ((rc = make_tmap_dq(&tdq, dq_acc, B * H, S, D))) return rc;
+    rc = launch_bwd_pp(tq, tk, tv, tdo, tdq, a, s);
+  } else {
+    rc = D == 64 ? launch_bwd<64>(tq, tk, tv, tdo, a, s) : launch_bwd<128>(tq, tk, tv, tdo, a, s);
+  }
   if (rc) return rc;
   long long n8 = rows * D / 8;
   int blocks = (int)((n8 + 255) / 256);

@@ -35,6 +35,14 @@ def set_fwd_impl(impl: int) -> None:
     lib.nkb_attn_set_fwd_impl(int(impl))
 
 
+def set_bwd_impl(impl: int) -> None:
+    """Backward kernel for head dim 64: 1 = warp-specialised (default), 0 = serial."""
+    lib = _lib.load()
+    lib.nkb_attn_set_bwd_impl.argtypes = [_lib.i32]
+    lib.nkb_attn_set_bwd_impl.restype = None
+    lib.nkb_attn_set_bwd_impl(int(impl))
+
+
 def _ref_attention(q, k, v, causal, scale):
     # q,k,v: [B,H,S,D] fp32
     s = (q @ k.transpose(-1, -2)) * scale
