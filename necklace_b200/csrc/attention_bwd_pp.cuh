@@ -133,13 +133,21 @@ attn_bwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);  // S^T, dP^T
       constexpr uint32_t idesc_ts = umma_idesc_bf16(128, D, 0, 1);   // dV, dK: A from TMEM
       constexpr uint32_t idesc_dq = umma_idesc_bf16(128, D, 1, 1);   // dQ: both MN-major
-      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV);
+      // descriptors are built once; per MMA only the start-address field (16-byte units) moves
+      const uint64_t dK_k = umma_desc_sw128(smem_u32(sK), 16, 1024);      // K, K-major (A of S^T)
+      const uint64_t dV_k = umma_desc_sw128(smem_u32(sV), 16, 1024);      // V, K-major (A of dP^T)
+      const uint64_t dK_mn = umma_desc_sw128(smem_u32(sK), 16384, 1024);  // K, MN-major (B of dQ)
+      const uint64_t dQ_k0 = umma_desc_sw128(smem_u32(sQ), 16, 1024);     // Q, K-major (B of S^T)
+      const uint64_t dDO_k0 = umma_desc_sw128(smem_u32(sDO), 16, 1024);
+      const uint64_t dQ_mn0 = umma_desc_sw128(smem_u32(sQ), 16384, 1024);   // Q, MN-major (B of dK)
+      const uint64_t dDO_mn0 = umma_desc_sw128(smem_u32(sDO), 16384, 1024);
+      const uint64_t dDS0 = umma_desc_sw128(smem_u32(sDS), 16384, 1024);    // dS^T, MN-major A
       auto issue_dq = [&](int it) {
-        const uint32_t aDS = smem_u32(sDS + (it & 1) * 32768);
+        const uint64_t dds = dDS0 + (uint32_t)(it & 1) * (32768 >> 4);
 #pragma unroll
         for (int k = 0; k < 8; ++k)  // 16 keys per MMA
-          umma_bf16_ss(tmem_base + DQ_COL, umma_desc_sw128(aDS + k * 2048, 16384, 1024),
-                       umma_desc_sw128(aK + k * 2048, 16384, 1024), idesc_dq, k > 0 ? 1u : 0u);
+          umma_bf16_ss(tmem_base + DQ_COL, dds + k * 128, dK_mn + k * 128, idesc_dq,
+                       k > 0 ? 1u : 0u);
         umma_commit(dq_full);
       };
       bool ok = mbar_wait(kv_full, 0, abort_flag);
@@ -152,17 +160,17 @@ attn_bwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           break;
         }
         tc_fence_after();
-        const uint32_t aQ = smem_u32(sQ + st * TILE), aDO = smem_u32(sDO + st * TILE);
+        const uint32_t soff = (uint32_t)st * (TILE >> 4);
         // S^T = K Q^T ; dP^T = V dO^T   (the tensor pipe runs in order, so the P^T / dS^T
         // of the previous block have been consumed before these overwrite them)
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          umma_bf16_ss(tmem_base + ST_COL, umma_desc_sw128(aK + k * 32, 16, 1024),
-                       umma_desc_sw128(aQ + k * 32, 16, 1024), idesc_s, k > 0 ? 1u : 0u);
+          umma_bf16_ss(tmem_base + ST_COL, dK_k + k * 2, dQ_k0 + soff + k * 2, idesc_s,
+                       k > 0 ? 1u : 0u);
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          umma_bf16_ss(tmem_base + DPT_COL, umma_desc_sw128(aV + k * 32, 16, 1024),
-                       umma_desc_sw128(aDO + k * 32, 16, 1024), idesc_s, k > 0 ? 1u : 0u);
+          umma_bf16_ss(tmem_base + DPT_COL, dV_k + k * 2, dDO_k0 + soff + k * 2, idesc_s,
+                       k > 0 ? 1u : 0u);
         umma_commit(sdp_full);
         if (it > 0) {
           // dQ of the previous block, once the writer has read the one before it
@@ -185,13 +193,11 @@ attn_bwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 #pragma unroll
         for (int k = 0; k < 8; ++k)
           umma_bf16_ts(tmem_base + DV_COL, tmem_base + ST_COL + (k >> 2) * 64 + (k & 3) * 8,
-                       umma_desc_sw128(aDO + k * 2048, 16384, 1024), idesc_ts,
-                       (it > 0 || k > 0) ? 1u : 0u);
+                       dDO_mn0 + soff + k * 128, idesc_ts, (it > 0 || k > 0) ? 1u : 0u);
 #pragma unroll
         for (int k = 0; k < 8; ++k)
           umma_bf16_ts(tmem_base + DK_COL, tmem_base + DPT_COL + (k >> 2) * 64 + (k & 3) * 8,
-                       umma_desc_sw128(aQ + k * 2048, 16384, 1024), idesc_ts,
-                       (it > 0 || k > 0) ? 1u : 0u);
+                       dQ_mn0 + soff + k * 128, idesc_ts, (it > 0 || k > 0) ? 1u : 0u);
         umma_commit(&qdo_empty[st]);
       }
       if (ok && niter > 0) {

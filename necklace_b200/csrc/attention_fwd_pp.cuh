@@ -3,7 +3,10 @@
 //
 // One CTA per (256-query block, batch*head), one CTA per SM.  Two softmax warpgroups
 // (warps 0-3: query rows 0..127 of the block, warps 4-7: rows 128..255) share every
-// K / V tile; warp 8 issues the TMA loads and warp 9 the tcgen05.mma instructions.
+// K / V tile; warp 8 issues the TMA loads, warps 9 and 10 the tcgen05.mma instructions of
+// one half each (an issuing thread blocks while the tensor pipe is busy and every
+// barrier probe costs ~50 cycles, so one thread for both halves was the bottleneck);
+// the control warpgroup hands most of its registers to the softmax warpgroups.
 // While one warpgroup runs its softmax the tensor cores work for the other one, so the
 // exponential unit, not the dependency chain S -> softmax -> PV, sets the pace.
 //
@@ -27,7 +30,21 @@
 // The reference has no attention layer.
 #pragma once
 
-constexpr int ATT2_THREADS = 320;
+constexpr int ATT2_THREADS = 384;
+
+// Event trace for development builds (-DNKB_ATT_TRACE): CTA (0,0) stores clock64() per
+// (event tag, key block) with plain stores.  Compiled out otherwise.
+#ifdef NKB_ATT_TRACE
+#ifndef NKB_ATT_TRACE_BX
+#define NKB_ATT_TRACE_BX 0
+#define NKB_ATT_TRACE_BY 0
+#endif
+#define ATT_DBG(tag, jj)                                                      \
+  if (a.dbg && blockIdx.x == NKB_ATT_TRACE_BX && blockIdx.y == NKB_ATT_TRACE_BY) \
+    a.dbg[(tag) * 16 + (jj)] = clock64();
+#else
+#define ATT_DBG(tag, jj)
+#endif
 
 template <int D, int EXPM>
 __global__ void __launch_bounds__(ATT2_THREADS, 1)
@@ -60,6 +77,7 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) { ATT_DBG(60, 0); }
   const int nq2 = (a.S + 255) / 256;
   const int qb = nq2 - 1 - blockIdx.y;  // heavy (late) query blocks are scheduled first
   const int bh = blockIdx.x;
@@ -76,8 +94,8 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1);
       mbar_init(&v_full[i], 1);
-      mbar_init(&k_empty[i], 1);
-      mbar_init(&v_empty[i], 1);
+      mbar_init(&k_empty[i], n1 > 0 ? 2 : 1);  // one commit per active half
+      mbar_init(&v_empty[i], n1 > 0 ? 2 : 1);
       mbar_init(&s_full[i], 1);
       mbar_init(&p_full[i], 4);  // one arrival per softmax warp
       mbar_init(&p_free[i], 1);
@@ -95,6 +113,7 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  if (warp >= 8) reg_alloc_dec<40>();
   if (warp == 8) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
@@ -113,90 +132,87 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           break;
         }
         mbar_expect_tx(&k_full[st], TILE);
+        ATT_DBG(1, j);
         load_tile(sK + st * TILE, &tmK, &k_full[st], j * 128);
         if (!mbar_wait(&v_empty[st], par, abort_flag)) {
           att_error(a.status, abort_flag, NKB_ERR_EMPTY_WAIT);
           break;
         }
         mbar_expect_tx(&v_full[st], TILE);
+        ATT_DBG(2, j);
         load_tile(sV + st * TILE, &tmV, &v_full[st], j * 128);
       }
     }
-  } else if (warp == 9) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+  } else if (warp == 9 || warp == 10) {
+    // ------------------------------------------------- MMA issuer of half x = warp - 9
+    const int x = warp - 9;
+    const int nx = x ? n1 : n0;
+    if (lane == 0 && nx > 0) {
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);
       constexpr uint32_t idesc_o = umma_idesc_bf16(128, D, 0, 1);
-      auto issue_s = [&](int x, int stage) {
-        const uint32_t aq = smem_u32(sQ + x * TILE), ak = smem_u32(sK + stage * TILE);
+      // descriptors are built once; per MMA only the start-address field (16-byte units) moves
+      const uint64_t dq = umma_desc_sw128(smem_u32(sQ + x * TILE), 16, 1024);
+      const uint64_t dK0 = umma_desc_sw128(smem_u32(sK), 16, 1024);
+      const uint64_t dV0 = umma_desc_sw128(smem_u32(sV), 16384, 1024);
+      const uint32_t t_sx = tmem_base + x * 128, t_ox = tmem_base + O_COL + x * D;
+      const uint32_t t_px = tmem_base + (PSEP ? P_COL + x * 64 : x * 128);
+      bool ok = true;
+      auto wait_or_fail = [&](uint64_t* bar, uint32_t parity, int code) {
+        if (ok && !mbar_wait(bar, parity, abort_flag)) {
+          att_error(a.status, abort_flag, code);
+          ok = false;
+        }
+      };
+      // S of block j (K stage j & 1), then its commits
+      auto issue_s = [&](int j) {
+        wait_or_fail(&k_full[j & 1], (j >> 1) & 1, NKB_ERR_TMA_WAIT);
+        if (!ok) return;
+        tc_fence_after();
+        ATT_DBG(10 + x, j);
+        const uint64_t dk = dK0 + (uint32_t)(j & 1) * (TILE >> 4);
 #pragma unroll
         for (int kd = 0; kd < NKD; ++kd)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            umma_bf16_ss(tmem_base + x * 128, umma_desc_sw128(aq + kd * 16384 + k * 32, 16, 1024),
-                         umma_desc_sw128(ak + kd * 16384 + k * 32, 16, 1024), idesc_s,
+            umma_bf16_ss(t_sx, dq + (kd * 1024 + k * 2), dk + (kd * 1024 + k * 2), idesc_s,
                          (kd > 0 || k > 0) ? 1u : 0u);
         umma_commit(&s_full[x]);
+        umma_commit(&k_empty[j & 1]);
+        ATT_DBG(12 + x, j);
       };
-      auto issue_pv = [&](int x, int stage, bool first) {
-        const uint32_t av = smem_u32(sV + stage * TILE);
-        const uint32_t tp = tmem_base + (PSEP ? P_COL + x * 64 : x * 128);
+      auto issue_pv = [&](int j) {
+        wait_or_fail(&p_full[x], j & 1, NKB_ERR_ACC_WAIT);
+        wait_or_fail(&v_full[j & 1], (j >> 1) & 1, NKB_ERR_TMA_WAIT);
+        if (!ok) return;
+        tc_fence_after();
+        ATT_DBG(20 + x, j);
+        const uint64_t dv = dV0 + (uint32_t)(j & 1) * (TILE >> 4);
 #pragma unroll
         for (int k = 0; k < 8; ++k)  // 16 keys per MMA: 8 TMEM columns of bf16 pairs
-          umma_bf16_ts(tmem_base + O_COL + x * D, tp + k * 8,
-                       umma_desc_sw128(av + k * 2048, 16384, 1024), idesc_o,
-                       (!first || k > 0) ? 1u : 0u);
+          umma_bf16_ts(t_ox, t_px + k * 8, dv + k * 128, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
         umma_commit(&p_free[x]);
+        umma_commit(&v_empty[j & 1]);
+        ATT_DBG(22 + x, j);
       };
-      bool ok = mbar_wait(q_full, 0, abort_flag) && mbar_wait(&k_full[0], 0, abort_flag);
-      if (!ok) att_error(a.status, abort_flag, NKB_ERR_TMA_WAIT);
-      if (ok) {
-        tc_fence_after();
-        if (n0 > 0) issue_s(0, 0);
-        if (n1 > 0) issue_s(1, 0);
-        umma_commit(&k_empty[0]);
-      }
-      // Event-driven issue: per half, js = next S block to issue, jp = next P V block.
-      int js[2] = {1, 1}, jp[2] = {0, 0};
-      const int nn[2] = {n0, n1};
-      long long t_last = clock64();
-      while (ok && (jp[0] < n0 || jp[1] < n1)) {
-        bool progress = false;
-#pragma unroll
-        for (int x = 0; x < 2; ++x) {
-          const int y = x ^ 1;
-          if (js[x] < nn[x]) {
-            const int j = js[x];
-            const bool s_ok = PSEP ? mbar_test_wait(&s_free[x], (j - 1) & 1) : (jp[x] >= j);
-            if (s_ok && mbar_test_wait(&k_full[j & 1], (j >> 1) & 1)) {
-              tc_fence_after();
-              issue_s(x, j & 1);
-              if (j >= nn[y] || js[y] > j) umma_commit(&k_empty[j & 1]);
-              ++js[x];
-              progress = true;
-            }
+      wait_or_fail(q_full, 0, NKB_ERR_TMA_WAIT);
+      issue_s(0);
+      for (int j = 0; j < nx && ok; ++j) {
+        if (PSEP) {
+          // the next S goes out as soon as the warpgroup has read the current one
+          if (j + 1 < nx) {
+            wait_or_fail(&s_free[x], j & 1, NKB_ERR_ACC_FREE);
+            issue_s(j + 1);
           }
-          if (jp[x] < nn[x]) {
-            const int j = jp[x];
-            if (mbar_test_wait(&p_full[x], j & 1) && mbar_test_wait(&v_full[j & 1], (j >> 1) & 1)) {
-              tc_fence_after();
-              issue_pv(x, j & 1, j == 0);
-              if (j >= nn[y] || jp[y] > j) umma_commit(&v_empty[j & 1]);
-              ++jp[x];
-              progress = true;
-            }
-          }
-        }
-        if (progress) {
-          t_last = clock64();
-        } else if (*abort_flag || clock64() - t_last > NKB_WAIT_CYCLES) {
-          att_error(a.status, abort_flag, NKB_ERR_ACC_WAIT);
-          ok = false;
+          issue_pv(j);
+        } else {
+          issue_pv(j);  // P overwrites S: the next S follows the P V that reads it
+          if (j + 1 < nx) issue_s(j + 1);
         }
       }
     }
-  } else {
+  } else if (warp < 8) {
     // --------------------------------------------------------------------- softmax
+    reg_alloc_inc<232>();
     const int x = warp >> 2;                 // which half of the query block
     const int r = (warp & 3) * 32 + lane;    // row inside the 128-row tile (TMEM lane)
     const int qi = m0 + x * 128 + r;
@@ -214,6 +230,7 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         break;
       }
       tc_fence_after();
+      if ((warp & 3) == 0 && lane == 0) { ATT_DBG(30 + x, j); }
       uint32_t s[128];
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld_32x32(t_s + c * 32, s + c * 32);
@@ -239,18 +256,29 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         mx1 = max3_f32(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
       }
       const float mx = fmaxf(mx0, mx1);
+      if ((warp & 3) == 0 && lane == 0) { ATT_DBG(34 + x, j); }
+      // P V of block j-1 must have retired before O is rescaled or P overwritten; the wait
+      // sits as late as possible (after the exponentials unless O has to be rescaled)
+      bool pv_done = (j == 0);
+      auto wait_pv = [&]() -> bool {
+        if (pv_done) return true;
+        if (!mbar_wait(&p_free[x], (j - 1) & 1, abort_flag)) {
+          att_error(a.status, abort_flag, NKB_ERR_ACC_WAIT);
+          return false;
+        }
+        tc_fence_after();
+        pv_done = true;
+        return true;
+      };
       if (j == 0) {
         m_ref = (mx == -INFINITY) ? 0.f : mx;
       } else {
-        // P V of block j-1 must have retired before O is rescaled or P overwritten
-        if (!mbar_wait(&p_free[x], (j - 1) & 1, abort_flag)) {
-          att_error(a.status, abort_flag, NKB_ERR_ACC_WAIT);
-          ok = false;
-          break;
-        }
-        tc_fence_after();
         const bool grow = (mx - m_ref) * a.scale_log2 > RESCALE_LOG2;
         if (__any_sync(0xffffffffu, grow)) {
+          if (!wait_pv()) {
+            ok = false;
+            break;
+          }
           const float alpha = grow ? ex2_f32((m_ref - mx) * a.scale_log2) : 1.f;
           l *= alpha;
 #pragma unroll
@@ -267,32 +295,47 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
       }
       const float mneg = -m_ref * a.scale_log2;
-      float sum0 = 0.f, sum1 = 0.f;
+      float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+      uint32_t pk[64];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float x0 = fmaf(__uint_as_float(s[c * 32 + i]), a.scale_log2, mneg);
-          const float x1 = fmaf(__uint_as_float(s[c * 32 + i + 1]), a.scale_log2, mneg);
-          float p0, p1;
-          if (EXPM == 0) {
-            p0 = ex2_f32(x0);
-            p1 = ex2_f32(x1);
-          } else {
-            unpack_f16x2(ex2_f16x2(x0, x1), p0, p1);
-          }
-          sum0 += p0;
-          sum1 += p1;
-          pk[i >> 1] = pack_bf16x2(p0, p1);
+      for (int i = 0; i < 128; i += 4) {
+        const float x0 = fmaf(__uint_as_float(s[i]), a.scale_log2, mneg);
+        const float x1 = fmaf(__uint_as_float(s[i + 1]), a.scale_log2, mneg);
+        const float x2 = fmaf(__uint_as_float(s[i + 2]), a.scale_log2, mneg);
+        const float x3 = fmaf(__uint_as_float(s[i + 3]), a.scale_log2, mneg);
+        float p0, p1, p2, p3;
+        if (EXPM == 0) {
+          p0 = ex2_f32(x0);
+          p1 = ex2_f32(x1);
+          p2 = ex2_f32(x2);
+          p3 = ex2_f32(x3);
+        } else {
+          unpack_f16x2(ex2_f16x2(x0, x1), p0, p1);
+          unpack_f16x2(ex2_f16x2(x2, x3), p2, p3);
         }
-        tmem_st_32x16(t_p + c * 16, pk);
+        sum0 += p0;
+        sum1 += p1;
+        sum2 += p2;
+        sum3 += p3;
+        pk[i >> 1] = pack_bf16x2(p0, p1);
+        pk[(i >> 1) + 1] = pack_bf16x2(p2, p3);
       }
+      if ((warp & 3) == 0 && lane == 0) { ATT_DBG(38 + x, j); }
+      if (!wait_pv()) {
+        ok = false;
+        break;
+      }
+      if ((warp & 3) == 0 && lane == 0) { ATT_DBG(40 + x, j); }
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_st_32x16(t_p + c * 16, pk + c * 16);
+      sum0 += sum2;
+      sum1 += sum3;
       l += sum0 + sum1;
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[x]);
+      if ((warp & 3) == 0 && lane == 0) { ATT_DBG(50 + x, j); }
     }
     if (nkv > 0) {
       if (ok && mbar_wait(&p_free[x], (nkv - 1) & 1, abort_flag)) {
@@ -327,6 +370,7 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) { ATT_DBG(61, 0); }
   if (warp == 9) {
     if (*abort_flag)
       for (int i = 0; i < 1000; ++i) __nanosleep(1000);

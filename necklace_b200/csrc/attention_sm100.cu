@@ -33,6 +33,9 @@ struct AttnFwdArgs {
   float scale, scale_log2;
   int causal;
   int* status;
+#ifdef NKB_ATT_TRACE
+  long long* dbg;
+#endif
 };
 
 __device__ __forceinline__ void att_error(int* status, volatile int* abort_flag, int code) {
@@ -811,6 +814,10 @@ extern "C" void nkb_attn_set_bwd_impl(int impl) { nkb::g_attn_bwd_impl = impl; }
 extern "C" void nkb_attn_set_exp_mode(int mode) { nkb::g_attn_exp_mode = mode; }
 // 1 = ping-pong forward kernel (default), 0 = one query tile per CTA
 extern "C" void nkb_attn_set_fwd_impl(int impl) { nkb::g_attn_fwd_impl = impl; }
+#ifdef NKB_ATT_TRACE
+static long long* g_attn_dbg = nullptr;
+extern "C" void nkb_attn_set_dbg(long long* p) { g_attn_dbg = p; }
+#endif
 
 extern "C" int nkb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
                             int B, int H, int S, int D, long long sb, long long sh, long long ss,
@@ -832,6 +839,9 @@ extern "C" int nkb_attn_fwd(const void* q, const void* k, const void* v, void* o
   a.scale_log2 = scale * LOG2E;
   a.causal = causal;
   a.status = status;
+#ifdef NKB_ATT_TRACE
+  a.dbg = g_attn_dbg;
+#endif
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   return D == 64 ? launch_fwd_mode<64>(tq, tk, tv, a, s) : launch_fwd_mode<128>(tq, tk, tv, a, s);
 }

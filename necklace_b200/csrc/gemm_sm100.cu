@@ -639,6 +639,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ---------------------------------------------------------- MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      const uint64_t dA0 = umma_desc_sw128(smem_u32(smem), A_MN ? 64 * BK * 2 : 16, 1024);
+      const uint64_t dB0 =
+          umma_desc_sw128(smem_u32(smem) + A_STAGE_BYTES, B_MN ? 64 * BK * 2 : 16, 1024);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -660,19 +663,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             break;
           }
           tc_fence_after();
-          const uint32_t aA = smem_u32(smem + stage * STAGE_BYTES);
-          const uint32_t aB = aA + A_STAGE_BYTES;
+          // descriptors: only the 14-bit start-address field (16-byte units) changes
+          const uint64_t dA = dA0 + (uint32_t)stage * (STAGE_BYTES >> 4);
+          const uint64_t dB = dB0 + (uint32_t)stage * (STAGE_BYTES >> 4);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            uint64_t da, db;
-            if constexpr (!A_MN)
-              da = umma_desc_sw128(aA + k * (UMMA_K * 2), 16, 1024);
-            else
-              da = umma_desc_sw128(aA + k * (UMMA_K * 128), 64 * BK * 2, 1024);
-            if constexpr (!B_MN)
-              db = umma_desc_sw128(aB + k * (UMMA_K * 2), 16, 1024);
-            else
-              db = umma_desc_sw128(aB + k * (UMMA_K * 128), 64 * BK * 2, 1024);
+            const uint64_t da = dA + (A_MN ? k * (UMMA_K * 128 >> 4) : k * (UMMA_K * 2 >> 4));
+            const uint64_t db = dB + (B_MN ? k * (UMMA_K * 128 >> 4) : k * (UMMA_K * 2 >> 4));
             umma_bf16_ss(d_tmem, da, db, idesc, (kb > kb_lo || k > 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);  // frees the stage when these MMAs retire
@@ -890,6 +887,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
   } else if (warp == 1) {
     if (lane == 0 && leader) {
       constexpr uint32_t idesc = umma_idesc_bf16(256, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      const uint64_t dA0 = umma_desc_sw128(smem_u32(smem), A_MN ? 64 * BK * 2 : 16, 1024);
+      const uint64_t dB0 =
+          umma_desc_sw128(smem_u32(smem) + A_STAGE_BYTES, B_MN ? 64 * BK * 2 : 16, 1024);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -911,19 +911,12 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
             break;
           }
           tc_fence_after();
-          const uint32_t aA = smem_u32(smem + stage * PAIR_STAGE_BYTES);
-          const uint32_t aB = aA + A_STAGE_BYTES;
+          const uint64_t dA = dA0 + (uint32_t)stage * (PAIR_STAGE_BYTES >> 4);
+          const uint64_t dB = dB0 + (uint32_t)stage * (PAIR_STAGE_BYTES >> 4);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            uint64_t da, db;
-            if constexpr (!A_MN)
-              da = umma_desc_sw128(aA + k * (UMMA_K * 2), 16, 1024);
-            else
-              da = umma_desc_sw128(aA + k * (UMMA_K * 128), 64 * BK * 2, 1024);
-            if constexpr (!B_MN)
-              db = umma_desc_sw128(aB + k * (UMMA_K * 2), 16, 1024);
-            else
-              db = umma_desc_sw128(aB + k * (UMMA_K * 128), 64 * BK * 2, 1024);
+            const uint64_t da = dA + (A_MN ? k * (UMMA_K * 128 >> 4) : k * (UMMA_K * 2 >> 4));
+            const uint64_t db = dB + (B_MN ? k * (UMMA_K * 128 >> 4) : k * (UMMA_K * 2 >> 4));
             umma_bf16_ss_2cta(d_tmem, da, db, idesc, (kb > kb_lo || k > 0) ? 1u : 0u);
           }
           umma_commit_2cta(&empty_bar[stage], 3);  // frees the stage in both CTAs
