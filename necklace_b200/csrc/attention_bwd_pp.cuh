@@ -23,6 +23,8 @@
 #pragma once
 
 constexpr int BWD2_THREADS = 512;
+// setmaxnreg budget: the CTA owns threads x 128 registers (the compile-time cap)
+static_assert(256 * 184 + 128 * 88 + 128 * 40 <= BWD2_THREADS * 128, "register budget");
 
 struct AttnBwd2Smem {
   static constexpr int TILE = 128 * 64 * 2;      // 16 KB bf16 tile

@@ -31,6 +31,8 @@
 #pragma once
 
 constexpr int ATT2_THREADS = 384;
+// setmaxnreg budget: the CTA owns threads x 168 registers (the compile-time cap)
+static_assert(128 * 40 + 256 * 232 <= ATT2_THREADS * 168, "register budget");
 
 // Event trace for development builds (-DNKB_ATT_TRACE): CTA (0,0) stores clock64() per
 // (event tag, key block) with plain stores.  Compiled out otherwise.

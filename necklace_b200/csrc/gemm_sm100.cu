@@ -27,7 +27,14 @@ constexpr int BM = 128;
 constexpr int BK = 64;  // 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int A_STAGE_BYTES = BM * BK * 2;
-constexpr int GEMM_THREADS = 192;
+// warps 0-3: control warpgroup (0 = TMA producer, 1 = MMA issuer / TMEM owner, 2-3 idle);
+// warps 4-11: epilogue, two warps per TMEM lane quarter, each taking half of the columns
+constexpr int GEMM_THREADS = 384;
+constexpr int EPI_WARPS = 8;
+// Register hand-over between the warpgroups (setmaxnreg).  The CTA owns what it was launched
+// with (threads x the compile-time cap of 168); asking for more would block forever.
+constexpr int GEMM_CTRL_REGS = 72, GEMM_EPI_REGS = 216;
+static_assert(128 * GEMM_CTRL_REGS + 256 * GEMM_EPI_REGS <= GEMM_THREADS * 168, "register budget");
 
 struct GemmArgs {
   int M, N, K;
@@ -352,22 +359,57 @@ __device__ __forceinline__ void stage_load_f32(uint8_t* stg, int lane, const flo
 
 // Epilogue of one 128 x BN accumulator slab: this warp's 32 rows (TMEM lanes), BN
 // columns starting at global column n0; fused math, then staged coalesced stores.
+// Residual / saved-activation rows that the epilogue adds or multiplies do not depend on
+// the accumulator, so their global loads are issued before the wait on the accumulator
+// (coalesced pieces in registers) and moved to the staging tile when the chunk is used.
+struct EpiPrefetch {
+  uint4 v[2][8];   // up to two 64-column chunks per warp
+  bool ok[2];      // chunk was prefetched (full, 16-byte aligned chunk)
+};
+template <int NCW>
+__device__ __forceinline__ void epi_prefetch(EpiPrefetch& pf, const __nv_bfloat16* src,
+                                             long long ld, int row0, int rows_valid, int col0,
+                                             int N, int lane) {
+  const bool vec = src != nullptr && ((ld & 7) == 0) &&
+                   ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
+#pragma unroll
+  for (int c = 0; c < NCW; ++c) {
+    const int cbase = col0 + c * 64;
+    pf.ok[c] = vec && rows_valid > 0 && cbase + 64 <= N;
+    if (pf.ok[c]) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int row = i * 4 + (lane >> 3), ch = lane & 7;
+        pf.v[c][i] = make_uint4(0, 0, 0, 0);
+        if (row < rows_valid)
+          pf.v[c][i] = ld_nc_v4(src + (long long)(row0 + row) * ld + cbase + ch * 8);
+      }
+    }
+  }
+}
+__device__ __forceinline__ void stage_from_regs(uint8_t* stg, int lane, const uint4* v) {
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < 8; ++i) stage_set(stg, i * 4 + (lane >> 3), lane & 7, v[i]);
+  __syncwarp();
+}
+
 // MODE 0: plain epilogue; 1: kernel fused with a collective (rs_dst set: raw partial
 // sums to the owner's staging slab); 2: split-K (raw fp32 partial sums to raw_dst).
-template <int BN, int MODE>
-__device__ __forceinline__ void epilogue_tile(const GemmArgs& g, uint8_t* stg, int lane,
-                                              uint32_t t_addr, int row0, int rows_valid, int n0,
-                                              float alpha, bool bias_vec,
-                                              __nv_bfloat16* rs_dst = nullptr,
-                                              long long rs_ld = 0, float* raw_dst = nullptr) {
-#pragma unroll 1
-  for (int cc = 0; cc < BN / 64; ++cc) {
+// One 64-column chunk (index cc) of this warp's 32-row slab; pf_v / pf_ok: the prefetched
+// residual (or, for the GELU backward epilogue, saved pre-activation) pieces of the chunk.
+template <int MODE>
+__device__ __forceinline__ void epilogue_chunk(const GemmArgs& g, uint8_t* stg, int lane,
+                                               uint32_t t_addr, int row0, int rows_valid, int n0,
+                                               float alpha, bool bias_vec, int cc, const uint4* pf_v,
+                                               bool pf_ok, __nv_bfloat16* rs_dst, long long rs_ld,
+                                               float* raw_dst) {
     uint32_t r[64];
     tmem_ld_32x32(t_addr + cc * 64, r);
     tmem_ld_32x32(t_addr + cc * 64 + 32, r + 32);
     tmem_ld_wait();
     const int col0 = n0 + cc * 64;
-    if (rows_valid == 0 || col0 >= g.N) continue;  // warp-uniform
+    if (rows_valid == 0 || col0 >= g.N) return;  // warp-uniform
     const int cols_valid = (g.N - col0) < 64 ? (g.N - col0) : 64;
     float v[64];
 #pragma unroll
@@ -387,7 +429,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, uint8_t* stg, i
           stage_store_f32(stg, lane, raw_dst + cc * 64 + half * 32, g.N, rows_valid, cv);
         }
       }
-      continue;
+      return;
     }
     if constexpr (MODE == 1) {
       if (rs_dst) {
@@ -395,7 +437,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, uint8_t* stg, i
         // bias / residual are applied by the owner after the cross-rank sum
         stage_put_bf16(stg, lane, v);
         stage_store_bf16(stg, lane, rs_dst + cc * 64, rs_ld, rows_valid, cols_valid);
-        continue;
+        return;
       }
     }
     if (g.bias) {
@@ -425,8 +467,11 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, uint8_t* stg, i
 #pragma unroll
       for (int i = 0; i < 64; ++i) v[i] = gelu_tanh(v[i]);
     } else if (g.epi == NKB_EPI_GELU_BWD) {
-      stage_load_bf16(stg, lane, g.aux_in + (long long)row0 * g.ldaux + col0, g.ldaux,
-                      rows_valid, cols_valid);
+      if (!g.res && pf_ok)
+        stage_from_regs(stg, lane, pf_v);
+      else
+        stage_load_bf16(stg, lane, g.aux_in + (long long)row0 * g.ldaux + col0, g.ldaux,
+                        rows_valid, cols_valid);
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
         uint4 z = stage_get(stg, lane, q);
@@ -443,8 +488,11 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, uint8_t* stg, i
       for (int i = 0; i < 64; ++i) v[i] = fmaxf(v[i], 0.f);
     }
     if (g.res) {
-      stage_load_bf16(stg, lane, g.res + (long long)row0 * g.ldres + col0, g.ldres, rows_valid,
-                      cols_valid);
+      if (pf_ok)
+        stage_from_regs(stg, lane, pf_v);
+      else
+        stage_load_bf16(stg, lane, g.res + (long long)row0 * g.ldres + col0, g.ldres, rows_valid,
+                        cols_valid);
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
         uint4 z = stage_get(stg, lane, q);
@@ -462,7 +510,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, uint8_t* stg, i
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         const int cv = cols_valid - half * 32;
-        if (cv <= 0) continue;
+        if (cv > 0) {
         if (g.accumulate) {
           stage_load_f32(stg, lane, cbase + half * 32, g.ldc, rows_valid, cv);
 #pragma unroll
@@ -483,6 +531,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, uint8_t* stg, i
                                __float_as_uint(v[half * 32 + q * 4 + 2]),
                                __float_as_uint(v[half * 32 + q * 4 + 3])));
         stage_store_f32(stg, lane, cbase + half * 32, g.ldc, rows_valid, cv);
+        }
       }
     } else {
       __nv_bfloat16* cbase =
@@ -504,7 +553,21 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, uint8_t* stg, i
       stage_put_bf16(stg, lane, v);
       stage_store_bf16(stg, lane, cbase, g.ldc, rows_valid, cols_valid);
     }
-  }
+}
+
+// The warp handles chunks [cc0, cc0 + NCW) of the slab.
+template <int BN, int MODE, int NCW>
+__device__ __forceinline__ void epilogue_tile(const GemmArgs& g, uint8_t* stg, int lane,
+                                              uint32_t t_addr, int row0, int rows_valid, int n0,
+                                              float alpha, bool bias_vec, int cc0,
+                                              const EpiPrefetch& pf,
+                                              __nv_bfloat16* rs_dst = nullptr,
+                                              long long rs_ld = 0, float* raw_dst = nullptr) {
+  epilogue_chunk<MODE>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec, cc0, pf.v[0],
+                       pf.ok[0], rs_dst, rs_ld, raw_dst);
+  if constexpr (NCW > 1)
+    epilogue_chunk<MODE>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec, cc0 + 1,
+                         pf.v[1], pf.ok[1], rs_dst, rs_ld, raw_dst);
 }
 
 template <int BN, bool A_MN, bool B_MN, int MODE>
@@ -521,7 +584,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                               ~uintptr_t(1023));
   uint64_t* full_bar =
-      reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES + 4 * EPI_STAGE_BYTES);
+      reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES + EPI_WARPS * EPI_STAGE_BYTES);
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* acc_full = empty_bar + STAGES;
   uint64_t* acc_empty = acc_full + 2;
@@ -563,7 +626,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&acc_full[a], 1);
-      mbar_init(&acc_empty[a], 128);
+      mbar_init(&acc_empty[a], EPI_WARPS);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -578,7 +641,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-
+  // The control warpgroup keeps GEMM_CTRL_REGS registers per thread and the epilogue warpgroups take
+  // the rest; each setmaxnreg sits inside its own role branch so that no code is reachable
+  // from both.
+  if (warp < 4) {
+    reg_alloc_dec<GEMM_CTRL_REGS>();
+  }
   if (warp == 0) {
     // ------------------------------------------------------------ producer
     if (lane == 0) {
@@ -686,17 +754,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
       }
     }
-  } else {
+  } else if (warp >= 4) {
+    reg_alloc_inc<GEMM_EPI_REGS>();
     // ------------------------------------------------------------ epilogue
     // Each thread owns one accumulator row (TMEM lane).  Global traffic goes
     // through a per-warp 32-row x 128-byte staging tile so that every global
     // load / store instruction of the warp covers whole 128-byte lines.
     const int lane_grp = warp & 3;  // TMEM lanes this warp may touch: 32*lane_grp ..
-    uint8_t* stg = smem + STAGES * STAGE_BYTES + (warp - 2) * EPI_STAGE_BYTES;
+    const int ew = warp - 4;        // epilogue warp 0..7
+    constexpr int NCW = BN / 128;   // 64-column chunks per warp (two warps share a lane quarter)
+    const int cc0 = (ew >> 2) * NCW;
+    uint8_t* stg = smem + STAGES * STAGE_BYTES + ew * EPI_STAGE_BYTES;
     int acc = 0;
     uint32_t acc_phase = 0;
     const float alpha = g.alpha_dev ? g.alpha * __ldg(g.alpha_dev) : g.alpha;
     const bool bias_vec = g.bias && ((reinterpret_cast<uintptr_t>(g.bias) & 15) == 0);
+    const __nv_bfloat16* pf_src = g.res ? g.res : (g.epi == NKB_EPI_GELU_BWD ? g.aux_in : nullptr);
+    const long long pf_ld = g.res ? g.ldres : g.ldaux;
     for (int u = cta_id; u < num_units; u += n_ctas) {
       const int t = u % num_tiles, ks = u / num_tiles;
       const int mb = (t % g.num_m_blocks + mb_shift) % g.num_m_blocks, nb = t / g.num_m_blocks;
@@ -704,6 +778,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int n0 = nb * BN;
       int rows_valid = g.M - row0;
       rows_valid = rows_valid < 0 ? 0 : (rows_valid > 32 ? 32 : rows_valid);
+      EpiPrefetch pf;
+      pf.ok[0] = pf.ok[1] = false;
+      if (MODE == 0 && pf_src) epi_prefetch<NCW>(pf, pf_src, pf_ld, row0, rows_valid, n0 + cc0 * 64, g.N, lane);
       if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag)) {
         set_error(g.status, abort_flag, NKB_ERR_ACC_WAIT);
         break;
@@ -713,18 +790,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (rs_ctas) {
         int* tflag;
         __nv_bfloat16* dst = rs_tile_dst(g, mb * BM, lane_grp, n0, &tflag, nb, g.num_n_blocks);
-        epilogue_tile<BN, MODE>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec, dst,
-                                g.N);
+        epilogue_tile<BN, MODE, NCW>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec,
+                                     cc0, pf, dst, g.N);
         __threadfence_system();
-        asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
-        if (warp == 2 && lane == 0) st_release_sys(tflag, rs_epoch);
+        asm volatile("bar.sync 1, 256;" ::: "memory");  // the eight epilogue warps
+        if (ew == 0 && lane == 0) st_release_sys(tflag, rs_epoch);
       } else {
         float* raw = MODE == 2 ? g.splitk_ws + ((long long)ks * g.M + row0) * g.N + n0 : nullptr;
-        epilogue_tile<BN, MODE>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec,
-                                nullptr, 0, raw);
+        epilogue_tile<BN, MODE, NCW>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec,
+                                     cc0, pf, nullptr, 0, raw);
       }
       tc_fence_before();
-      mbar_arrive(&acc_empty[acc]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
       if (++acc == 2) {
         acc = 0;
         acc_phase ^= 1;
@@ -768,7 +846,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                               ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + PAIR_STAGES * PAIR_STAGE_BYTES +
-                                                   4 * EPI_STAGE_BYTES);
+                                                   EPI_WARPS * EPI_STAGE_BYTES);
   uint64_t* empty_bar = full_bar + PAIR_STAGES;
   uint64_t* acc_full = empty_bar + PAIR_STAGES;
   uint64_t* acc_empty = acc_full + 2;
@@ -811,7 +889,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&acc_full[a], 1);
-      mbar_init(&acc_empty[a], 8);  // 4 epilogue warps x 2 CTAs arrive on the leader's copy
+      mbar_init(&acc_empty[a], 2 * EPI_WARPS);  // epilogue warps of both CTAs, leader's copy
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -828,7 +906,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
   cluster_wait();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-
+  if (warp < 4) {
+    reg_alloc_dec<GEMM_CTRL_REGS>();
+  }
   if (warp == 0) {
     if (lane == 0) {
       int stage = 0;
@@ -933,13 +1013,19 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
         }
       }
     }
-  } else {
+  } else if (warp >= 4) {
+    reg_alloc_inc<GEMM_EPI_REGS>();
     const int lane_grp = warp & 3;
-    uint8_t* stg = smem + PAIR_STAGES * PAIR_STAGE_BYTES + (warp - 2) * EPI_STAGE_BYTES;
+    const int ew = warp - 4;  // epilogue warp 0..7: two per TMEM lane quarter, 128 columns each
+    constexpr int NCW = 2;
+    const int cc0 = (ew >> 2) * NCW;
+    uint8_t* stg = smem + PAIR_STAGES * PAIR_STAGE_BYTES + ew * EPI_STAGE_BYTES;
     int acc = 0;
     uint32_t acc_phase = 0;
     const float alpha = g.alpha_dev ? g.alpha * __ldg(g.alpha_dev) : g.alpha;
     const bool bias_vec = g.bias && ((reinterpret_cast<uintptr_t>(g.bias) & 15) == 0);
+    const __nv_bfloat16* pf_src = g.res ? g.res : (g.epi == NKB_EPI_GELU_BWD ? g.aux_in : nullptr);
+    const long long pf_ld = g.res ? g.ldres : g.ldaux;
     for (int u = pair; u < num_units; u += npairs) {
       const int t = u % num_tiles, ks = u / num_tiles;
       const int mb2 = (t % num_m2 + mb_shift) % num_m2, nb = t / num_m2;
@@ -947,6 +1033,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       const int n0 = nb * BN;
       int rows_valid = g.M - row0;
       rows_valid = rows_valid < 0 ? 0 : (rows_valid > 32 ? 32 : rows_valid);
+      EpiPrefetch pf;
+      pf.ok[0] = pf.ok[1] = false;
+      if (MODE == 0 && pf_src) epi_prefetch<NCW>(pf, pf_src, pf_ld, row0, rows_valid, n0 + cc0 * 64, g.N, lane);
       if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag)) {
         set_error(g.status, abort_flag, NKB_ERR_ACC_WAIT);
         break;
@@ -957,15 +1046,15 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
         int* tflag;
         __nv_bfloat16* dst = rs_tile_dst(g, mb2 * 256 + (int)rank * 128, lane_grp, n0, &tflag, nb,
                                          g.num_n_blocks);
-        epilogue_tile<BN, MODE>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec, dst,
-                                g.N);
+        epilogue_tile<BN, MODE, NCW>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec,
+                                     cc0, pf, dst, g.N);
         __threadfence_system();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (warp == 2 && lane == 0) st_release_sys(tflag, rs_epoch);
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (ew == 0 && lane == 0) st_release_sys(tflag, rs_epoch);
       } else {
         float* raw = MODE == 2 ? g.splitk_ws + ((long long)ks * g.M + row0) * g.N + n0 : nullptr;
-        epilogue_tile<BN, MODE>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec,
-                                nullptr, 0, raw);
+        epilogue_tile<BN, MODE, NCW>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec,
+                                     cc0, pf, nullptr, 0, raw);
       }
       tc_fence_before();
       __syncwarp();
@@ -1047,7 +1136,7 @@ static int launch_gemm_mode(const CUtensorMap& tmA, const CUtensorMap& tmB, Gemm
                             int max_ctas, cudaStream_t stream) {
   constexpr int STAGES = (BN == 256) ? 4 : 6;
   constexpr int smem_bytes =
-      STAGES * (A_STAGE_BYTES + BN * BK * 2) + 4 * EPI_STAGE_BYTES + 1024 + 256;
+      STAGES * (A_STAGE_BYTES + BN * BK * 2) + EPI_WARPS * EPI_STAGE_BYTES + 1024 + 256;
   static bool configured = false;
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, MODE>;
   if (!configured) {
@@ -1080,7 +1169,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs&
 template <bool A_MN, bool B_MN, int MODE>
 static int launch_gemm_pair_mode(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs& g,
                                  int max_ctas, cudaStream_t stream) {
-  constexpr int smem_bytes = PAIR_STAGES * PAIR_STAGE_BYTES + 4 * EPI_STAGE_BYTES + 1024 + 256;
+  constexpr int smem_bytes = PAIR_STAGES * PAIR_STAGE_BYTES + EPI_WARPS * EPI_STAGE_BYTES + 1024 + 256;
   static bool configured = false;
   auto kern = gemm_bf16_pair_kernel<A_MN, B_MN, MODE>;
   if (!configured) {
