@@ -37,6 +37,12 @@ int nkb_norm_bwd_dx(const void* dy, const void* x, const void* w, const float* s
 // `acc` is fp32 [2][C] scratch that must be zero on entry.
 int nkb_colsum(const void* dy, const void* x, const float* stats, float* acc, int rows, int C,
                long long ld, int rms, void* stream);
+// Column sums straight to bf16 outputs in one launch (the last CTA of a column strip converts
+// and re-zeroes).  acc (fp32 [2][C]) and tickets (int [ceil(C/256)]) are caller-owned, zero
+// before the first call and left zero; calls sharing them must be ordered on one stream.
+int nkb_colsum_fused(const void* dy, const void* x, const float* stats, float* acc, int* tickets,
+                     void* out_a, void* out_b, int accum_a, int accum_b, int rows, int C,
+                     long long ld, int rms, void* stream);
 // out_bf16[i] = (accumulate ? out[i] : 0) + acc[i]
 int nkb_f32_to_bf16(const float* src, void* dst, long long n, int accumulate, void* stream);
 

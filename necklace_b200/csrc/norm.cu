@@ -154,7 +154,8 @@ norm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
 __global__ void __launch_bounds__(256)
 colsum_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
               const float* __restrict__ stats, float* __restrict__ acc, int rows, int C,
-              long long ld, int rms) {
+              long long ld, int rms, int* __restrict__ tickets, __nv_bfloat16* __restrict__ out_a,
+              __nv_bfloat16* __restrict__ out_b, int accum_a, int accum_b) {
   __shared__ float sh[8][256 + 8];
   const int lane = threadIdx.x & 31, wy = threadIdx.x >> 5;
   const int col = blockIdx.x * 256 + lane * 8;
@@ -213,6 +214,28 @@ colsum_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restr
     const int gc = blockIdx.x * 256 + c;
     if (gc < C) atomicAdd(&acc[(long long)which * C + gc], s);
   }
+  if (!tickets) return;
+  // Fused finish: the last CTA of a column strip (ticket counter) turns the sums into bf16
+  // outputs and leaves the accumulator and the counter at zero for the next call.
+  __shared__ int sh_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) sh_last = (atomicAdd(&tickets[blockIdx.x], 1) == (int)gridDim.y - 1);
+  __syncthreads();
+  if (!sh_last) return;
+  __threadfence();
+  const int gc = blockIdx.x * 256 + threadIdx.x;
+  if (gc < C) {
+    for (int which = x ? 0 : 1; which < 2; ++which) {
+      float v = atomicExch(&acc[(long long)which * C + gc], 0.f);
+      __nv_bfloat16* out = which == 0 ? out_a : out_b;
+      if (out) {
+        if (which == 0 ? accum_a : accum_b) v += __bfloat162float(out[gc]);
+        out[gc] = __float2bfloat16(v);
+      }
+    }
+  }
+  if (threadIdx.x == 0) tickets[blockIdx.x] = 0;
 }
 
 __global__ void f32_to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst,
@@ -285,7 +308,27 @@ extern "C" int nkb_colsum(const void* dy, const void* x, const float* stats, flo
   if (gy < 1) gy = 1;
   colsum_kernel<<<dim3(gx, gy), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), stats, acc, rows,
-      C, ld, rms);
+      C, ld, rms, nullptr, nullptr, nullptr, 0, 0);
+  return (int)cudaGetLastError();
+}
+
+// Column sums straight to bf16 outputs in one launch.  acc: fp32 [2][C] and tickets: int
+// [ceil(C/256)], both owned by the caller, zero before the first call and left zero by every
+// call (calls that share them must be ordered on one stream).  With x / stats: out_a = sum of
+// dy * xhat (norm weight gradient), out_b = sum of dy; without: only out_b.
+extern "C" int nkb_colsum_fused(const void* dy, const void* x, const float* stats, float* acc,
+                                int* tickets, void* out_a, void* out_b, int accum_a, int accum_b,
+                                int rows, int C, long long ld, int rms, void* stream) {
+  if ((C & 1) || (ld & 1) || !acc || !tickets) return -3;
+  int gx = (C + 255) / 256;
+  int gy = (8 * 148 + gx - 1) / gx;
+  int max_gy = (rows + 7) / 8;
+  if (gy > max_gy) gy = max_gy;
+  if (gy < 1) gy = 1;
+  colsum_kernel<<<dim3(gx, gy), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), stats, acc, rows,
+      C, ld, rms, tickets, static_cast<__nv_bfloat16*>(out_a), static_cast<__nv_bfloat16*>(out_b),
+      accum_a, accum_b);
   return (int)cudaGetLastError();
 }
 

@@ -53,5 +53,16 @@ def scratch(key: str, numel: int, dtype: torch.dtype, device) -> torch.Tensor:
     return t[:numel]
 
 
+def scratch_zero(key: str, numel: int, dtype: torch.dtype, device) -> torch.Tensor:
+    """Like ``scratch`` but zero-filled when (re)allocated; for kernels that leave their
+    scratch at zero on exit (accumulators, ticket counters)."""
+    k = (key, str(device), dtype, "z")
+    t = _scratch.get(k)
+    if t is None or t.numel() < numel:
+        t = torch.zeros(max(numel, 1), dtype=dtype, device=device)
+        _scratch[k] = t
+    return t
+
+
 def ptr(t) -> int | None:
     return None if t is None else t.data_ptr()

@@ -16,7 +16,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .. import _lib
-from ._common import on_gpu, ptr, status_word, scratch
+from ._common import scratch_zero, on_gpu, ptr, status_word, scratch
 
 EPI_NONE, EPI_GELU_FWD, EPI_GELU_BWD, EPI_RELU = 0, 1, 2, 3
 
@@ -142,14 +142,21 @@ def colsum(dy: torch.Tensor, out: torch.Tensor | None = None, accumulate: bool =
         out.copy_(((out.float() + s) if accumulate else s).to(out.dtype))
         return out
     assert dy.dtype == torch.bfloat16 and dy.stride(1) == 1
-    acc = scratch("colsum", 2 * Cn, torch.float32, dy.device)
-    acc.zero_()
-    _lib.call("nkb_colsum", dy.data_ptr(), None, None, acc.data_ptr(), rows, Cn, dy.stride(0), 0,
+    acc, tickets = colsum_scratch(Cn, dy.device)
+    _lib.call("nkb_colsum_fused", dy.data_ptr(), None, None, acc.data_ptr(), tickets.data_ptr(),
+              None, out.data_ptr(), 0, int(accumulate), rows, Cn, dy.stride(0), 0,
               _lib.stream_ptr())
-    _lib.call("nkb_f32_to_bf16", acc[Cn:].data_ptr(), out.data_ptr(), Cn, int(accumulate),
-              _lib.stream_ptr())
-    _lib.count_launch(2)
+    _lib.count_launch()
     return out
+
+
+def colsum_scratch(Cn: int, device):
+    """fp32 accumulator [2][C] and ticket counters of the fused column-sum kernel; shared by
+    all calls on the device's compute stream (the kernel leaves both at zero)."""
+    acc = scratch_zero("colsum_acc", 2 * 65536, torch.float32, device)
+    tickets = scratch_zero("colsum_tickets", 256, torch.int32, device)
+    assert Cn <= 65536
+    return acc, tickets
 
 
 # ---------------------------------------------------------------- autograd

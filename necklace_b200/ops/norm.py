@@ -6,7 +6,7 @@ import torch.nn as nn
 
 from .. import _lib
 from ._common import on_gpu, ptr, scratch
-from .gemm import _deliver_grad
+from .gemm import _deliver_grad, colsum_scratch
 
 
 def norm_fwd(x2: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None, eps: float, rms: bool):
@@ -86,10 +86,48 @@ class NormFn(torch.autograd.Function):
     def backward(ctx, dy):
         x2, w, stats = ctx.saved_tensors
         dy2 = dy.reshape(-1, dy.shape[-1])
-        dx, dw32, db32 = norm_bwd(dy2, x2, w, stats, ctx.rms)
-        dw = _store_f32_grad(w, dw32)
-        db = _store_f32_grad(ctx.b_ref, db32) if ctx.b_ref is not None else None
-        return dx.view(dy.shape), dw, db, None, None
+        b = ctx.b_ref
+        bf16_targets = all(t is None or (getattr(t, "_nkb_grad", t).dtype == torch.bfloat16)
+                           for t in (w, b))
+        if not on_gpu(x2) or not bf16_targets:
+            dx, dw32, db32 = norm_bwd(dy2, x2, w, stats, ctx.rms)
+            dw = _store_f32_grad(w, dw32)
+            db = _store_f32_grad(b, db32) if b is not None else None
+            return dx.view(dy.shape), dw, db, None, None
+        # GPU: dx kernel, then one column-sum kernel that writes both parameter gradients as
+        # bf16 straight into their destination (flat gradient buffer or a fresh tensor)
+        dx, _, _ = norm_bwd(dy2, x2, w, stats, ctx.rms, need_wgrad=False, need_bgrad=False)
+        dy2 = dy2.contiguous()
+        rows, Cn = x2.shape
+        tgt_w, acc_w, ret_w = _grad_target(w)
+        tgt_b, acc_b, ret_b = _grad_target(b) if b is not None else (None, False, None)
+        acc, tickets = colsum_scratch(Cn, x2.device)
+        _lib.call("nkb_colsum_fused", dy2.data_ptr(), x2.data_ptr(), stats.data_ptr(),
+                  acc.data_ptr(), tickets.data_ptr(), tgt_w.data_ptr(), ptr(tgt_b), int(acc_w),
+                  int(acc_b), rows, Cn, Cn, int(ctx.rms), _lib.stream_ptr())
+        _lib.count_launch()
+        _grad_done(w)
+        if b is not None:
+            _grad_done(b)
+        return dx.view(dy.shape), ret_w, ret_b, None, None
+
+
+def _grad_target(p):
+    """(tensor the kernel writes, accumulate?, what autograd gets) for parameter ``p``."""
+    buf = getattr(p, "_nkb_grad", None)
+    if buf is None:
+        out = torch.empty_like(p)
+        return out, False, out
+    return buf, bool(getattr(p, "_nkb_grad_has", False)), None
+
+
+def _grad_done(p):
+    if getattr(p, "_nkb_grad", None) is None:
+        return
+    p._nkb_grad_has = True
+    cb = getattr(p, "_nkb_grad_ready", None)
+    if cb is not None:
+        cb(p)
 
 
 class LayerNorm(nn.Module):
