@@ -394,12 +394,152 @@ __device__ __forceinline__ void stage_from_regs(uint8_t* stg, int lane, const ui
   __syncwarp();
 }
 
+// ---- bf16-output fast path of the epilogue -------------------------------------------
+// The chunk is processed as two 32-column halves by ONE copy of the code (the half loop is
+// not unrolled): the fully unrolled 64-column form was several tens of KB of straight-line
+// code per warp and the eight epilogue warps, each at a different place in it, stalled on
+// instruction fetch.  At most one staged input tile (residual, saved pre-activation or the
+// old C for accumulation) is supported here; other combinations take the general form.
+// values travel as packed fp32 pairs (one instruction per two columns)
+__device__ __forceinline__ void epi_load_half(uint32_t taddr, float alpha, f32x2_t* v) {
+  uint32_t r[32];
+  tmem_ld_32x32(taddr, r);
+  tmem_ld_wait();
+  const f32x2_t a2 = f2_pack(alpha, alpha);
+#pragma unroll
+  for (int i = 0; i < 16; ++i)
+    v[i] = f2_mul(f2_pack(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])), a2);
+}
+__device__ __forceinline__ void epi_bias_half(const GemmArgs& g, f32x2_t* v, int c0, int cv,
+                                              bool vec) {
+  if (!g.bias) return;
+  if (vec) {
+    const uint4* bp = reinterpret_cast<const uint4*>(g.bias + c0);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const uint4 b = __ldg(bp + q);
+      const uint32_t w[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[q * 4 + j] = f2_add(v[q * 4 + j], f2_from_bf16x2(w[j]));
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float b0 = (2 * i < cv) ? __bfloat162float(g.bias[c0 + 2 * i]) : 0.f;
+      const float b1 = (2 * i + 1 < cv) ? __bfloat162float(g.bias[c0 + 2 * i + 1]) : 0.f;
+      v[i] = f2_add(v[i], f2_pack(b0, b1));
+    }
+  }
+}
+// tanh-form GELU and its derivative on packed pairs
+__device__ __forceinline__ f32x2_t gelu_tanh2(f32x2_t x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  const f32x2_t x2 = f2_mul(x, x);
+  const f32x2_t u = f2_mul(x, f2_fma(x2, f2_pack(k0 * k1, k0 * k1), f2_pack(k0, k0)));
+  const f32x2_t t = f2_tanh(u);
+  const f32x2_t hx = f2_mul(x, f2_pack(0.5f, 0.5f));
+  return f2_fma(hx, t, hx);
+}
+__device__ __forceinline__ f32x2_t gelu_tanh_grad2(f32x2_t x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  const f32x2_t x2 = f2_mul(x, x);
+  const f32x2_t u = f2_mul(x, f2_fma(x2, f2_pack(k0 * k1, k0 * k1), f2_pack(k0, k0)));
+  const f32x2_t t = f2_tanh(u);
+  const f32x2_t du = f2_fma(x2, f2_pack(3.f * k0 * k1, 3.f * k0 * k1), f2_pack(k0, k0));
+  const f32x2_t one_m_t2 = f2_fma(f2_mul(t, f2_pack(-1.f, -1.f)), t, f2_pack(1.f, 1.f));
+  const f32x2_t w = f2_mul(f2_mul(f2_mul(x, f2_pack(0.5f, 0.5f)), one_m_t2), du);
+  return f2_add(f2_fma(t, f2_pack(0.5f, 0.5f), f2_pack(0.5f, 0.5f)), w);
+}
+// thread `lane` writes 16 packed pairs as bf16 into half h of row `lane`
+__device__ __forceinline__ void stage_put_half(uint8_t* stg, int lane, int h, const f32x2_t* v) {
+#pragma unroll
+  for (int q = 0; q < 4; ++q)
+    stage_set(stg, lane, 4 * h + q,
+              make_uint4(f2_to_bf16x2(v[q * 4 + 0]), f2_to_bf16x2(v[q * 4 + 1]),
+                         f2_to_bf16x2(v[q * 4 + 2]), f2_to_bf16x2(v[q * 4 + 3])));
+}
+__device__ __forceinline__ void epilogue_chunk_fast(const GemmArgs& g, uint8_t* stg, int lane,
+                                                    uint32_t t_addr, int row0, int rows_valid,
+                                                    int n0, float alpha, bool bias_vec, int cc,
+                                                    const uint4* pf_v, bool pf_ok) {
+  const int col0 = n0 + cc * 64;
+  if (rows_valid == 0 || col0 >= g.N) return;  // warp-uniform
+  const int cols_valid = (g.N - col0) < 64 ? (g.N - col0) : 64;
+  const bool vec_bias = bias_vec && cols_valid == 64 && (col0 & 7) == 0;
+  const uint32_t t_c = t_addr + cc * 64;
+  if (g.epi == NKB_EPI_GELU_FWD) {
+    // first pass: the pre-activation goes out for the backward pass
+    __syncwarp();
+#pragma unroll 1
+    for (int h = 0; h < 2; ++h) {
+      f32x2_t v[16];
+      epi_load_half(t_c + h * 32, alpha, v);
+      epi_bias_half(g, v, col0 + h * 32, cols_valid - h * 32, vec_bias);
+      stage_put_half(stg, lane, h, v);
+    }
+    stage_store_bf16(stg, lane, g.aux_out + (long long)row0 * g.ldaux + col0, g.ldaux, rows_valid,
+                     cols_valid);
+  }
+  const bool in_res = g.res != nullptr, in_aux = g.epi == NKB_EPI_GELU_BWD;
+  const bool in_acc = g.accumulate != 0;
+  if (in_res || in_aux) {
+    if (pf_ok) {
+      stage_from_regs(stg, lane, pf_v);
+    } else if (in_res) {
+      stage_load_bf16(stg, lane, g.res + (long long)row0 * g.ldres + col0, g.ldres, rows_valid,
+                      cols_valid);
+    } else {
+      stage_load_bf16(stg, lane, g.aux_in + (long long)row0 * g.ldaux + col0, g.ldaux, rows_valid,
+                      cols_valid);
+    }
+  } else if (in_acc) {
+    stage_load_bf16(stg, lane, reinterpret_cast<const __nv_bfloat16*>(g.C) +
+                                   (long long)row0 * g.ldc + col0, g.ldc, rows_valid, cols_valid);
+  } else {
+    __syncwarp();  // the previous chunk's cooperative store has read the tile
+  }
+#pragma unroll 1
+  for (int h = 0; h < 2; ++h) {
+    f32x2_t v[16];
+    epi_load_half(t_c + h * 32, alpha, v);
+    epi_bias_half(g, v, col0 + h * 32, cols_valid - h * 32, vec_bias);
+    if (g.epi == NKB_EPI_GELU_FWD) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[i] = gelu_tanh2(v[i]);
+    } else if (g.epi == NKB_EPI_RELU) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        float a, b;
+        f2_unpack(v[i], a, b);
+        v[i] = f2_pack(fmaxf(a, 0.f), fmaxf(b, 0.f));
+      }
+    }
+    if (in_res || in_aux || in_acc) {
+      // this thread's own row of the staged input; half h is overwritten right after
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint4 z = stage_get(stg, lane, 4 * h + q);
+        const uint32_t w[4] = {z.x, z.y, z.z, z.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const f32x2_t f = f2_from_bf16x2(w[j]);
+          if (in_aux) v[q * 4 + j] = f2_mul(v[q * 4 + j], gelu_tanh_grad2(f));
+          else v[q * 4 + j] = f2_add(v[q * 4 + j], f);
+        }
+      }
+    }
+    stage_put_half(stg, lane, h, v);
+  }
+  stage_store_bf16(stg, lane, reinterpret_cast<__nv_bfloat16*>(g.C) + (long long)row0 * g.ldc + col0,
+                   g.ldc, rows_valid, cols_valid);
+}
+
 // MODE 0: plain epilogue; 1: kernel fused with a collective (rs_dst set: raw partial
 // sums to the owner's staging slab); 2: split-K (raw fp32 partial sums to raw_dst).
 // One 64-column chunk (index cc) of this warp's 32-row slab; pf_v / pf_ok: the prefetched
 // residual (or, for the GELU backward epilogue, saved pre-activation) pieces of the chunk.
 template <int MODE>
-__device__ __forceinline__ void epilogue_chunk(const GemmArgs& g, uint8_t* stg, int lane,
+__device__ __forceinline__ void epilogue_chunk_general(const GemmArgs& g, uint8_t* stg, int lane,
                                                uint32_t t_addr, int row0, int rows_valid, int n0,
                                                float alpha, bool bias_vec, int cc, const uint4* pf_v,
                                                bool pf_ok, __nv_bfloat16* rs_dst, long long rs_ld,
@@ -563,11 +703,22 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, uint8_t* stg, i
                                               const EpiPrefetch& pf,
                                               __nv_bfloat16* rs_dst = nullptr,
                                               long long rs_ld = 0, float* raw_dst = nullptr) {
-  epilogue_chunk<MODE>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec, cc0, pf.v[0],
-                       pf.ok[0], rs_dst, rs_ld, raw_dst);
+  if constexpr (MODE == 0) {
+    const int n_in = (g.res ? 1 : 0) + (g.epi == NKB_EPI_GELU_BWD ? 1 : 0) + (g.accumulate ? 1 : 0);
+    if (!g.c_fp32 && n_in <= 1) {
+      epilogue_chunk_fast(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec, cc0, pf.v[0],
+                          pf.ok[0]);
+      if constexpr (NCW > 1)
+        epilogue_chunk_fast(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec, cc0 + 1,
+                            pf.v[1], pf.ok[1]);
+      return;
+    }
+  }
+  epilogue_chunk_general<MODE>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec, cc0,
+                               pf.v[0], pf.ok[0], rs_dst, rs_ld, raw_dst);
   if constexpr (NCW > 1)
-    epilogue_chunk<MODE>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec, cc0 + 1,
-                         pf.v[1], pf.ok[1], rs_dst, rs_ld, raw_dst);
+    epilogue_chunk_general<MODE>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec,
+                                 cc0 + 1, pf.v[1], pf.ok[1], rs_dst, rs_ld, raw_dst);
 }
 
 template <int BN, bool A_MN, bool B_MN, int MODE>

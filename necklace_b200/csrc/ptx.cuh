@@ -445,6 +445,40 @@ __device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
   return v;
 }
 
+// ------------------------------------------------ packed fp32 pairs (sm_100 f32x2)
+// Two fp32 values in one 64-bit register pair; one instruction does both lanes.
+typedef uint64_t f32x2_t;
+__device__ __forceinline__ f32x2_t f2_pack(float a, float b) {
+  f32x2_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(f32x2_t v, float& a, float& b) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ f32x2_t f2_fma(f32x2_t a, f32x2_t b, f32x2_t c) {
+  f32x2_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ f32x2_t f2_mul(f32x2_t a, f32x2_t b) {
+  f32x2_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ f32x2_t f2_add(f32x2_t a, f32x2_t b) {
+  f32x2_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ f32x2_t f2_tanh(f32x2_t v) {
+  float a, b;
+  f2_unpack(v, a, b);
+  asm("tanh.approx.f32 %0, %0;" : "+f"(a));
+  asm("tanh.approx.f32 %0, %0;" : "+f"(b));
+  return f2_pack(a, b);
+}
+
 // -------------------------------------------------------------- bf16 utils
 __device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
   __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
@@ -453,6 +487,16 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
 __device__ __forceinline__ float2 unpack_bf16x2(uint32_t u) {
   __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162*>(&u);
   return __bfloat1622float2(v);
+}
+
+// bf16 pair -> packed fp32 pair (bf16 is the upper half of an fp32)
+__device__ __forceinline__ f32x2_t f2_from_bf16x2(uint32_t u) {
+  return f2_pack(__uint_as_float(u << 16), __uint_as_float(u & 0xFFFF0000u));
+}
+__device__ __forceinline__ uint32_t f2_to_bf16x2(f32x2_t v) {
+  float a, b;
+  f2_unpack(v, a, b);
+  return pack_bf16x2(a, b);
 }
 
 }  // namespace nkb

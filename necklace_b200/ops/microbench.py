@@ -139,17 +139,39 @@ def bench_attn(flush):
 
 
 def one_gemm(argv):
-    """``gemm_one M N K [a_mn b_mn]``: a handful of launches of one shape (ncu captures)."""
-    from . import gemm
+    """``gemm_one M N K [a_mn b_mn [epilogue]]``: a handful of launches of one shape (ncu
+    captures); epilogue: none | bias | gelu (bias + GELU, saves the pre-activation) |
+    gelubwd (times GELU' of a saved pre-activation) | res (bias + residual)."""
+    from . import gemm, EPI_GELU_FWD, EPI_GELU_BWD
     M, N, K = (int(x) for x in argv[2:5])
     a_mn = len(argv) > 5 and argv[5] == "1"
     b_mn = len(argv) > 6 and argv[6] == "1"
+    epi = argv[7] if len(argv) > 7 else "none"
     A = torch.randn((K, M) if a_mn else (M, K), device="cuda").bfloat16()
     B = torch.randn((K, N) if b_mn else (N, K), device="cuda").bfloat16()
     out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    bias = torch.randn(N, device="cuda").bfloat16()
+    aux = torch.randn(M, N, device="cuda").bfloat16()
+    kw = {}
+    if epi == "bias":
+        kw = dict(bias=bias)
+    elif epi == "gelu":
+        kw = dict(bias=bias, epi=EPI_GELU_FWD, aux=aux)
+    elif epi == "gelubwd":
+        kw = dict(epi=EPI_GELU_BWD, aux=aux)
+    elif epi == "res":
+        kw = dict(bias=bias, res=aux)
     for _ in range(5):
-        gemm(A, B, a_mn=a_mn, b_mn=b_mn, out=out)
+        gemm(A, B, a_mn=a_mn, b_mn=b_mn, out=out, **kw)
     torch.cuda.synchronize()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    ev[0].record()
+    for _ in range(20):
+        gemm(A, B, a_mn=a_mn, b_mn=b_mn, out=out, **kw)
+    ev[1].record()
+    torch.cuda.synchronize()
+    print(json.dumps({"op": "gemm_one", "M": M, "N": N, "K": K, "epi": epi,
+                      "ms": round(ev[0].elapsed_time(ev[1]) / 20, 4)}), flush=True)
 
 
 def one_attn(argv):
