@@ -359,47 +359,40 @@ __device__ __forceinline__ void stage_load_f32(uint8_t* stg, int lane, const flo
 
 // Epilogue of one 128 x BN accumulator slab: this warp's 32 rows (TMEM lanes), BN
 // columns starting at global column n0; fused math, then staged coalesced stores.
-// Residual / saved-activation rows that the epilogue adds or multiplies do not depend on
-// the accumulator, so their global loads are issued before the wait on the accumulator
-// (coalesced pieces in registers) and moved to the staging tile when the chunk is used.
-struct EpiPrefetch {
-  uint4 v[2][8];   // up to two 64-column chunks per warp
-  bool ok[2];      // chunk was prefetched (full, 16-byte aligned chunk)
-};
-template <int NCW>
-__device__ __forceinline__ void epi_prefetch(EpiPrefetch& pf, const __nv_bfloat16* src,
-                                             long long ld, int row0, int rows_valid, int col0,
-                                             int N, int lane) {
-  const bool vec = src != nullptr && ((ld & 7) == 0) &&
-                   ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
-#pragma unroll
-  for (int c = 0; c < NCW; ++c) {
-    const int cbase = col0 + c * 64;
-    pf.ok[c] = vec && rows_valid > 0 && cbase + 64 <= N;
-    if (pf.ok[c]) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int row = i * 4 + (lane >> 3), ch = lane & 7;
-        pf.v[c][i] = make_uint4(0, 0, 0, 0);
-        if (row < rows_valid)
-          pf.v[c][i] = ld_nc_v4(src + (long long)(row0 + row) * ld + cbase + ch * 8);
-      }
-    }
-  }
-}
-__device__ __forceinline__ void stage_from_regs(uint8_t* stg, int lane, const uint4* v) {
+// Residual / saved-activation rows that the epilogue adds or multiplies do not depend on the
+// accumulator: their 32 x 64 bf16 block is copied global -> staging tile with cp.async
+// (no registers), for a tile's first chunk before the wait on the accumulator.  Returns
+// false (nothing issued) for ragged or unaligned blocks, which take the synchronous load.
+__device__ __forceinline__ bool epi_stage_async(uint8_t* stg, int lane, const __nv_bfloat16* src,
+                                                long long ld, int row0, int rows_valid, int col0,
+                                                int N) {
+  const bool ok = src != nullptr && ((ld & 7) == 0) &&
+                  ((reinterpret_cast<uintptr_t>(src) & 15) == 0) && rows_valid == 32 &&
+                  col0 + 64 <= N;
+  if (!ok) return false;
   __syncwarp();
 #pragma unroll
-  for (int i = 0; i < 8; ++i) stage_set(stg, i * 4 + (lane >> 3), lane & 7, v[i]);
+  for (int i = 0; i < 8; ++i) {
+    const int row = i * 4 + (lane >> 3), ch = lane & 7;
+    const uint32_t dst = smem_u32(stg + row * 128 + ((ch ^ (row & 7)) << 4));
+    const __nv_bfloat16* gp = src + (long long)(row0 + row) * ld + col0 + ch * 8;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(gp) : "memory");
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  return true;
+}
+__device__ __forceinline__ void epi_stage_async_wait() {
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
   __syncwarp();
 }
 
 // ---- bf16-output fast path of the epilogue -------------------------------------------
-// The chunk is processed as two 32-column halves by ONE copy of the code (the half loop is
-// not unrolled): the fully unrolled 64-column form was several tens of KB of straight-line
-// code per warp and the eight epilogue warps, each at a different place in it, stalled on
-// instruction fetch.  At most one staged input tile (residual, saved pre-activation or the
-// old C for accumulation) is supported here; other combinations take the general form.
+// Straight-line code that runs once per tile is bound by instruction fetch (a trace showed
+// ~20 cycles per instruction in the fully unrolled form), so the fast path is ONE copy of a
+// 32-column half body inside loops that are not unrolled: chunks of the warp's share, halves
+// of a chunk.  Math runs on packed fp32 pairs.  At most one staged input tile (residual,
+// saved pre-activation or the old C for accumulation) and no input together with the GELU
+// forward (whose first pass uses the staging tile); other combinations take the general form.
 // values travel as packed fp32 pairs (one instruction per two columns)
 __device__ __forceinline__ void epi_load_half(uint32_t taddr, float alpha, f32x2_t* v) {
   uint32_t r[32];
@@ -459,14 +452,13 @@ __device__ __forceinline__ void stage_put_half(uint8_t* stg, int lane, int h, co
                          f2_to_bf16x2(v[q * 4 + 2]), f2_to_bf16x2(v[q * 4 + 3])));
 }
 __device__ __forceinline__ void epilogue_chunk_fast(const GemmArgs& g, uint8_t* stg, int lane,
-                                                    uint32_t t_addr, int row0, int rows_valid,
-                                                    int n0, float alpha, bool bias_vec, int cc,
-                                                    const uint4* pf_v, bool pf_ok) {
-  const int col0 = n0 + cc * 64;
-  if (rows_valid == 0 || col0 >= g.N) return;  // warp-uniform
+                                                    uint32_t t_c, int row0, int rows_valid,
+                                                    int col0, float alpha, bool bias_vec,
+                                                    bool in_async) {
   const int cols_valid = (g.N - col0) < 64 ? (g.N - col0) : 64;
   const bool vec_bias = bias_vec && cols_valid == 64 && (col0 & 7) == 0;
-  const uint32_t t_c = t_addr + cc * 64;
+  const bool in_res = g.res != nullptr, in_aux = g.epi == NKB_EPI_GELU_BWD;
+  const bool in_acc = g.accumulate != 0;
   if (g.epi == NKB_EPI_GELU_FWD) {
     // first pass: the pre-activation goes out for the backward pass
     __syncwarp();
@@ -479,19 +471,14 @@ __device__ __forceinline__ void epilogue_chunk_fast(const GemmArgs& g, uint8_t* 
     }
     stage_store_bf16(stg, lane, g.aux_out + (long long)row0 * g.ldaux + col0, g.ldaux, rows_valid,
                      cols_valid);
-  }
-  const bool in_res = g.res != nullptr, in_aux = g.epi == NKB_EPI_GELU_BWD;
-  const bool in_acc = g.accumulate != 0;
-  if (in_res || in_aux) {
-    if (pf_ok) {
-      stage_from_regs(stg, lane, pf_v);
-    } else if (in_res) {
-      stage_load_bf16(stg, lane, g.res + (long long)row0 * g.ldres + col0, g.ldres, rows_valid,
-                      cols_valid);
-    } else {
-      stage_load_bf16(stg, lane, g.aux_in + (long long)row0 * g.ldaux + col0, g.ldaux, rows_valid,
-                      cols_valid);
-    }
+  } else if (in_async) {
+    epi_stage_async_wait();
+  } else if (in_res) {
+    stage_load_bf16(stg, lane, g.res + (long long)row0 * g.ldres + col0, g.ldres, rows_valid,
+                    cols_valid);
+  } else if (in_aux) {
+    stage_load_bf16(stg, lane, g.aux_in + (long long)row0 * g.ldaux + col0, g.ldaux, rows_valid,
+                    cols_valid);
   } else if (in_acc) {
     stage_load_bf16(stg, lane, reinterpret_cast<const __nv_bfloat16*>(g.C) +
                                    (long long)row0 * g.ldc + col0, g.ldc, rows_valid, cols_valid);
@@ -534,15 +521,45 @@ __device__ __forceinline__ void epilogue_chunk_fast(const GemmArgs& g, uint8_t* 
                    g.ldc, rows_valid, cols_valid);
 }
 
+__device__ __forceinline__ bool epi_fast_ok(const GemmArgs& g) {
+  const int n_in = (g.res ? 1 : 0) + (g.epi == NKB_EPI_GELU_BWD ? 1 : 0) + (g.accumulate ? 1 : 0);
+  return !g.c_fp32 && n_in <= 1 && !(n_in == 1 && g.epi == NKB_EPI_GELU_FWD);
+}
+// source of the staged input that may be fetched ahead (residual or saved pre-activation)
+__device__ __forceinline__ const __nv_bfloat16* epi_async_src(const GemmArgs& g, long long* ld) {
+  if (g.res) { *ld = g.ldres; return g.res; }
+  if (g.epi == NKB_EPI_GELU_BWD) { *ld = g.ldaux; return g.aux_in; }
+  *ld = 0;
+  return nullptr;
+}
+// The warp's share of a tile: chunks [cc0, cc0 + ncw); first_async: the first chunk's input
+// is already on its way into the staging tile.
+__device__ __forceinline__ void epilogue_fast_tile(const GemmArgs& g, uint8_t* stg, int lane,
+                                                   uint32_t t_addr, int row0, int rows_valid,
+                                                   int n0, float alpha, bool bias_vec, int cc0,
+                                                   int ncw, bool first_async) {
+  if (rows_valid == 0) return;
+  long long in_ld;
+  const __nv_bfloat16* in_src = epi_async_src(g, &in_ld);
+#pragma unroll 1
+  for (int c = 0; c < ncw; ++c) {
+    const int col0 = n0 + (cc0 + c) * 64;
+    if (col0 >= g.N) break;  // warp-uniform
+    bool in_async = first_async;
+    if (c > 0) in_async = epi_stage_async(stg, lane, in_src, in_ld, row0, rows_valid, col0, g.N);
+    epilogue_chunk_fast(g, stg, lane, t_addr + (cc0 + c) * 64, row0, rows_valid, col0, alpha,
+                        bias_vec, in_async);
+  }
+}
+
 // MODE 0: plain epilogue; 1: kernel fused with a collective (rs_dst set: raw partial
 // sums to the owner's staging slab); 2: split-K (raw fp32 partial sums to raw_dst).
-// One 64-column chunk (index cc) of this warp's 32-row slab; pf_v / pf_ok: the prefetched
-// residual (or, for the GELU backward epilogue, saved pre-activation) pieces of the chunk.
+// General form: one 64-column chunk (index cc) of this warp's 32-row slab, fully unrolled.
 template <int MODE>
 __device__ __forceinline__ void epilogue_chunk_general(const GemmArgs& g, uint8_t* stg, int lane,
                                                uint32_t t_addr, int row0, int rows_valid, int n0,
-                                               float alpha, bool bias_vec, int cc, const uint4* pf_v,
-                                               bool pf_ok, __nv_bfloat16* rs_dst, long long rs_ld,
+                                               float alpha, bool bias_vec, int cc,
+                                               __nv_bfloat16* rs_dst, long long rs_ld,
                                                float* raw_dst) {
     uint32_t r[64];
     tmem_ld_32x32(t_addr + cc * 64, r);
@@ -607,11 +624,8 @@ __device__ __forceinline__ void epilogue_chunk_general(const GemmArgs& g, uint8_
 #pragma unroll
       for (int i = 0; i < 64; ++i) v[i] = gelu_tanh(v[i]);
     } else if (g.epi == NKB_EPI_GELU_BWD) {
-      if (!g.res && pf_ok)
-        stage_from_regs(stg, lane, pf_v);
-      else
-        stage_load_bf16(stg, lane, g.aux_in + (long long)row0 * g.ldaux + col0, g.ldaux,
-                        rows_valid, cols_valid);
+      stage_load_bf16(stg, lane, g.aux_in + (long long)row0 * g.ldaux + col0, g.ldaux,
+                      rows_valid, cols_valid);
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
         uint4 z = stage_get(stg, lane, q);
@@ -628,11 +642,8 @@ __device__ __forceinline__ void epilogue_chunk_general(const GemmArgs& g, uint8_
       for (int i = 0; i < 64; ++i) v[i] = fmaxf(v[i], 0.f);
     }
     if (g.res) {
-      if (pf_ok)
-        stage_from_regs(stg, lane, pf_v);
-      else
-        stage_load_bf16(stg, lane, g.res + (long long)row0 * g.ldres + col0, g.ldres, rows_valid,
-                        cols_valid);
+      stage_load_bf16(stg, lane, g.res + (long long)row0 * g.ldres + col0, g.ldres, rows_valid,
+                      cols_valid);
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
         uint4 z = stage_get(stg, lane, q);
@@ -695,30 +706,18 @@ __device__ __forceinline__ void epilogue_chunk_general(const GemmArgs& g, uint8_
     }
 }
 
-// The warp handles chunks [cc0, cc0 + NCW) of the slab.
+// The warp handles chunks [cc0, cc0 + NCW) of the slab (general form).
 template <int BN, int MODE, int NCW>
 __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, uint8_t* stg, int lane,
                                               uint32_t t_addr, int row0, int rows_valid, int n0,
                                               float alpha, bool bias_vec, int cc0,
-                                              const EpiPrefetch& pf,
                                               __nv_bfloat16* rs_dst = nullptr,
                                               long long rs_ld = 0, float* raw_dst = nullptr) {
-  if constexpr (MODE == 0) {
-    const int n_in = (g.res ? 1 : 0) + (g.epi == NKB_EPI_GELU_BWD ? 1 : 0) + (g.accumulate ? 1 : 0);
-    if (!g.c_fp32 && n_in <= 1) {
-      epilogue_chunk_fast(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec, cc0, pf.v[0],
-                          pf.ok[0]);
-      if constexpr (NCW > 1)
-        epilogue_chunk_fast(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec, cc0 + 1,
-                            pf.v[1], pf.ok[1]);
-      return;
-    }
-  }
   epilogue_chunk_general<MODE>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec, cc0,
-                               pf.v[0], pf.ok[0], rs_dst, rs_ld, raw_dst);
+                               rs_dst, rs_ld, raw_dst);
   if constexpr (NCW > 1)
     epilogue_chunk_general<MODE>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec,
-                                 cc0 + 1, pf.v[1], pf.ok[1], rs_dst, rs_ld, raw_dst);
+                                 cc0 + 1, rs_dst, rs_ld, raw_dst);
 }
 
 template <int BN, bool A_MN, bool B_MN, int MODE>
@@ -920,8 +919,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint32_t acc_phase = 0;
     const float alpha = g.alpha_dev ? g.alpha * __ldg(g.alpha_dev) : g.alpha;
     const bool bias_vec = g.bias && ((reinterpret_cast<uintptr_t>(g.bias) & 15) == 0);
-    const __nv_bfloat16* pf_src = g.res ? g.res : (g.epi == NKB_EPI_GELU_BWD ? g.aux_in : nullptr);
-    const long long pf_ld = g.res ? g.ldres : g.ldaux;
+    const bool fast = MODE == 0 && epi_fast_ok(g);
+    long long in_ld;
+    const __nv_bfloat16* in_src = epi_async_src(g, &in_ld);
     for (int u = cta_id; u < num_units; u += n_ctas) {
       const int t = u % num_tiles, ks = u / num_tiles;
       const int mb = (t % g.num_m_blocks + mb_shift) % g.num_m_blocks, nb = t / g.num_m_blocks;
@@ -929,9 +929,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int n0 = nb * BN;
       int rows_valid = g.M - row0;
       rows_valid = rows_valid < 0 ? 0 : (rows_valid > 32 ? 32 : rows_valid);
-      EpiPrefetch pf;
-      pf.ok[0] = pf.ok[1] = false;
-      if (MODE == 0 && pf_src) epi_prefetch<NCW>(pf, pf_src, pf_ld, row0, rows_valid, n0 + cc0 * 64, g.N, lane);
+      // the first chunk's residual / saved activation starts moving before the accumulator is ready
+      bool first_async = false;
+      if (fast && in_src)
+        first_async = epi_stage_async(stg, lane, in_src, in_ld, row0, rows_valid, n0 + cc0 * 64, g.N);
       if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag)) {
         set_error(g.status, abort_flag, NKB_ERR_ACC_WAIT);
         break;
@@ -942,14 +943,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         int* tflag;
         __nv_bfloat16* dst = rs_tile_dst(g, mb * BM, lane_grp, n0, &tflag, nb, g.num_n_blocks);
         epilogue_tile<BN, MODE, NCW>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec,
-                                     cc0, pf, dst, g.N);
+                                     cc0, dst, g.N);
         __threadfence_system();
         asm volatile("bar.sync 1, 256;" ::: "memory");  // the eight epilogue warps
         if (ew == 0 && lane == 0) st_release_sys(tflag, rs_epoch);
+      } else if (fast) {
+        epilogue_fast_tile(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec, cc0, NCW,
+                           first_async);
       } else {
         float* raw = MODE == 2 ? g.splitk_ws + ((long long)ks * g.M + row0) * g.N + n0 : nullptr;
         epilogue_tile<BN, MODE, NCW>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec,
-                                     cc0, pf, nullptr, 0, raw);
+                                     cc0, nullptr, 0, raw);
       }
       tc_fence_before();
       __syncwarp();
@@ -1175,8 +1179,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
     uint32_t acc_phase = 0;
     const float alpha = g.alpha_dev ? g.alpha * __ldg(g.alpha_dev) : g.alpha;
     const bool bias_vec = g.bias && ((reinterpret_cast<uintptr_t>(g.bias) & 15) == 0);
-    const __nv_bfloat16* pf_src = g.res ? g.res : (g.epi == NKB_EPI_GELU_BWD ? g.aux_in : nullptr);
-    const long long pf_ld = g.res ? g.ldres : g.ldaux;
+    const bool fast = MODE == 0 && epi_fast_ok(g);
+    long long in_ld;
+    const __nv_bfloat16* in_src = epi_async_src(g, &in_ld);
     for (int u = pair; u < num_units; u += npairs) {
       const int t = u % num_tiles, ks = u / num_tiles;
       const int mb2 = (t % num_m2 + mb_shift) % num_m2, nb = t / num_m2;
@@ -1184,9 +1189,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       const int n0 = nb * BN;
       int rows_valid = g.M - row0;
       rows_valid = rows_valid < 0 ? 0 : (rows_valid > 32 ? 32 : rows_valid);
-      EpiPrefetch pf;
-      pf.ok[0] = pf.ok[1] = false;
-      if (MODE == 0 && pf_src) epi_prefetch<NCW>(pf, pf_src, pf_ld, row0, rows_valid, n0 + cc0 * 64, g.N, lane);
+      // the first chunk's residual / saved activation starts moving before the accumulator is ready
+      bool first_async = false;
+      if (fast && in_src)
+        first_async = epi_stage_async(stg, lane, in_src, in_ld, row0, rows_valid, n0 + cc0 * 64, g.N);
       if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag)) {
         set_error(g.status, abort_flag, NKB_ERR_ACC_WAIT);
         break;
@@ -1198,14 +1204,17 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
         __nv_bfloat16* dst = rs_tile_dst(g, mb2 * 256 + (int)rank * 128, lane_grp, n0, &tflag, nb,
                                          g.num_n_blocks);
         epilogue_tile<BN, MODE, NCW>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec,
-                                     cc0, pf, dst, g.N);
+                                     cc0, dst, g.N);
         __threadfence_system();
         asm volatile("bar.sync 1, 256;" ::: "memory");
         if (ew == 0 && lane == 0) st_release_sys(tflag, rs_epoch);
+      } else if (fast) {
+        epilogue_fast_tile(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec, cc0, NCW,
+                           first_async);
       } else {
         float* raw = MODE == 2 ? g.splitk_ws + ((long long)ks * g.M + row0) * g.N + n0 : nullptr;
         epilogue_tile<BN, MODE, NCW>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec,
-                                     cc0, pf, nullptr, 0, raw);
+                                     cc0, nullptr, 0, raw);
       }
       tc_fence_before();
       __syncwarp();
