@@ -93,6 +93,10 @@ struct GemmArgs {
   // accumulate / output type.
   int split_k;
   float* splitk_ws;
+  // Output (and saved pre-activation) tiles leave through TMA stores when their layout
+  // allows it (16-byte aligned base and row pitch): box = 64 columns x 32 rows, 128B swizzle.
+  int tma_c, tma_aux;
+  CUtensorMap tm_c, tm_aux;
 };
 
 // Reduce role of the fused reduce-scatter (see GemmArgs).
@@ -370,6 +374,7 @@ __device__ __forceinline__ bool epi_stage_async(uint8_t* stg, int lane, const __
                   ((reinterpret_cast<uintptr_t>(src) & 15) == 0) && rows_valid == 32 &&
                   col0 + 64 <= N;
   if (!ok) return false;
+  if (lane == 0) tma_store_wait_read<0>();  // an earlier TMA store may still read the tile
   __syncwarp();
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
@@ -451,6 +456,32 @@ __device__ __forceinline__ void stage_put_half(uint8_t* stg, int lane, int h, co
               make_uint4(f2_to_bf16x2(v[q * 4 + 0]), f2_to_bf16x2(v[q * 4 + 1]),
                          f2_to_bf16x2(v[q * 4 + 2]), f2_to_bf16x2(v[q * 4 + 3])));
 }
+// The staging tile goes to global memory: one TMA store issued by lane 0 (the tensor map clips
+// rows / columns outside the matrix), else the cooperative copy.  Shared memory is the scarce
+// resource here: the MMA operand reads and the TMA operand writes already use most of its
+// bandwidth, and a copy by the warp costs a ld.shared + st.global per 512 bytes.
+__device__ __forceinline__ void stage_out(const uint8_t* stg, int lane, const CUtensorMap* tm,
+                                          bool use_tma, __nv_bfloat16* gptr, long long ld, int row0,
+                                          int col0, int rows_valid, int cols_valid) {
+  if (use_tma) {
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_2d(tm, stg, col0, row0);
+      tma_store_commit();
+    }
+  } else {
+    stage_store_bf16(stg, lane, gptr, ld, rows_valid, cols_valid);
+  }
+}
+// before the tile is written again: the store has finished reading it
+__device__ __forceinline__ void stage_out_drain(int lane, bool use_tma) {
+  if (use_tma) {
+    if (lane == 0) tma_store_wait_read<0>();
+    __syncwarp();
+  }
+}
+
 __device__ __forceinline__ void epilogue_chunk_fast(const GemmArgs& g, uint8_t* stg, int lane,
                                                     uint32_t t_c, int row0, int rows_valid,
                                                     int col0, float alpha, bool bias_vec,
@@ -459,6 +490,7 @@ __device__ __forceinline__ void epilogue_chunk_fast(const GemmArgs& g, uint8_t* 
   const bool vec_bias = bias_vec && cols_valid == 64 && (col0 & 7) == 0;
   const bool in_res = g.res != nullptr, in_aux = g.epi == NKB_EPI_GELU_BWD;
   const bool in_acc = g.accumulate != 0;
+  if (!in_async) stage_out_drain(lane, true);  // the previous chunk's store has read the tile
   if (g.epi == NKB_EPI_GELU_FWD) {
     // first pass: the pre-activation goes out for the backward pass
     __syncwarp();
@@ -469,8 +501,9 @@ __device__ __forceinline__ void epilogue_chunk_fast(const GemmArgs& g, uint8_t* 
       epi_bias_half(g, v, col0 + h * 32, cols_valid - h * 32, vec_bias);
       stage_put_half(stg, lane, h, v);
     }
-    stage_store_bf16(stg, lane, g.aux_out + (long long)row0 * g.ldaux + col0, g.ldaux, rows_valid,
-                     cols_valid);
+    stage_out(stg, lane, &g.tm_aux, g.tma_aux != 0, g.aux_out + (long long)row0 * g.ldaux + col0,
+              g.ldaux, row0, col0, rows_valid, cols_valid);
+    stage_out_drain(lane, g.tma_aux != 0);
   } else if (in_async) {
     epi_stage_async_wait();
   } else if (in_res) {
@@ -517,8 +550,9 @@ __device__ __forceinline__ void epilogue_chunk_fast(const GemmArgs& g, uint8_t* 
     }
     stage_put_half(stg, lane, h, v);
   }
-  stage_store_bf16(stg, lane, reinterpret_cast<__nv_bfloat16*>(g.C) + (long long)row0 * g.ldc + col0,
-                   g.ldc, rows_valid, cols_valid);
+  stage_out(stg, lane, &g.tm_c, g.tma_c != 0,
+            reinterpret_cast<__nv_bfloat16*>(g.C) + (long long)row0 * g.ldc + col0, g.ldc, row0, col0,
+            rows_valid, cols_valid);
 }
 
 __device__ __forceinline__ bool epi_fast_ok(const GemmArgs& g) {
@@ -723,7 +757,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, uint8_t* stg, i
 template <int BN, bool A_MN, bool B_MN, int MODE>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const GemmArgs g) {
+                 const __grid_constant__ GemmArgs g) {
   constexpr int B_STAGE_BYTES = BN * BK * 2;
   constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
   constexpr int STAGES = (BN == 256) ? 4 : 6;
@@ -963,6 +997,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         acc_phase ^= 1;
       }
     }
+    if (lane == 0) tma_store_wait<0>();  // bulk stores of this warp have landed
   }
 
   // ------------------------------------------------------------- teardown
@@ -994,7 +1029,7 @@ constexpr int PAIR_STAGE_BYTES = A_STAGE_BYTES + PAIR_B_BYTES;
 template <bool A_MN, bool B_MN, int MODE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
-                      const __grid_constant__ CUtensorMap tmB, const GemmArgs g) {
+                      const __grid_constant__ CUtensorMap tmB, const __grid_constant__ GemmArgs g) {
   constexpr int BN = 256;
   constexpr uint32_t TMEM_COLS = 512;
   extern __shared__ uint8_t smem_raw[];
@@ -1227,6 +1262,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
         acc_phase ^= 1;
       }
     }
+    if (lane == 0) tma_store_wait<0>();  // bulk stores of this warp have landed
   }
 
   tc_fence_before();
@@ -1446,6 +1482,14 @@ static int gemm_run(GemmArgs g, const void* A, long long lda, int a_mn, const vo
   }
   CUtensorMap tmA, tmB;
   int rc;
+  g.tma_c = g.tma_aux = 0;
+  if (!g.c_fp32 && !g.ag_ctas && !g.rs_ctas && g.split_k == 1 && (g.ldc & 7) == 0 &&
+      (reinterpret_cast<uintptr_t>(g.C) & 15) == 0 &&
+      make_tmap_bf16_2d(&g.tm_c, g.C, N, M, g.ldc, 64, 32) == 0)
+    g.tma_c = 1;
+  if (g.aux_out && (g.ldaux & 7) == 0 && (reinterpret_cast<uintptr_t>(g.aux_out) & 15) == 0 &&
+      make_tmap_bf16_2d(&g.tm_aux, g.aux_out, N, M, g.ldaux, 64, 32) == 0)
+    g.tma_aux = 1;
   if (!a_mn) rc = make_tmap_bf16_2d(&tmA, A, K, M, lda, BK, BM);
   else rc = make_tmap_bf16_2d(&tmA, A, M, K, lda, 64, BK);
   if (rc) return rc;
