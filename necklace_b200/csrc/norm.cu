@@ -150,7 +150,9 @@ norm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
 
 // Column sums.  Block = 32 x 8 threads: a lane owns 8 adjacent columns (one 16-byte
 // load per row), the 8 warps take interleaved rows; grid = (ceil(C/256), row_splits).
-// Two rows are in flight per thread to cover memory latency.
+// A warp keeps COLSUM_UNROLL rows (independent 16-byte loads) in flight and the grid is sized
+// to about two CTAs per SM, so that each SM has tens of KB outstanding (latency x bandwidth).
+constexpr int COLSUM_UNROLL = 8;
 __global__ void __launch_bounds__(256)
 colsum_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
               const float* __restrict__ stats, float* __restrict__ acc, int rows, int C,
@@ -165,7 +167,44 @@ colsum_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restr
   const bool vec = (col + 8 <= C) && ((ld & 7) == 0);
   const int stride = gridDim.y * 8;
   if (col < C) {
-    for (int r = blockIdx.y * 8 + wy; r < rows; r += stride) {
+    int r = blockIdx.y * 8 + wy;
+    if (vec) {
+      // main part: COLSUM_UNROLL rows per step, all loads issued before any use
+      for (; r + (COLSUM_UNROLL - 1) * stride < rows; r += COLSUM_UNROLL * stride) {
+        uint4 gu[COLSUM_UNROLL], xu[COLSUM_UNROLL];
+        float mean[COLSUM_UNROLL], rstd[COLSUM_UNROLL];
+#pragma unroll
+        for (int u = 0; u < COLSUM_UNROLL; ++u) {
+          const long long rr = r + (long long)u * stride;
+          gu[u] = ld_nc_v4(dy + rr * ld + col);
+          xu[u] = make_uint4(0, 0, 0, 0);
+          mean[u] = 0.f;
+          rstd[u] = 0.f;
+          if (x) {
+            xu[u] = ld_nc_v4(x + rr * ld + col);
+            mean[u] = rms ? 0.f : stats[2 * rr];
+            rstd[u] = stats[2 * rr + 1];
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < COLSUM_UNROLL; ++u) {
+          const uint32_t w[4] = {gu[u].x, gu[u].y, gu[u].z, gu[u].w};
+          const uint32_t v[4] = {xu[u].x, xu[u].y, xu[u].z, xu[u].w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = unpack_bf16x2(w[j]);
+            b[2 * j] += f.x;
+            b[2 * j + 1] += f.y;
+            if (x) {
+              const float2 xf = unpack_bf16x2(v[j]);
+              a[2 * j] += f.x * (xf.x - mean[u]) * rstd[u];
+              a[2 * j + 1] += f.y * (xf.y - mean[u]) * rstd[u];
+            }
+          }
+        }
+      }
+    }
+    for (; r < rows; r += stride) {
       float g[8], xv[8];
       if (vec) {
         uint4 gu = ld_nc_v4(dy + (long long)r * ld + col);
@@ -298,14 +337,20 @@ extern "C" int nkb_norm_bwd_dx(const void* dy, const void* x, const void* w, con
   NKB_NCH_DISPATCH(launch_bwd, dy, x, w, stats, dx, rows, C, rms, s);
 }
 
+// row splits: about two CTAs per SM, and at least COLSUM_UNROLL rows per warp when possible
+static int colsum_row_splits(int gx, int rows) {
+  int gy = (2 * 148 + gx - 1) / gx;
+  int max_gy = rows / (8 * nkb::COLSUM_UNROLL);
+  if (max_gy < 1) max_gy = 1;
+  if (gy > max_gy) gy = max_gy;
+  return gy < 1 ? 1 : gy;
+}
+
 extern "C" int nkb_colsum(const void* dy, const void* x, const float* stats, float* acc, int rows,
                           int C, long long ld, int rms, void* stream) {
   if ((C & 1) || (ld & 1)) return -3;
   int gx = (C + 255) / 256;
-  int gy = (8 * 148 + gx - 1) / gx;
-  int max_gy = (rows + 7) / 8;
-  if (gy > max_gy) gy = max_gy;
-  if (gy < 1) gy = 1;
+  int gy = colsum_row_splits(gx, rows);
   colsum_kernel<<<dim3(gx, gy), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), stats, acc, rows,
       C, ld, rms, nullptr, nullptr, nullptr, 0, 0);
@@ -321,10 +366,7 @@ extern "C" int nkb_colsum_fused(const void* dy, const void* x, const float* stat
                                 int rows, int C, long long ld, int rms, void* stream) {
   if ((C & 1) || (ld & 1) || !acc || !tickets) return -3;
   int gx = (C + 255) / 256;
-  int gy = (8 * 148 + gx - 1) / gx;
-  int max_gy = (rows + 7) / 8;
-  if (gy > max_gy) gy = max_gy;
-  if (gy < 1) gy = 1;
+  int gy = colsum_row_splits(gx, rows);
   colsum_kernel<<<dim3(gx, gy), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), stats, acc, rows,
       C, ld, rms, tickets, static_cast<__nv_bfloat16*>(out_a), static_cast<__nv_bfloat16*>(out_b),

@@ -79,6 +79,16 @@ def bench_norm(flush):
                       "GBps_min_traffic": round(3 * byts / ms_b / 1e6)}), flush=True)
 
 
+def bench_colsum(flush):
+    from .gemm import colsum
+    for (rows, C) in [(8192, 1024), (8192, 3072), (8192, 4096)]:
+        dy = torch.randn(rows, C, device="cuda").bfloat16()
+        out = torch.empty(C, device="cuda", dtype=torch.bfloat16)
+        ms = _time(lambda: colsum(dy, out), flush=flush)
+        print(json.dumps({"op": "colsum", "rows": rows, "C": C, "ms": round(ms, 4),
+                          "GBps": round(rows * C * 2 / ms / 1e6)}), flush=True)
+
+
 def bench_ce(flush):
     from . import cross_entropy_fwd_bwd
     T, V, ld = 8192, 50257, 50304
@@ -192,7 +202,7 @@ def main(argv):
     if which == "attn_one":
         return one_attn(argv)
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
-    table = {"gemm": bench_gemm, "norm": bench_norm, "ce": bench_ce, "adam": bench_adam,
+    table = {"gemm": bench_gemm, "colsum": bench_colsum, "norm": bench_norm, "ce": bench_ce, "adam": bench_adam,
              "attn": bench_attn}
     for name, fn in table.items():
         if which in ("all", name):
