@@ -27,6 +27,7 @@ _SIGS = {
                       i64, i32, vp, i64, vp, vp, i32, i32, i32, i32, vp, vp],
     "nkb_norm_fwd": [vp, vp, vp, vp, vp, i32, i32, f32, i32, vp],
     "nkb_norm_bwd_dx": [vp, vp, vp, vp, vp, i32, i32, i32, vp],
+    "nkb_norm_bwd_dx_res": [vp, vp, vp, vp, vp, i32, i32, i32, vp, vp],
     "nkb_colsum": [vp, vp, vp, vp, i32, i32, i64, i32, vp],
     "nkb_colsum_fused": [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i64, i32, vp],
     "nkb_f32_to_bf16": [vp, vp, i64, i32, vp],

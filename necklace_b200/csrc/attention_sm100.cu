@@ -617,35 +617,77 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
 #include "attention_bwd_pp.cuh"
 
-// delta[b,h,s] = sum_d o * do ; 8 lanes per row
+// delta[b,h,s] = sum_d o * do ; 8 lanes per row, DELTA_ROWS rows per thread so that each
+// thread has several independent 16-byte loads in flight
+constexpr int DELTA_ROWS = 4;
 __global__ void __launch_bounds__(256)
 attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
                   float* __restrict__ delta, int B, int H, int S, int D, long long ob, long long oh,
                   long long os) {
-  const long long row = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 3;
+  const long long slot = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 3;
   const int sub = threadIdx.x & 7;
   const long long total = (long long)B * H * S;
-  float acc = 0.f;
-  if (row < total) {
-    const int s = (int)(row % S);
-    const int h = (int)((row / S) % H);
-    const int b = (int)(row / ((long long)S * H));
-    const long long off = (long long)b * ob + (long long)h * oh + (long long)s * os;
-    for (int d = sub * 8; d < D; d += 64) {
-      uint4 x = *reinterpret_cast<const uint4*>(o + off + d);
-      uint4 y = *reinterpret_cast<const uint4*>(dout + off + d);
-      uint32_t xu[4] = {x.x, x.y, x.z, x.w}, yu[4] = {y.x, y.y, y.z, y.w};
+  const long long nslots = (long long)gridDim.x * (blockDim.x >> 3);
+  float acc[DELTA_ROWS];
+  uint4 xs[DELTA_ROWS], ys[DELTA_ROWS];
+  if (D == 64) {
+    // one 16-byte piece of o and of dout per lane and row: issue all loads, then reduce
+#pragma unroll
+    for (int u = 0; u < DELTA_ROWS; ++u) {
+      const long long row = slot + u * nslots;
+      xs[u] = ys[u] = make_uint4(0, 0, 0, 0);
+      if (row < total) {
+        const int s = (int)(row % S);
+        const int h = (int)((row / S) % H);
+        const int b = (int)(row / ((long long)S * H));
+        const long long off = (long long)b * ob + (long long)h * oh + (long long)s * os + sub * 8;
+        xs[u] = ld_nc_v4(o + off);
+        ys[u] = ld_nc_v4(dout + off);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < DELTA_ROWS; ++u) {
+      const uint32_t xu[4] = {xs[u].x, xs[u].y, xs[u].z, xs[u].w};
+      const uint32_t yu[4] = {ys[u].x, ys[u].y, ys[u].z, ys[u].w};
+      acc[u] = 0.f;
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        float2 f = unpack_bf16x2(xu[q]), g = unpack_bf16x2(yu[q]);
-        acc += f.x * g.x + f.y * g.y;
+        const float2 f = unpack_bf16x2(xu[q]), g = unpack_bf16x2(yu[q]);
+        acc[u] += f.x * g.x + f.y * g.y;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int u = 0; u < DELTA_ROWS; ++u) {
+      const long long row = slot + u * nslots;
+      acc[u] = 0.f;
+      if (row < total) {
+        const int s = (int)(row % S);
+        const int h = (int)((row / S) % H);
+        const int b = (int)(row / ((long long)S * H));
+        const long long off = (long long)b * ob + (long long)h * oh + (long long)s * os;
+        for (int d = sub * 8; d < D; d += 64) {
+          const uint4 x = ld_nc_v4(o + off + d);
+          const uint4 y = ld_nc_v4(dout + off + d);
+          const uint32_t xu[4] = {x.x, x.y, x.z, x.w}, yu[4] = {y.x, y.y, y.z, y.w};
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float2 f = unpack_bf16x2(xu[q]), g = unpack_bf16x2(yu[q]);
+            acc[u] += f.x * g.x + f.y * g.y;
+          }
+        }
       }
     }
   }
-  acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-  acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-  acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-  if (row < total && sub == 0) delta[row] = acc;
+#pragma unroll
+  for (int u = 0; u < DELTA_ROWS; ++u) {
+    float a = acc[u];
+    a += __shfl_xor_sync(0xffffffffu, a, 1);
+    a += __shfl_xor_sync(0xffffffffu, a, 2);
+    a += __shfl_xor_sync(0xffffffffu, a, 4);
+    const long long row = slot + u * nslots;
+    if (row < total && sub == 0) delta[row] = a;
+  }
 }
 
 // dq (bf16, strided) <- dq_acc (fp32 [B,H,S,D])
@@ -860,7 +902,7 @@ extern "C" int nkb_attn_bwd(const void* q, const void* k, const void* v, const v
   if ((rc = make_tmap_bshd(&tv, v, B, H, S, D, sb, sh, ss))) return rc;
   if ((rc = make_tmap_bshd(&tdo, dout, B, H, S, D, ob, oh, os))) return rc;
   const long long rows = (long long)B * H * S;
-  attn_delta_kernel<<<(unsigned)((rows * 8 + 255) / 256), 256, 0, s>>>(
+  attn_delta_kernel<<<(unsigned)((rows * 8 + 256 * DELTA_ROWS - 1) / (256 * DELTA_ROWS)), 256, 0, s>>>(
       static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(dout), delta, B, H, S,
       D, ob, oh, os);
   AttnBwdArgs a;

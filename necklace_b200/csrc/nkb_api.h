@@ -33,6 +33,9 @@ int nkb_norm_fwd(const void* x, const void* w, const void* b, void* y, float* st
                  int C, float eps, int rms, void* stream);
 int nkb_norm_bwd_dx(const void* dy, const void* x, const void* w, const float* stats, void* dx,
                     int rows, int C, int rms, void* stream);
+// same, plus dres [rows, C] (bf16): the gradient that reaches x along a residual connection
+int nkb_norm_bwd_dx_res(const void* dy, const void* x, const void* w, const float* stats, void* dx,
+                        int rows, int C, int rms, const void* dres, void* stream);
 // Column sums over rows: acc[0][c] += sum_r dy[r,c]*xhat[r,c] (if x) ; acc[1][c] += sum_r dy[r,c].
 // `acc` is fp32 [2][C] scratch that must be zero on entry.
 int nkb_colsum(const void* dy, const void* x, const float* stats, float* acc, int rows, int C,

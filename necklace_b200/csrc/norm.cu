@@ -93,7 +93,10 @@ template <int NCH>
 __global__ void __launch_bounds__(128)
 norm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                    const __nv_bfloat16* __restrict__ w, const float* __restrict__ stats,
-                   __nv_bfloat16* __restrict__ dx, int rows, int C, int rms) {
+                   __nv_bfloat16* __restrict__ dx, int rows, int C, int rms,
+                   const __nv_bfloat16* __restrict__ dres) {
+  // dres (optional): gradient that reaches x along the residual path; added here so that no
+  // separate accumulation kernel runs
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -101,6 +104,7 @@ norm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   const float rstd = stats[2 * row + 1];
   const uint4* xp = reinterpret_cast<const uint4*>(x + (long long)row * C);
   const uint4* gp = reinterpret_cast<const uint4*>(dy + (long long)row * C);
+  const uint4* rp = reinterpret_cast<const uint4*>(dres + (dres ? (long long)row * C : 0));
   const uint4* wp = reinterpret_cast<const uint4*>(w);
   // dyw (dy*w) and xhat kept as packed bf16? keep fp32-exact by recomputing from
   // the cached raw bf16 inputs instead.
@@ -133,15 +137,20 @@ norm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
     const int e = c * 256 + lane * 8;
     if (e < C) {
       uint4 wv = __ldg(wp + c * 32 + lane);
+      uint4 rv = make_uint4(0, 0, 0, 0);
+      if (dres) rv = ld_nc_v4(rp + c * 32 + lane);
       uint32_t xu[4] = {xv[c].x, xv[c].y, xv[c].z, xv[c].w};
       uint32_t gu[4] = {gv[c].x, gv[c].y, gv[c].z, gv[c].w};
       uint32_t wu[4] = {wv.x, wv.y, wv.z, wv.w};
+      uint32_t ru[4] = {rv.x, rv.y, rv.z, rv.w};
       uint32_t o[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         float2 xf = unpack_bf16x2(xu[j]), gf = unpack_bf16x2(gu[j]), wf = unpack_bf16x2(wu[j]);
+        float2 rf = unpack_bf16x2(ru[j]);
         float h0 = (xf.x - mean) * rstd, h1 = (xf.y - mean) * rstd;
-        o[j] = pack_bf16x2(rstd * (gf.x * wf.x - s1 - h0 * s2), rstd * (gf.y * wf.y - s1 - h1 * s2));
+        o[j] = pack_bf16x2(rstd * (gf.x * wf.x - s1 - h0 * s2) + rf.x,
+                           rstd * (gf.y * wf.y - s1 - h1 * s2) + rf.y);
       }
       op[c * 32 + lane] = make_uint4(o[0], o[1], o[2], o[3]);
     }
@@ -299,10 +308,11 @@ static int launch_fwd(const void* x, const void* w, const void* b, void* y, floa
 }
 template <int NCH>
 static int launch_bwd(const void* dy, const void* x, const void* w, const float* stats, void* dx,
-                      int rows, int C, int rms, cudaStream_t s) {
+                      int rows, int C, int rms, const void* dres, cudaStream_t s) {
   norm_bwd_dx_kernel<NCH><<<(rows + 3) / 4, 128, 0, s>>>(
       static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
-      static_cast<const __nv_bfloat16*>(w), stats, static_cast<__nv_bfloat16*>(dx), rows, C, rms);
+      static_cast<const __nv_bfloat16*>(w), stats, static_cast<__nv_bfloat16*>(dx), rows, C, rms,
+      static_cast<const __nv_bfloat16*>(dres));
   return (int)cudaGetLastError();
 }
 
@@ -334,7 +344,16 @@ extern "C" int nkb_norm_bwd_dx(const void* dy, const void* x, const void* w, con
                                void* dx, int rows, int C, int rms, void* stream) {
   if (C % 8) return -3;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  NKB_NCH_DISPATCH(launch_bwd, dy, x, w, stats, dx, rows, C, rms, s);
+  NKB_NCH_DISPATCH(launch_bwd, dy, x, w, stats, dx, rows, C, rms, nullptr, s);
+}
+
+// dx = norm backward of dy + dres (the gradient arriving along the residual connection)
+extern "C" int nkb_norm_bwd_dx_res(const void* dy, const void* x, const void* w, const float* stats,
+                                   void* dx, int rows, int C, int rms, const void* dres,
+                                   void* stream) {
+  if (C % 8) return -3;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  NKB_NCH_DISPATCH(launch_bwd, dy, x, w, stats, dx, rows, C, rms, dres, s);
 }
 
 // row splits: about two CTAs per SM, and at least COLSUM_UNROLL rows per warp when possible

@@ -13,6 +13,8 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
+import os
+
 import torch
 import torch.nn as nn
 
@@ -42,6 +44,11 @@ class GPT2Config:
         return GPT2Config(n_layer=2, d_model=128, n_head=2, d_ff=512, vocab=1000, max_seq=128)
 
 
+# NKB_NORM_SPLIT=0 falls back to plain norms (autograd then adds the residual-path gradient
+# with a separate kernel); kept as a switch for A/B timing.
+_NORM_SPLIT = os.environ.get("NKB_NORM_SPLIT", "1") != "0"
+
+
 class Block(nn.Module):
     def __init__(self, cfg: GPT2Config, device=None):
         super().__init__()
@@ -59,11 +66,17 @@ class Block(nn.Module):
         self.w_fc2, self.b_fc2 = mk(C, cfg.d_ff, pstd), zb(C)
 
     def forward(self, x):
-        h = self.ln1(x)
+        if not _NORM_SPLIT:
+            h = self.ln1(x)
+        else:
+            x, h = self.ln1.split(x)  # the residual-path gradient is added in the norm backward
         qkv = linear(h, self.w_qkv, self.b_qkv)
         a = attention_qkv(qkv, self.n_head, True)
         x = linear(a, self.w_proj, self.b_proj, residual=x)
-        h = self.ln2(x)
+        if not _NORM_SPLIT:
+            h = self.ln2(x)
+        else:
+            x, h = self.ln2.split(x)
         return mlp(h, self.w_fc1, self.b_fc1, self.w_fc2, self.b_fc2, residual=x, act="gelu")
 
 

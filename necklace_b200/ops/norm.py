@@ -29,8 +29,11 @@ def norm_fwd(x2: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None, eps: flo
     return y, stats
 
 
-def norm_bwd(dy2, x2, w, stats, rms: bool, need_wgrad: bool = True, need_bgrad: bool = True):
-    """Returns (dx, dw_fp32 or None, db_fp32 or None); dw/db are fp32 rows of length C."""
+def norm_bwd(dy2, x2, w, stats, rms: bool, need_wgrad: bool = True, need_bgrad: bool = True,
+             dres=None):
+    """Returns (dx, dw_fp32 or None, db_fp32 or None); dw/db are fp32 rows of length C.
+    ``dres`` (optional, same shape as x2) is added to dx inside the kernel: the gradient that
+    reaches x along a residual connection."""
     rows, Cn = x2.shape
     if not on_gpu(x2):
         xf, gf, wf = x2.float(), dy2.float(), w.float()
@@ -39,13 +42,20 @@ def norm_bwd(dy2, x2, w, stats, rms: bool, need_wgrad: bool = True, need_bgrad: 
         a = gf * wf
         s1 = torch.zeros(rows, 1) if rms else a.mean(1, keepdim=True)
         s2 = (a * xhat).mean(1, keepdim=True)
-        dx = (rstd * (a - s1 - xhat * s2)).to(x2.dtype)
-        return dx, (gf * xhat).sum(0), gf.sum(0)
+        dx = rstd * (a - s1 - xhat * s2)
+        if dres is not None:
+            dx = dx + dres.float()
+        return dx.to(x2.dtype), (gf * xhat).sum(0), gf.sum(0)
     dy2 = dy2.contiguous()
     dx = torch.empty_like(x2)
     st = _lib.stream_ptr()
-    _lib.call("nkb_norm_bwd_dx", dy2.data_ptr(), x2.data_ptr(), w.data_ptr(), stats.data_ptr(),
-              dx.data_ptr(), rows, Cn, int(rms), st)
+    if dres is not None:
+        dres = dres.contiguous()
+        _lib.call("nkb_norm_bwd_dx_res", dy2.data_ptr(), x2.data_ptr(), w.data_ptr(),
+                  stats.data_ptr(), dx.data_ptr(), rows, Cn, int(rms), dres.data_ptr(), st)
+    else:
+        _lib.call("nkb_norm_bwd_dx", dy2.data_ptr(), x2.data_ptr(), w.data_ptr(), stats.data_ptr(),
+                  dx.data_ptr(), rows, Cn, int(rms), st)
     acc = None
     if need_wgrad or need_bgrad:
         acc = torch.zeros(2, Cn, dtype=torch.float32, device=x2.device)
@@ -83,20 +93,23 @@ class NormFn(torch.autograd.Function):
         return y.view(x.shape)
 
     @staticmethod
-    def backward(ctx, dy):
+    def backward(ctx, dy, dres=None):
         x2, w, stats = ctx.saved_tensors
         dy2 = dy.reshape(-1, dy.shape[-1])
+        if dres is not None:
+            dres = dres.reshape(-1, dres.shape[-1])
         b = ctx.b_ref
         bf16_targets = all(t is None or (getattr(t, "_nkb_grad", t).dtype == torch.bfloat16)
                            for t in (w, b))
         if not on_gpu(x2) or not bf16_targets:
-            dx, dw32, db32 = norm_bwd(dy2, x2, w, stats, ctx.rms)
+            dx, dw32, db32 = norm_bwd(dy2, x2, w, stats, ctx.rms, dres=dres)
             dw = _store_f32_grad(w, dw32)
             db = _store_f32_grad(b, db32) if b is not None else None
             return dx.view(dy.shape), dw, db, None, None
         # GPU: dx kernel, then one column-sum kernel that writes both parameter gradients as
         # bf16 straight into their destination (flat gradient buffer or a fresh tensor)
-        dx, _, _ = norm_bwd(dy2, x2, w, stats, ctx.rms, need_wgrad=False, need_bgrad=False)
+        dx, _, _ = norm_bwd(dy2, x2, w, stats, ctx.rms, need_wgrad=False, need_bgrad=False,
+                            dres=dres)
         dy2 = dy2.contiguous()
         rows, Cn = x2.shape
         tgt_w, acc_w, ret_w = _grad_target(w)
@@ -130,6 +143,23 @@ def _grad_done(p):
         cb(p)
 
 
+class NormSplitFn(torch.autograd.Function):
+    """``(x_alias, y) = (x, norm(x))``: the residual branch takes ``x_alias``.  Both gradients
+    arrive in one backward call, so the residual-path gradient is added inside the norm
+    backward kernel instead of by a separate accumulation kernel."""
+
+    @staticmethod
+    def forward(ctx, x, w, b, eps, rms):
+        y = NormFn.forward(ctx, x, w, b, eps, rms)
+        return x.view_as(x), y
+
+    @staticmethod
+    def backward(ctx, dres, dy):
+        if dy is None:  # only the residual branch was used
+            return dres, None, None, None, None
+        return NormFn.backward(ctx, dy, dres)
+
+
 class LayerNorm(nn.Module):
     def __init__(self, dim: int, eps: float = 1e-5, bias: bool = True, dtype=torch.bfloat16,
                  device=None):
@@ -141,6 +171,10 @@ class LayerNorm(nn.Module):
     def forward(self, x):
         return NormFn.apply(x, self.weight, self.bias, self.eps, False)
 
+    def split(self, x):
+        """``(x, norm(x))`` for a pre-norm residual block (see ``NormSplitFn``)."""
+        return NormSplitFn.apply(x, self.weight, self.bias, self.eps, False)
+
 
 class RMSNorm(nn.Module):
     def __init__(self, dim: int, eps: float = 1e-6, dtype=torch.bfloat16, device=None):
@@ -150,3 +184,7 @@ class RMSNorm(nn.Module):
 
     def forward(self, x):
         return NormFn.apply(x, self.weight, None, self.eps, True)
+
+    def split(self, x):
+        """``(x, norm(x))`` for a pre-norm residual block (see ``NormSplitFn``)."""
+        return NormSplitFn.apply(x, self.weight, None, self.eps, True)

@@ -139,3 +139,18 @@ def test_adam_sgd_cpu():
         ref.grad = g.clone()
         opt.step()
     assert torch.allclose(master, ref.data, atol=1e-6)
+
+
+def test_norm_split_cpu_matches_plain_composition():
+    import torch.nn.functional as F
+    from necklace_b200.ops.norm import LayerNorm
+    torch.manual_seed(3)
+    ln = LayerNorm(32, dtype=torch.float32)
+    x = torch.randn(5, 32, requires_grad=True)
+    xa, h = ln.split(x)
+    ((xa * 2 + h * 3).sum() + (h ** 2).sum()).backward()
+    g = x.grad.clone()
+    x.grad = None
+    h2 = F.layer_norm(x, (32,), ln.weight, ln.bias, ln.eps)
+    ((x * 2 + h2 * 3).sum() + (h2 ** 2).sum()).backward()
+    assert torch.allclose(g, x.grad, atol=1e-5)

@@ -329,3 +329,25 @@ def test_attention_backward_variants(impl, causal, B, H, S):
     for name, sl in (("dq", slice(0, C)), ("dk", slice(C, 2 * C)), ("dv", slice(2 * C, 3 * C))):
         err = _rel_err(dqkv[..., sl], ref_in.grad[..., sl])
         assert err < 3e-2, (name, err)
+
+
+@pytest.mark.parametrize("rms", [False, True])
+def test_norm_split_adds_residual_gradient(rms):
+    """(x, norm(x)) with the residual-path gradient added inside the norm backward kernel."""
+    from necklace_b200.ops.norm import LayerNorm, RMSNorm
+    torch.manual_seed(13)
+    C = 1024
+    mod = (RMSNorm(C, device=DEV) if rms else LayerNorm(C, device=DEV))
+    x = torch.randn(6, 40, C, device=DEV).bfloat16().requires_grad_(True)
+    g_res = torch.randn(6, 40, C, device=DEV).bfloat16()
+    g_h = torch.randn(6, 40, C, device=DEV).bfloat16()
+    xa, h = mod.split(x)
+    torch.autograd.backward([xa, h], [g_res, g_h])
+    xr = x.detach().float().requires_grad_(True)
+    w = mod.weight.detach().float()
+    if rms:
+        hr = xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + mod.eps) * w
+    else:
+        hr = F.layer_norm(xr, (C,), w, mod.bias.detach().float(), mod.eps)
+    torch.autograd.backward([xr, hr], [g_res.float(), g_h.float()])
+    assert _rel_err(x.grad, xr.grad) < 1e-2
