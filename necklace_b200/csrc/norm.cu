@@ -157,87 +157,86 @@ norm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   }
 }
 
-// Column sums.  Block = 32 x 8 threads: a lane owns 8 adjacent columns (one 16-byte
-// load per row), the 8 warps take interleaved rows; grid = (ceil(C/256), row_splits).
-// A warp keeps COLSUM_UNROLL rows (independent 16-byte loads) in flight and the grid is sized
-// to about two CTAs per SM, so that each SM has tens of KB outstanding (latency x bandwidth).
-constexpr int COLSUM_UNROLL = 8;
+// Column sums.  Block = 32 x 8 threads: a lane owns 8 adjacent columns (one 16-byte piece
+// per row), the 8 warps take interleaved rows; grid = (ceil(C/256), row_splits).
+// Each thread streams its pieces through a private ring of COLSUM_RING shared-memory slots
+// filled by cp.async (no registers held while in flight, no barriers: a thread only reads
+// what it copied itself), so a CTA keeps COLSUM_RING x 4 KB (x2 with the norm input) in
+// flight; plain register loads kept only ~1 load per warp outstanding at 2.4 TB/s.
+constexpr int COLSUM_RING = 8;
+constexpr int COLSUM_UNROLL = COLSUM_RING;  // rows per warp the row split aims for
+constexpr int COLSUM_SMEM_BYTES = 2 * COLSUM_RING * 256 * 16;
+__device__ __forceinline__ void colsum_cp16(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc)
+               : "memory");
+}
 __global__ void __launch_bounds__(256)
 colsum_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
               const float* __restrict__ stats, float* __restrict__ acc, int rows, int C,
               long long ld, int rms, int* __restrict__ tickets, __nv_bfloat16* __restrict__ out_a,
               __nv_bfloat16* __restrict__ out_b, int accum_a, int accum_b) {
-  __shared__ float sh[8][256 + 8];
+  // ring slots [which: dy | x][slot][thread] (16 bytes each); the reduction buffer reuses it
+  extern __shared__ __align__(16) uint8_t colsum_smem[];  // COLSUM_SMEM_BYTES, dynamic
+  uint4 (*ring)[COLSUM_RING][256] = reinterpret_cast<uint4 (*)[COLSUM_RING][256]>(colsum_smem);
+  float (*sh)[256 + 8] = reinterpret_cast<float (*)[256 + 8]>(colsum_smem);
   const int lane = threadIdx.x & 31, wy = threadIdx.x >> 5;
   const int col = blockIdx.x * 256 + lane * 8;
   float a[8], b[8];
 #pragma unroll
   for (int k = 0; k < 8; ++k) a[k] = b[k] = 0.f;
-  const bool vec = (col + 8 <= C) && ((ld & 7) == 0);
+  const bool vec = (col + 8 <= C) && ((ld & 7) == 0) &&
+                   ((reinterpret_cast<uintptr_t>(dy) & 15) == 0) &&
+                   (!x || (reinterpret_cast<uintptr_t>(x) & 15) == 0);
   const int stride = gridDim.y * 8;
-  if (col < C) {
-    int r = blockIdx.y * 8 + wy;
-    if (vec) {
-      // main part: COLSUM_UNROLL rows per step, all loads issued before any use
-      for (; r + (COLSUM_UNROLL - 1) * stride < rows; r += COLSUM_UNROLL * stride) {
-        uint4 gu[COLSUM_UNROLL], xu[COLSUM_UNROLL];
-        float mean[COLSUM_UNROLL], rstd[COLSUM_UNROLL];
-#pragma unroll
-        for (int u = 0; u < COLSUM_UNROLL; ++u) {
-          const long long rr = r + (long long)u * stride;
-          gu[u] = ld_nc_v4(dy + rr * ld + col);
-          xu[u] = make_uint4(0, 0, 0, 0);
-          mean[u] = 0.f;
-          rstd[u] = 0.f;
-          if (x) {
-            xu[u] = ld_nc_v4(x + rr * ld + col);
-            mean[u] = rms ? 0.f : stats[2 * rr];
-            rstd[u] = stats[2 * rr + 1];
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < COLSUM_UNROLL; ++u) {
-          const uint32_t w[4] = {gu[u].x, gu[u].y, gu[u].z, gu[u].w};
-          const uint32_t v[4] = {xu[u].x, xu[u].y, xu[u].z, xu[u].w};
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float2 f = unpack_bf16x2(w[j]);
-            b[2 * j] += f.x;
-            b[2 * j + 1] += f.y;
-            if (x) {
-              const float2 xf = unpack_bf16x2(v[j]);
-              a[2 * j] += f.x * (xf.x - mean[u]) * rstd[u];
-              a[2 * j + 1] += f.y * (xf.y - mean[u]) * rstd[u];
-            }
-          }
-        }
+  const int r0 = blockIdx.y * 8 + wy;
+  if (col < C && vec) {
+    const int n = r0 < rows ? (rows - r0 + stride - 1) / stride : 0;  // rows of this thread
+    auto issue = [&](int k) {
+      if (k < n) {
+        const long long off = (long long)(r0 + (long long)k * stride) * ld + col;
+        colsum_cp16(&ring[0][k % COLSUM_RING][threadIdx.x], dy + off);
+        if (x) colsum_cp16(&ring[1][k % COLSUM_RING][threadIdx.x], x + off);
       }
-    }
-    for (; r < rows; r += stride) {
-      float g[8], xv[8];
-      if (vec) {
-        uint4 gu = ld_nc_v4(dy + (long long)r * ld + col);
-        uint32_t w[4] = {gu.x, gu.y, gu.z, gu.w};
+      asm volatile("cp.async.commit_group;" ::: "memory");  // one group per step, empty or not
+    };
+#pragma unroll
+    for (int k = 0; k < COLSUM_RING; ++k) issue(k);
+    for (int k = 0; k < n; ++k) {
+      asm volatile("cp.async.wait_group %0;" ::"n"(COLSUM_RING - 1) : "memory");
+      const uint4 gu = ring[0][k % COLSUM_RING][threadIdx.x];
+      const uint32_t w[4] = {gu.x, gu.y, gu.z, gu.w};
+      if (x) {
+        const uint4 xu = ring[1][k % COLSUM_RING][threadIdx.x];
+        const uint32_t v[4] = {xu.x, xu.y, xu.z, xu.w};
+        const long long rr = r0 + (long long)k * stride;
+        const float mean = rms ? 0.f : stats[2 * rr];
+        const float rstd = stats[2 * rr + 1];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          float2 f = unpack_bf16x2(w[j]);
-          g[2 * j] = f.x; g[2 * j + 1] = f.y;
-        }
-        if (x) {
-          uint4 xu = ld_nc_v4(x + (long long)r * ld + col);
-          uint32_t v[4] = {xu.x, xu.y, xu.z, xu.w};
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            float2 f = unpack_bf16x2(v[j]);
-            xv[2 * j] = f.x; xv[2 * j + 1] = f.y;
-          }
+          const float2 f = unpack_bf16x2(w[j]), xf = unpack_bf16x2(v[j]);
+          b[2 * j] += f.x;
+          b[2 * j + 1] += f.y;
+          a[2 * j] += f.x * (xf.x - mean) * rstd;
+          a[2 * j + 1] += f.y * (xf.y - mean) * rstd;
         }
       } else {
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          g[k] = (col + k < C) ? __bfloat162float(dy[(long long)r * ld + col + k]) : 0.f;
-          xv[k] = (x && col + k < C) ? __bfloat162float(x[(long long)r * ld + col + k]) : 0.f;
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = unpack_bf16x2(w[j]);
+          b[2 * j] += f.x;
+          b[2 * j + 1] += f.y;
         }
+      }
+      issue(k + COLSUM_RING);  // refill the slot just read
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+  } else if (col < C) {
+    for (int r = r0; r < rows; r += stride) {
+      float g[8], xv[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        g[k] = (col + k < C) ? __bfloat162float(dy[(long long)r * ld + col + k]) : 0.f;
+        xv[k] = (x && col + k < C) ? __bfloat162float(x[(long long)r * ld + col + k]) : 0.f;
       }
 #pragma unroll
       for (int k = 0; k < 8; ++k) b[k] += g[k];
@@ -356,9 +355,24 @@ extern "C" int nkb_norm_bwd_dx_res(const void* dy, const void* x, const void* w,
   NKB_NCH_DISPATCH(launch_bwd, dy, x, w, stats, dx, rows, C, rms, dres, s);
 }
 
-// row splits: about two CTAs per SM, and at least COLSUM_UNROLL rows per warp when possible
+// the ring needs more than the 48 KB a kernel gets without opting in (once per device)
+static int colsum_configure() {
+  static bool done[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+  if (!done[dev]) {
+    if (cudaFuncSetAttribute(nkb::colsum_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             nkb::COLSUM_SMEM_BYTES) != cudaSuccess)
+      return -1;
+    done[dev] = true;
+  }
+  return 0;
+}
+
+// row splits: about three CTAs per SM (64 KB of ring each), and at least COLSUM_UNROLL rows per
+// warp when possible
 static int colsum_row_splits(int gx, int rows) {
-  int gy = (2 * 148 + gx - 1) / gx;
+  int gy = (3 * 148 + gx - 1) / gx;
   int max_gy = rows / (8 * nkb::COLSUM_UNROLL);
   if (max_gy < 1) max_gy = 1;
   if (gy > max_gy) gy = max_gy;
@@ -370,7 +384,8 @@ extern "C" int nkb_colsum(const void* dy, const void* x, const float* stats, flo
   if ((C & 1) || (ld & 1)) return -3;
   int gx = (C + 255) / 256;
   int gy = colsum_row_splits(gx, rows);
-  colsum_kernel<<<dim3(gx, gy), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  if (colsum_configure()) return -6;
+  colsum_kernel<<<dim3(gx, gy), 256, nkb::COLSUM_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), stats, acc, rows,
       C, ld, rms, nullptr, nullptr, nullptr, 0, 0);
   return (int)cudaGetLastError();
@@ -386,7 +401,8 @@ extern "C" int nkb_colsum_fused(const void* dy, const void* x, const float* stat
   if ((C & 1) || (ld & 1) || !acc || !tickets) return -3;
   int gx = (C + 255) / 256;
   int gy = colsum_row_splits(gx, rows);
-  colsum_kernel<<<dim3(gx, gy), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  if (colsum_configure()) return -6;
+  colsum_kernel<<<dim3(gx, gy), 256, nkb::COLSUM_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), stats, acc, rows,
       C, ld, rms, tickets, static_cast<__nv_bfloat16*>(out_a), static_cast<__nv_bfloat16*>(out_b),
       accum_a, accum_b);
