@@ -87,7 +87,9 @@ attn_bwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const int niter = nq - i0;
   const long long bh_off = ((long long)b * a.H + h) * a.S;
 
-  if (threadIdx.x == 0) {
+  // The TMA thread sets up the barriers and puts the first loads (K, V, two Q / dO stages) in
+  // flight before the CTA-wide syncs, so they overlap the TMEM allocation and zero fill.
+  if (threadIdx.x == 384) {
     mbar_init(kv_full, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&qdo_full[i], 1);
@@ -106,6 +108,14 @@ attn_bwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     mbar_init(stg_full, 128);
     *abort_flag = 0;
     mbar_fence_init();
+    mbar_expect_tx(kv_full, 2 * TILE);
+    tma_load_4d(sK, &tmK, kv_full, 0, h, j * 128, b);
+    tma_load_4d(sV, &tmV, kv_full, 0, h, j * 128, b);
+    for (int it = 0; it < 2 && it < niter; ++it) {
+      mbar_expect_tx(&qdo_full[it], 2 * TILE);
+      tma_load_4d(sQ + it * TILE, &tmQ, &qdo_full[it], 0, h, (i0 + it) * 128, b);
+      tma_load_4d(sDO + it * TILE, &tmDO, &qdo_full[it], 0, h, (i0 + it) * 128, b);
+    }
   }
   if (warp == 13) {
     tmem_alloc(tmem_slot, TMEM_COLS);
@@ -138,10 +148,7 @@ attn_bwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       auto load_tile = [&](uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, int row0) {
         tma_load_4d(dst, tm, bar, 0, h, row0, b);
       };
-      mbar_expect_tx(kv_full, 2 * TILE);
-      load_tile(sK, &tmK, kv_full, j * 128);
-      load_tile(sV, &tmV, kv_full, j * 128);
-      for (int it = 0; it < niter; ++it) {
+      for (int it = 2; it < niter; ++it) {  // stages 0 and 1 were filled before the syncs
         const int st = it & 1;
         if (!mbar_wait(&qdo_empty[st], ((it >> 1) & 1) ^ 1, abort_flag)) {
           att_error(a.status, abort_flag, NKB_ERR_EMPTY_WAIT);

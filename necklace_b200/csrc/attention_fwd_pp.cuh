@@ -91,7 +91,13 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const int n1 = (m0 + 128 < a.S) ? (a.causal ? min(nkv_all, 2 * qb + 2) : nkv_all) : 0;
   const int nmax = max(n0, n1);
 
-  if (threadIdx.x == 0) {
+  // The TMA thread sets up the barriers and puts the first loads (Q, two K / V stages) in
+  // flight before the CTA-wide sync, so they overlap the TMEM allocation and the sync.
+  auto load_tile = [&](uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, int row0) {
+#pragma unroll
+    for (int kd = 0; kd < NKD; ++kd) tma_load_4d(dst + kd * 16384, tm, bar, kd * 64, h, row0, b);
+  };
+  if (threadIdx.x == 256) {
     mbar_init(q_full, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1);
@@ -105,6 +111,15 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
     *abort_flag = 0;
     mbar_fence_init();
+    mbar_expect_tx(q_full, 2 * TILE);
+    load_tile(sQ, &tmQ, q_full, m0);
+    load_tile(sQ + TILE, &tmQ, q_full, m0 + 128);
+    for (int j = 0; j < 2 && j < nmax; ++j) {
+      mbar_expect_tx(&k_full[j], TILE);
+      load_tile(sK + j * TILE, &tmK, &k_full[j], j * 128);
+      mbar_expect_tx(&v_full[j], TILE);
+      load_tile(sV + j * TILE, &tmV, &v_full[j], j * 128);
+    }
   }
   if (warp == 9) {
     tmem_alloc(tmem_slot, TMEM_COLS);
@@ -119,14 +134,7 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (warp == 8) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      auto load_tile = [&](uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, int row0) {
-#pragma unroll
-        for (int kd = 0; kd < NKD; ++kd) tma_load_4d(dst + kd * 16384, tm, bar, kd * 64, h, row0, b);
-      };
-      mbar_expect_tx(q_full, 2 * TILE);
-      load_tile(sQ, &tmQ, q_full, m0);
-      load_tile(sQ + TILE, &tmQ, q_full, m0 + 128);
-      for (int j = 0; j < nmax; ++j) {
+      for (int j = 2; j < nmax; ++j) {  // stages 0 and 1 were filled before the sync
         const int st = j & 1;
         const uint32_t par = ((j >> 1) & 1) ^ 1;
         if (!mbar_wait(&k_empty[st], par, abort_flag)) {
