@@ -338,7 +338,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 struct AttnBwdArgs {
   const float* lse;
   const float* delta;
-  float* dq_acc;            // [B,H,S,D] fp32, zero on entry
+  float* dq_acc;            // [B,H,S,D] fp32, cleared by the delta kernel of the same call
   __nv_bfloat16* dk;
   __nv_bfloat16* dv;        // same strides as k / v
   int B, H, S;
@@ -623,7 +623,9 @@ constexpr int DELTA_ROWS = 4;
 __global__ void __launch_bounds__(256)
 attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
                   float* __restrict__ delta, int B, int H, int S, int D, long long ob, long long oh,
-                  long long os) {
+                  long long os, float* __restrict__ dq_acc) {
+  // also clears the fp32 dQ accumulator [B*H*S, D] (each lane its D/8 floats of the row), so no
+  // separate fill kernel runs before the backward kernel
   const long long slot = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 3;
   const int sub = threadIdx.x & 7;
   const long long total = (long long)B * H * S;
@@ -687,6 +689,10 @@ attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __re
     a += __shfl_xor_sync(0xffffffffu, a, 4);
     const long long row = slot + u * nslots;
     if (row < total && sub == 0) delta[row] = a;
+    if (dq_acc && row < total) {
+      float4* z = reinterpret_cast<float4*>(dq_acc + row * D + sub * (D / 8));
+      for (int i = 0; i < D / 32; ++i) z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
   }
 }
 
@@ -717,6 +723,14 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 static EncodeTiledFn att_encode_fn() {
+  // The encode call is a driver-API entry and needs the primary context current on the calling
+  // thread; a thread that has made no runtime call yet (e.g. an autograd worker whose first
+  // work is this library) has none, so bind it once per thread.
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    cudaFree(nullptr);
+    ctx_bound = true;
+  }
   static EncodeTiledFn fn = nullptr;
   if (!fn) {
     void* p = nullptr;
@@ -904,7 +918,7 @@ extern "C" int nkb_attn_bwd(const void* q, const void* k, const void* v, const v
   const long long rows = (long long)B * H * S;
   attn_delta_kernel<<<(unsigned)((rows * 8 + 256 * DELTA_ROWS - 1) / (256 * DELTA_ROWS)), 256, 0, s>>>(
       static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(dout), delta, B, H, S,
-      D, ob, oh, os);
+      D, ob, oh, os, dq_acc);
   AttnBwdArgs a;
   a.lse = lse; a.delta = delta; a.dq_acc = dq_acc;
   a.dk = static_cast<__nv_bfloat16*>(dk);

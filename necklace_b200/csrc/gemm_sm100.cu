@@ -1284,6 +1284,14 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 static EncodeTiledFn get_encode_fn() {
+  // The encode call is a driver-API entry and needs the primary context current on the calling
+  // thread; a thread that has made no runtime call yet (e.g. an autograd worker whose first
+  // work is this library) has none, so bind it once per thread.
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    cudaFree(nullptr);
+    ctx_bound = true;
+  }
   static EncodeTiledFn fn = nullptr;
   if (!fn) {
     void* p = nullptr;

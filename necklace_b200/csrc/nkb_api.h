@@ -99,6 +99,7 @@ int nkb_sumsq(const void* src, int src_fp32, long long n, float* out_accum, void
 int nkb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int H,
                  int S, int D, long long sb, long long sh, long long ss, long long ob,
                  long long oh, long long os, float scale, int causal, int* status, void* stream);
+// delta: [B,H,S] fp32 scratch; dq_acc: [B,H,S,D] fp32 scratch (both written by the call itself).
 int nkb_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout,
                  const float* lse, void* dq, void* dk, void* dv, float* delta, float* dq_acc,
                  int B, int H, int S, int D, long long sb, long long sh, long long ss,

@@ -109,7 +109,7 @@ def attn_bwd(qkv, out, lse, dout, H: int, causal: bool = True):
     dqkv = torch.empty_like(qkv)
     dq, dk, dv, *_ = _split(dqkv, H)
     delta = torch.empty(B, H, S, dtype=torch.float32, device=qkv.device)
-    dq_acc = torch.zeros(B, H, S, D, dtype=torch.float32, device=qkv.device)
+    dq_acc = torch.empty(B, H, S, D, dtype=torch.float32, device=qkv.device)  # cleared by the delta kernel
     _lib.call("nkb_attn_bwd", q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
               dout.data_ptr(), lse.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
               delta.data_ptr(), dq_acc.data_ptr(), B, H, S, D, S * 3 * C, D, 3 * C, S * C, D, C,
