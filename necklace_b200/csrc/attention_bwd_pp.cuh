@@ -11,14 +11,11 @@
 //   warps 8-11  dQ writer: TMEM -> registers -> swizzled fp32 tile in shared memory ->
 //               one TMA reduce-add into the fp32 dQ accumulator (no per-thread atomics).
 //   warp 12     TMA producer (K, V once; Q, dO double-buffered).
-//   warps 13-14 tcgen05.mma issuers, one per compute warpgroup: each 64-query half of a
-//               block has its own S^T / dP^T columns, barriers and issuing thread, so the
-//               tensor pipe works for one half while the other warpgroup computes (an
-//               issuing thread blocks while the pipe is busy; one thread for both halves
-//               serialised them).  The second issuer also issues dQ = dS K of the block.
-//   warp 15     idle (completes the fourth warpgroup for setmaxnreg).
+//   warp 13     tcgen05.mma issuer.  dQ of block i-1 is issued behind S^T / dP^T of block
+//               i, so it runs while the compute warpgroups work on block i.
+//   warps 14-15 idle (they complete the fourth warpgroup for setmaxnreg).
 //
-//   TMEM columns: S^T [0,128) (half w at 64w; its P^T over [64w, 64w+32))
+//   TMEM columns: S^T [0,128) (P^T of warpgroup w over [64w, 64w+32))
 //                 dP^T [128,256) (dS^T likewise)  dV [256,320)  dK [320,384)  dQ [384,448)
 //
 // lse / delta of the query block are staged in shared memory (they index columns here),
@@ -65,17 +62,15 @@ attn_bwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint64_t* kv_full = bars + 0;
   uint64_t* qdo_full = bars + 1;   // [2]
   uint64_t* qdo_empty = bars + 3;  // [2]
-  uint64_t* sdp_full = bars + 5;   // [2] per half: S^T / dP^T ready
-  uint64_t* pds_full = bars + 7;   // [2] per half: P^T / dS^T written (4 compute warps)
-  uint64_t* dq_full = bars + 9;
-  uint64_t* dq_free = bars + 10;   // 4 dQ-writer warps
-  uint64_t* acc_full = bars + 11;  // both issuers
-  uint64_t* ld_ready = bars + 12;  // [2] lse / delta of a query block staged (256 threads)
-  uint64_t* stg_free = bars + 14;  // dQ staging tile reusable
-  uint64_t* stg_full = bars + 15;  // dQ staging tile written (128 threads)
-  uint64_t* dq_done = bars + 16;   // [2] dQ MMA of block i retired (index i & 1): its dS^T buffer is free
-  uint64_t* ds_ready = bars + 18;  // [2] half 0 of dS^T of block i (index i & 1) is in shared memory
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
+  uint64_t* sdp_full = bars + 5;
+  uint64_t* pds_full = bars + 6;   // 8 compute warps
+  uint64_t* dq_full = bars + 7;
+  uint64_t* dq_free = bars + 8;    // 4 dQ-writer warps
+  uint64_t* acc_full = bars + 9;
+  uint64_t* ld_ready = bars + 10;  // [2] lse / delta of a query block staged (256 threads)
+  uint64_t* stg_free = bars + 12;  // dQ staging tile reusable
+  uint64_t* stg_full = bars + 13;  // dQ staging tile written (128 threads)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -87,35 +82,23 @@ attn_bwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const int niter = nq - i0;
   const long long bh_off = ((long long)b * a.H + h) * a.S;
 
-  // The TMA thread sets up the barriers and puts the first loads (K, V, two Q / dO stages) in
-  // flight before the CTA-wide syncs, so they overlap the TMEM allocation and zero fill.
-  if (threadIdx.x == 384) {
+  if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&qdo_full[i], 1);
-      mbar_init(&qdo_empty[i], 2);  // both issuers release a Q / dO stage
-      mbar_init(&sdp_full[i], 1);
-      mbar_init(&pds_full[i], 4);
-      mbar_init(&dq_done[i], 1);
-      mbar_init(&ds_ready[i], 4);
+      mbar_init(&qdo_empty[i], 1);
     }
+    mbar_init(sdp_full, 1);
+    mbar_init(pds_full, 8);
     mbar_init(dq_full, 1);
     mbar_init(dq_free, 4);
-    mbar_init(acc_full, 2);
+    mbar_init(acc_full, 1);
     mbar_init(&ld_ready[0], 256);
     mbar_init(&ld_ready[1], 256);
     mbar_init(stg_free, 1);
     mbar_init(stg_full, 128);
     *abort_flag = 0;
     mbar_fence_init();
-    mbar_expect_tx(kv_full, 2 * TILE);
-    tma_load_4d(sK, &tmK, kv_full, 0, h, j * 128, b);
-    tma_load_4d(sV, &tmV, kv_full, 0, h, j * 128, b);
-    for (int it = 0; it < 2 && it < niter; ++it) {
-      mbar_expect_tx(&qdo_full[it], 2 * TILE);
-      tma_load_4d(sQ + it * TILE, &tmQ, &qdo_full[it], 0, h, (i0 + it) * 128, b);
-      tma_load_4d(sDO + it * TILE, &tmDO, &qdo_full[it], 0, h, (i0 + it) * 128, b);
-    }
   }
   if (warp == 13) {
     tmem_alloc(tmem_slot, TMEM_COLS);
@@ -125,20 +108,6 @@ attn_bwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // dV / dK accumulate from two issuing threads whose first MMAs are not ordered against
-  // each other, so the accumulators start from explicit zeros and every MMA accumulates
-  if (warp < 4) {
-    uint32_t z[16];
-#pragma unroll
-    for (int i = 0; i < 16; ++i) z[i] = 0u;
-#pragma unroll
-    for (int c = 0; c < 8; ++c)
-      tmem_st_32x16(tmem_base + (uint32_t(warp * 32) << 16) + DV_COL + c * 16, z);
-    tmem_st_wait();
-    tc_fence_before();
-  }
-  __syncthreads();
-  tc_fence_after();
 
   if (warp >= 12) {
     // =================================================================== control
@@ -148,7 +117,10 @@ attn_bwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       auto load_tile = [&](uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, int row0) {
         tma_load_4d(dst, tm, bar, 0, h, row0, b);
       };
-      for (int it = 2; it < niter; ++it) {  // stages 0 and 1 were filled before the syncs
+      mbar_expect_tx(kv_full, 2 * TILE);
+      load_tile(sK, &tmK, kv_full, j * 128);
+      load_tile(sV, &tmV, kv_full, j * 128);
+      for (int it = 0; it < niter; ++it) {
         const int st = it & 1;
         if (!mbar_wait(&qdo_empty[st], ((it >> 1) & 1) ^ 1, abort_flag)) {
           att_error(a.status, abort_flag, NKB_ERR_EMPTY_WAIT);
@@ -158,84 +130,87 @@ attn_bwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         load_tile(sQ + st * TILE, &tmQ, &qdo_full[st], (i0 + it) * 128);
         load_tile(sDO + st * TILE, &tmDO, &qdo_full[st], (i0 + it) * 128);
       }
-    } else if ((warp == 13 || warp == 14) && lane == 0) {
-      // ------------------------------------- MMA issuer of query half w = warp - 13
-      const int w = warp - 13;
-      constexpr uint32_t idesc_s = umma_idesc_bf16(128, 64, 0, 0);   // S^T, dP^T halves
+    } else if (warp == 13 && lane == 0) {
+      // -------------------------------------------------------------- MMA issuer
+      constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);  // S^T, dP^T
       constexpr uint32_t idesc_ts = umma_idesc_bf16(128, D, 0, 1);   // dV, dK: A from TMEM
       constexpr uint32_t idesc_dq = umma_idesc_bf16(128, D, 1, 1);   // dQ: both MN-major
-      // descriptors are built once; per MMA only the start-address field (16-byte units)
-      // moves.  Half w of a Q / dO tile starts 64 rows = 8192 bytes in.
-      const uint32_t hoff = (uint32_t)w * (8192 >> 4);
+      // descriptors are built once; per MMA only the start-address field (16-byte units) moves
       const uint64_t dK_k = umma_desc_sw128(smem_u32(sK), 16, 1024);      // K, K-major (A of S^T)
       const uint64_t dV_k = umma_desc_sw128(smem_u32(sV), 16, 1024);      // V, K-major (A of dP^T)
       const uint64_t dK_mn = umma_desc_sw128(smem_u32(sK), 16384, 1024);  // K, MN-major (B of dQ)
-      const uint64_t dQ_k0 = umma_desc_sw128(smem_u32(sQ), 16, 1024) + hoff;    // B of S^T
-      const uint64_t dDO_k0 = umma_desc_sw128(smem_u32(sDO), 16, 1024) + hoff;  // B of dP^T
-      const uint64_t dQ_mn0 = umma_desc_sw128(smem_u32(sQ), 16384, 1024) + hoff;   // B of dK
-      const uint64_t dDO_mn0 = umma_desc_sw128(smem_u32(sDO), 16384, 1024) + hoff; // B of dV
-      const uint64_t dDS0 = umma_desc_sw128(smem_u32(sDS), 16384, 1024);  // dS^T, MN-major A
-      const uint32_t t_st = tmem_base + ST_COL + w * 64, t_dpt = tmem_base + DPT_COL + w * 64;
-      bool ok = true;
-      auto wait_or_fail = [&](uint64_t* bar, uint32_t parity, int code) {
-        if (ok && !mbar_wait(bar, parity, abort_flag)) {
-          att_error(a.status, abort_flag, code);
-          ok = false;
-        }
+      const uint64_t dQ_k0 = umma_desc_sw128(smem_u32(sQ), 16, 1024);     // Q, K-major (B of S^T)
+      const uint64_t dDO_k0 = umma_desc_sw128(smem_u32(sDO), 16, 1024);
+      const uint64_t dQ_mn0 = umma_desc_sw128(smem_u32(sQ), 16384, 1024);   // Q, MN-major (B of dK)
+      const uint64_t dDO_mn0 = umma_desc_sw128(smem_u32(sDO), 16384, 1024);
+      const uint64_t dDS0 = umma_desc_sw128(smem_u32(sDS), 16384, 1024);    // dS^T, MN-major A
+      auto issue_dq = [&](int it) {
+        const uint64_t dds = dDS0 + (uint32_t)(it & 1) * (32768 >> 4);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)  // 16 keys per MMA
+          umma_bf16_ss(tmem_base + DQ_COL, dds + k * 128, dK_mn + k * 128, idesc_dq,
+                       k > 0 ? 1u : 0u);
+        umma_commit(dq_full);
       };
-      wait_or_fail(kv_full, 0, NKB_ERR_TMA_WAIT);
+      bool ok = mbar_wait(kv_full, 0, abort_flag);
+      if (!ok) att_error(a.status, abort_flag, NKB_ERR_TMA_WAIT);
       for (int it = 0; it < niter && ok; ++it) {
         const int st = it & 1;
-        wait_or_fail(&qdo_full[st], (it >> 1) & 1, NKB_ERR_TMA_WAIT);
-        if (!ok) break;
+        if (!mbar_wait(&qdo_full[st], (it >> 1) & 1, abort_flag)) {
+          att_error(a.status, abort_flag, NKB_ERR_TMA_WAIT);
+          ok = false;
+          break;
+        }
         tc_fence_after();
         const uint32_t soff = (uint32_t)st * (TILE >> 4);
-        // S^T_w = K Q_w^T ; dP^T_w = V dO_w^T.  This thread issued the dV / dK MMAs that read
-        // the previous P^T_w / dS^T_w, and its MMAs run in order.
+        // S^T = K Q^T ; dP^T = V dO^T   (the tensor pipe runs in order, so the P^T / dS^T
+        // of the previous block have been consumed before these overwrite them)
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          umma_bf16_ss(t_st, dK_k + k * 2, dQ_k0 + soff + k * 2, idesc_s, k > 0 ? 1u : 0u);
+          umma_bf16_ss(tmem_base + ST_COL, dK_k + k * 2, dQ_k0 + soff + k * 2, idesc_s,
+                       k > 0 ? 1u : 0u);
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          umma_bf16_ss(t_dpt, dV_k + k * 2, dDO_k0 + soff + k * 2, idesc_s, k > 0 ? 1u : 0u);
-        // Warpgroup 0 refills the dS^T buffer of block it-2 once this commit lands; the dQ MMA
-        // that reads it belongs to the other issuer, so its retirement is waited for here.
-        // (dq_done[b] advances once per two blocks and never runs ahead of this wait.)
-        if (w == 0 && it >= 2) wait_or_fail(&dq_done[it & 1], ((it >> 1) - 1) & 1, NKB_ERR_ACC_FREE);
-        if (!ok) break;
-        umma_commit(&sdp_full[w]);
-        wait_or_fail(&pds_full[w], it & 1, NKB_ERR_ACC_WAIT);
-        if (!ok) break;
-        tc_fence_after();
-        // dV += P^T_w dO_w ; dK += dS^T_w Q_w (64 queries: 4 MMAs each, A from TMEM: 16
-        // queries = 8 columns of bf16 pairs).  The accumulators were zeroed at start, so both
-        // issuers always accumulate and their order does not matter.
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-          umma_bf16_ts(tmem_base + DV_COL, t_st + k * 8, dDO_mn0 + soff + k * 128, idesc_ts, 1u);
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-          umma_bf16_ts(tmem_base + DK_COL, t_dpt + k * 8, dQ_mn0 + soff + k * 128, idesc_ts, 1u);
-        umma_commit(&qdo_empty[st]);
-        if (w == 1) {
-          // dQ = dS K of this block: both halves of dS^T are in shared memory and the writer
-          // has read the previous dQ.  (Warpgroup 0 may be a block ahead, so its half is
-          // signalled on a barrier that alternates with the block index: a parity wait on
-          // pds_full[0] could miss a phase.)
-          wait_or_fail(&ds_ready[it & 1], (it >> 1) & 1, NKB_ERR_ACC_WAIT);
-          if (it > 0) wait_or_fail(dq_free, (it - 1) & 1, NKB_ERR_ACC_FREE);
-          if (!ok) break;
+          umma_bf16_ss(tmem_base + DPT_COL, dV_k + k * 2, dDO_k0 + soff + k * 2, idesc_s,
+                       k > 0 ? 1u : 0u);
+        umma_commit(sdp_full);
+        if (it > 0) {
+          // dQ of the previous block, once the writer has read the one before it
+          if (it > 1 && !mbar_wait(dq_free, (it - 2) & 1, abort_flag)) {
+            att_error(a.status, abort_flag, NKB_ERR_ACC_FREE);
+            ok = false;
+            break;
+          }
           tc_fence_after();
-          const uint64_t dds = dDS0 + (uint32_t)(it & 1) * (32768 >> 4);
+          issue_dq(it - 1);
+        }
+        if (!mbar_wait(pds_full, it & 1, abort_flag)) {
+          att_error(a.status, abort_flag, NKB_ERR_ACC_WAIT);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        // dV += P^T dO ; dK += dS^T Q   (contraction over the 128 queries; A from TMEM:
+        // 16 queries = 8 columns of bf16 pairs, warpgroup w's columns start at 64w)
 #pragma unroll
-          for (int k = 0; k < 8; ++k)  // 16 keys per MMA
-            umma_bf16_ss(tmem_base + DQ_COL, dds + k * 128, dK_mn + k * 128, idesc_dq,
-                         k > 0 ? 1u : 0u);
-          umma_commit(dq_full);
-          umma_commit(&dq_done[it & 1]);
+        for (int k = 0; k < 8; ++k)
+          umma_bf16_ts(tmem_base + DV_COL, tmem_base + ST_COL + (k >> 2) * 64 + (k & 3) * 8,
+                       dDO_mn0 + soff + k * 128, idesc_ts, (it > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_bf16_ts(tmem_base + DK_COL, tmem_base + DPT_COL + (k >> 2) * 64 + (k & 3) * 8,
+                       dQ_mn0 + soff + k * 128, idesc_ts, (it > 0 || k > 0) ? 1u : 0u);
+        umma_commit(&qdo_empty[st]);
+      }
+      if (ok && niter > 0) {
+        if (niter > 1 && !mbar_wait(dq_free, (niter - 2) & 1, abort_flag)) {
+          att_error(a.status, abort_flag, NKB_ERR_ACC_FREE);
+        } else {
+          tc_fence_after();
+          issue_dq(niter - 1);
+          umma_commit(acc_full);
         }
       }
-      if (ok && niter > 0) umma_commit(acc_full);
     }
   } else if (warp >= 8) {
     // ================================================================= dQ writer
@@ -312,7 +287,7 @@ attn_bwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
       const float* sL = sLD + (it & 1) * 256 + w * 64;
       const float* sDl = sL + 128;
-      if (!mbar_wait(&sdp_full[w], it & 1, abort_flag)) {
+      if (!mbar_wait(sdp_full, it & 1, abort_flag)) {
         att_error(a.status, abort_flag, NKB_ERR_ACC_WAIT);
         ok = false;
         break;
@@ -363,10 +338,7 @@ attn_bwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&pds_full[w]);
-        if (w == 0) mbar_arrive(&ds_ready[it & 1]);
-      }
+      if (lane == 0) mbar_arrive(pds_full);
       if (it + 1 < niter) {
         sLD[((it + 1) & 1) * 256 + tid] = nxt;
         mbar_arrive(&ld_ready[(it + 1) & 1]);

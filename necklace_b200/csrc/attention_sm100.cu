@@ -616,6 +616,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 }
 
 #include "attention_bwd_pp.cuh"
+#include "attention_bwd_pp2.cuh"
 
 // delta[b,h,s] = sum_d o * do ; 8 lanes per row, DELTA_ROWS rows per thread so that each
 // thread has several independent 16-byte loads in flight
@@ -841,7 +842,7 @@ static int make_tmap_dq(CUtensorMap* out, float* base, int BH, int S, int D) {
   return r == CUDA_SUCCESS ? 0 : -(int)r - 1000;
 }
 
-// 1: warp-specialised kernel (head dim 64), 0: serial kernel
+// 1: warp-specialised kernel (head dim 64), 2: its two-issuer variant, 0: serial kernel
 static int g_attn_bwd_impl = 1;
 
 static int launch_bwd_pp(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
@@ -857,6 +858,22 @@ static int launch_bwd_pp(const CUtensorMap& tq, const CUtensorMap& tk, const CUt
   }
   dim3 grid(a.B * a.H, (a.S + 127) / 128);
   attn_bwd_pp_kernel<<<grid, BWD2_THREADS, smem, s>>>(tq, tk, tv, tdo, tdq, a);
+  return (int)cudaGetLastError();
+}
+
+static int launch_bwd_pp2(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                          const CUtensorMap& tdo, const CUtensorMap& tdq, const AttnBwdArgs& a,
+                          cudaStream_t s) {
+  constexpr int smem = AttnBwd3Smem::BYTES;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_bwd_pp2_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid(a.B * a.H, (a.S + 127) / 128);
+  attn_bwd_pp2_kernel<<<grid, BWD3_THREADS, smem, s>>>(tq, tk, tv, tdo, tdq, a);
   return (int)cudaGetLastError();
 }
 
@@ -929,10 +946,11 @@ extern "C" int nkb_attn_bwd(const void* q, const void* k, const void* v, const v
   a.scale_log2 = scale * LOG2E;
   a.causal = causal;
   a.status = status;
-  if (D == 64 && g_attn_bwd_impl == 1) {
+  if (D == 64 && g_attn_bwd_impl >= 1) {
     CUtensorMap tdq;
     if ((rc = make_tmap_dq(&tdq, dq_acc, B * H, S, D))) return rc;
-    rc = launch_bwd_pp(tq, tk, tv, tdo, tdq, a, s);
+    rc = g_attn_bwd_impl == 2 ? launch_bwd_pp2(tq, tk, tv, tdo, tdq, a, s)
+                              : launch_bwd_pp(tq, tk, tv, tdo, tdq, a, s);
   } else {
     rc = D == 64 ? launch_bwd<64>(tq, tk, tv, tdo, a, s) : launch_bwd<128>(tq, tk, tv, tdo, a, s);
   }

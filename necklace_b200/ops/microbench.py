@@ -137,6 +137,8 @@ def bench_attn(flush):
         from .attention import set_bwd_impl
         set_bwd_impl(0)
         ms_b0 = _time(lambda: attn_bwd(qkv, out, lse, do, H, True), flush=flush)
+        set_bwd_impl(2)
+        ms_b2 = _time(lambda: attn_bwd(qkv, out, lse, do, H, True), flush=flush)
         set_bwd_impl(1)
         fl = 4.0 * B * H * S * S * D / 2  # causal
         q, k, v = (t.view(B, S, H, D).transpose(1, 2) for t in qkv.split(C, -1))
@@ -144,7 +146,8 @@ def bench_attn(flush):
             q, k, v, is_causal=True), flush=flush)
         print(json.dumps({"op": "attn", "B": B, "H": H, "S": S, "D": D, "fwd_ms": round(ms, 4),
                           "fwd_tflops": round(fl / ms / 1e9, 1), "bwd_ms": round(ms_b, 4),
-                          "bwd_serial_ms": round(ms_b0, 4), "bwd_tflops": round(2.5 * fl / ms_b / 1e9, 1),
+                          "bwd_serial_ms": round(ms_b0, 4), "bwd_two_issuer_ms": round(ms_b2, 4),
+                          "bwd_tflops": round(2.5 * fl / ms_b / 1e9, 1),
                           "torch_sdpa_fwd_ms": round(ms_t, 4)}), flush=True)
 
 
