@@ -640,8 +640,10 @@ attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __re
       const long long row = slot + u * nslots;
       xs[u] = ys[u] = make_uint4(0, 0, 0, 0);
       if (row < total) {
-        const int s = (int)(row % S);
-        const int h = (int)((row / S) % H);
+        // slots walk (b, s, h): neighbouring slots read neighbouring heads of one token, i.e.
+        // contiguous memory of the [B, S, H*D] tensors
+        const int h = (int)(row % H);
+        const int s = (int)((row / H) % S);
         const int b = (int)(row / ((long long)S * H));
         const long long off = (long long)b * ob + (long long)h * oh + (long long)s * os + sub * 8;
         xs[u] = ld_nc_v4(o + off);
@@ -665,8 +667,10 @@ attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __re
       const long long row = slot + u * nslots;
       acc[u] = 0.f;
       if (row < total) {
-        const int s = (int)(row % S);
-        const int h = (int)((row / S) % H);
+        // slots walk (b, s, h): neighbouring slots read neighbouring heads of one token, i.e.
+        // contiguous memory of the [B, S, H*D] tensors
+        const int h = (int)(row % H);
+        const int s = (int)((row / H) % S);
         const int b = (int)(row / ((long long)S * H));
         const long long off = (long long)b * ob + (long long)h * oh + (long long)s * os;
         for (int d = sub * 8; d < D; d += 64) {
@@ -689,9 +693,11 @@ attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __re
     a += __shfl_xor_sync(0xffffffffu, a, 2);
     a += __shfl_xor_sync(0xffffffffu, a, 4);
     const long long row = slot + u * nslots;
-    if (row < total && sub == 0) delta[row] = a;
+    const long long orow = row < total
+        ? ((row / ((long long)S * H)) * H + row % H) * S + (row / H) % S : 0;  // (b*H + h)*S + s
+    if (row < total && sub == 0) delta[orow] = a;
     if (dq_acc && row < total) {
-      float4* z = reinterpret_cast<float4*>(dq_acc + row * D + sub * (D / 8));
+      float4* z = reinterpret_cast<float4*>(dq_acc + orow * D + sub * (D / 8));
       for (int i = 0; i < D / 32; ++i) z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
   }
