@@ -38,7 +38,9 @@ _SIGS = {
     "nkb_embed_bwd": [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp],
     "nkb_adam_flat": [vp, vp, vp, vp, i32, vp, i64, f32, f32, f32, f32, f32, f32, f32, f32, vp,
                       vp],
-    "nkb_sgd_flat": [vp, vp, vp, i32, vp, i64, f32, f32, f32, f32, i32, vp],
+    "nkb_hyper_advance": [vp, f32, f32, vp],
+    "nkb_sgd_flat": [vp, vp, vp, i32, vp, i64, f32, f32, f32, f32, i32, vp, vp],
+    "nkb_clip_coef": [vp, vp, f32, f32, vp],
     "nkb_quant2_flat": [vp, i32, vp, vp, i64, f32, vp],
     "nkb_dequant2_flat": [vp, vp, i32, i64, f32, f32, i32, vp],
     "nkb_quant2_matrix": [vp, vp, vp, i32, i32, f32, vp],

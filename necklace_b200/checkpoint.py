@@ -25,26 +25,24 @@ import torch.distributed as dist
 
 
 # ----------------------------------------------------------------------- engine (dp / zero)
-def _gather_flat(t: torch.Tensor, sharded: bool, world: int, group=None) -> torch.Tensor:
-    if not sharded or world == 1:
-        return t.detach().float().cpu()
-    parts = [torch.empty_like(t) for _ in range(world)]
-    dist.all_gather(parts, t.contiguous(), group=group)
-    return torch.cat(parts).float().cpu()
+def _gather_flat(engine, t: torch.Tensor, group=None) -> torch.Tensor:
+    """Full-length fp32 copy on the CPU of a per-rank optimizer-state tensor (the engine
+    knows how its shards interleave: one slice per rank in every bucket)."""
+    return engine.gather_state(t.detach(), group).float().cpu()
 
 
 def engine_state(engine, epoch: int = 0, extra: dict | None = None) -> dict:
     """Consolidated state of a ``TrainEngine`` (collective when the engine is sharded)."""
     f = engine.flat
     pg = getattr(getattr(engine.group, "heap", None), "group", None) if engine.sharded else None
-    master = _gather_flat(engine.master, engine.sharded, engine.world, pg)
+    master = _gather_flat(engine, engine.master, pg)
     sd = OrderedDict()
     for name, p, off in zip(f.names, f.params, f.offsets):
         sd[name] = master[off:off + p.numel()].view(p.shape).clone()
     optim = {"kind": engine.optim.kind, "step": engine.step_count}
     for key in ("s1", "s2"):
         t = getattr(engine, key)
-        optim[key] = None if t is None else _gather_flat(t, engine.sharded, engine.world, pg)
+        optim[key] = None if t is None else _gather_flat(engine, t, pg)
     meta = {"epoch": epoch, "step": engine.step_count, "rng": torch.get_rng_state(),
             "layout": {"names": f.names, "offsets": f.offsets, "numel": f.numel,
                        "world": engine.world, "mode": engine.mode}}
@@ -59,10 +57,8 @@ def load_engine_state(engine, state: dict) -> dict:
     full = torch.zeros(f.numel, dtype=torch.float32)
     for name, p, off in zip(f.names, f.params, f.offsets):
         full[off:off + p.numel()] = state["state_dict"][name].reshape(-1).float()
-    n = engine.master.numel()
-    lo = engine.rank * n if engine.sharded else 0
     dev = engine.master.device
-    engine.master.copy_(full[lo:lo + n].to(dev))
+    engine.master.copy_(engine.shard_of(full).to(dev))
     f.flat.copy_(full.to(dev).to(f.flat.dtype))
     old = state["meta"]["layout"]
     for key in ("s1", "s2"):
@@ -76,8 +72,8 @@ def load_engine_state(engine, state: dict) -> dict:
             o_off = dict(zip(old["names"], old["offsets"]))
             for name, p, off in zip(f.names, f.params, f.offsets):
                 buf[off:off + p.numel()] = src[o_off[name]:o_off[name] + p.numel()]
-        dst.copy_(buf[lo:lo + n].to(dev))
-    engine.step_count = int(state["optim"].get("step", 0))
+        dst.copy_(engine.shard_of(buf).to(dev))
+    engine.set_step_count(int(state["optim"].get("step", 0)))
     if state["meta"].get("rng") is not None:
         torch.set_rng_state(state["meta"]["rng"])
     return state["meta"]

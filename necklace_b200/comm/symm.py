@@ -281,5 +281,5 @@ class TorchGroup:
                       weight_decay=weight_decay, step=step, grad_scale=grad_scale, hyper=hyper)
         else:
             sgd_step(master, s1, mine, pshard, lr=lr, momentum=beta1, weight_decay=weight_decay,
-                     first_step=first_step, grad_scale=grad_scale)
+                     first_step=first_step, grad_scale=grad_scale, hyper=hyper)
         self.all_gather(params)

@@ -270,12 +270,12 @@ struct OptArgs {
   float lr, beta1, beta2, eps, wd, c1, c2, gscale;
   int adam;        // 1 = Adam(W), 0 = SGD momentum
   int first_step;  // SGD: momentum buffer initialised from the gradient
-  const float* hyper;  // optional device floats {lr, c1, c2} overriding the host values
+  const float* hyper;  // optional device floats {lr, c1, c2, t, gmul}: override lr, c1, c2; gmul scales gscale
 };
 
 __global__ void __launch_bounds__(COMM_THREADS)
 rs_opt_ag_kernel(CommCtx c, OptArgs o) {
-  if (o.hyper) { o.lr = o.hyper[0]; o.c1 = o.hyper[1]; o.c2 = o.hyper[2]; }
+  if (o.hyper) { o.lr = o.hyper[0]; o.c1 = o.hyper[1]; o.c2 = o.hyper[2]; o.gscale *= o.hyper[4]; }
   const int e = begin_call(c);
   bool ok = cta_barrier(c, 2 * e - 1);  // everyone's gradients are complete
   if (ok) {

@@ -71,11 +71,16 @@ int nkb_embed_bwd(const long long* idx, const void* dout, void* dwte, void* dwpe
 int nkb_adam_flat(float* master, float* m, float* v, const void* grad, int grad_fp32,
                   void* param_bf16, long long n, float lr, float beta1, float beta2, float eps,
                   float weight_decay, float bias_c1, float bias_c2, float grad_scale,
-                  const float* hyper_dev /* optional device {lr, c1, c2} */, void* stream);
+                  const float* hyper_dev /* optional device {lr, c1, c2, t, gmul} */, void* stream);
+// hyper = device floats {lr, c1, c2, t}: t += 1 and the Adam bias corrections follow from t.
+int nkb_hyper_advance(float* hyper, float beta1, float beta2, void* stream);
 // SGD with momentum on flat buffers (torch.optim.SGD semantics, dampening 0).
 int nkb_sgd_flat(float* master, float* mom, const void* grad, int grad_fp32, void* param_bf16,
                  long long n, float lr, float momentum, float weight_decay, float grad_scale,
-                 int first_step, void* stream);
+                 int first_step, const float* hyper_dev /* optional {lr, .., .., .., gmul} */,
+                 void* stream);
+// hyper[4] = min(1, max_norm / (sqrt(*sumsq) * gscale)); hyper[5] = the norm.
+int nkb_clip_coef(float* hyper, const float* sumsq, float max_norm, float gscale, void* stream);
 // 2-bit threshold codec with error feedback over a flat fp32/bf16 vector:
 //   a = g[i] + residual[i]; code 01 if a >= thr, 10 if a <= -thr, else 00;
 //   residual[i] = a - decode(code); 16 codes per uint32, element i in bits [2(i%16), 2(i%16)+2).

@@ -24,7 +24,7 @@ adam_flat_kernel(float* __restrict__ master, float* __restrict__ m, float* __res
                  const void* __restrict__ grad, int grad_fp32, __nv_bfloat16* __restrict__ pbf,
                  long long n, float lr, float b1, float b2, float eps, float wd, float c1,
                  float c2, float gscale, const float* __restrict__ hyper) {
-  if (hyper) { lr = hyper[0]; c1 = hyper[1]; c2 = hyper[2]; }
+  if (hyper) { lr = hyper[0]; c1 = hyper[1]; c2 = hyper[2]; gscale *= hyper[4]; }
   const long long n4 = n >> 2;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
@@ -73,7 +73,8 @@ adam_flat_kernel(float* __restrict__ master, float* __restrict__ m, float* __res
 __global__ void __launch_bounds__(256)
 sgd_flat_kernel(float* __restrict__ master, float* __restrict__ mom, const void* __restrict__ grad,
                 int grad_fp32, __nv_bfloat16* __restrict__ pbf, long long n, float lr, float mu,
-                float wd, float gscale, int first_step) {
+                float wd, float gscale, int first_step, const float* __restrict__ hyper) {
+  if (hyper) { lr = hyper[0]; gscale *= hyper[4]; }
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
     float p = master[i];
@@ -257,9 +258,45 @@ static int grid_for(long long work_items) {
   return (int)b;
 }
 
+// hyper[4] = min(1, max_norm / (sqrt(sumsq) * gscale)): the multiplier that clips the global
+// gradient norm; applied inside the optimizer kernels.
+__global__ void clip_coef_kernel(float* hyper, const float* sumsq, float max_norm, float gscale) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    const float nrm = sqrtf(sumsq[0]) * gscale;
+    hyper[4] = fminf(1.f, max_norm / (nrm + 1e-6f));
+    hyper[5] = nrm;
+  }
+}
+
+// Advances the optimizer's per-step scalars on the device: hyper = {lr, c1, c2, t}.
+// t += 1; c1 = 1 / (1 - beta1^t); c2 = 1 / (1 - beta2^t).  One thread.  Keeping the step
+// count on the device makes the values a function of how many steps the stream has run,
+// not of when the host last rewrote a staging buffer (the host may enqueue many steps, or
+// replay a CUDA graph, far ahead of the device).
+__global__ void hyper_advance_kernel(float* hyper, float beta1, float beta2) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    const float t = hyper[3] + 1.f;
+    hyper[3] = t;
+    // exact powers in double: 1 - beta^t loses its digits in fp32 for beta close to 1
+    hyper[1] = (float)(1.0 / (1.0 - pow((double)beta1, (double)t)));
+    hyper[2] = (float)(1.0 / (1.0 - pow((double)beta2, (double)t)));
+  }
+}
+
 }  // namespace nkb
 
 using namespace nkb;
+
+extern "C" int nkb_clip_coef(float* hyper, const float* sumsq, float max_norm, float gscale,
+                             void* stream) {
+  clip_coef_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(hyper, sumsq, max_norm, gscale);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int nkb_hyper_advance(float* hyper, float beta1, float beta2, void* stream) {
+  hyper_advance_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(hyper, beta1, beta2);
+  return (int)cudaGetLastError();
+}
 
 extern "C" int nkb_adam_flat(float* master, float* m, float* v, const void* grad, int grad_fp32,
                              void* param_bf16, long long n, float lr, float beta1, float beta2,
@@ -280,11 +317,12 @@ extern "C" int nkb_adam_flat(float* master, float* m, float* v, const void* grad
 
 extern "C" int nkb_sgd_flat(float* master, float* mom, const void* grad, int grad_fp32,
                             void* param_bf16, long long n, float lr, float momentum,
-                            float weight_decay, float grad_scale, int first_step, void* stream) {
+                            float weight_decay, float grad_scale, int first_step,
+                            const float* hyper_dev, void* stream) {
   if (n <= 0) return 0;
   sgd_flat_kernel<<<grid_for(n), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       master, mom, grad, grad_fp32, static_cast<__nv_bfloat16*>(param_bf16), n, lr, momentum,
-      weight_decay, grad_scale, first_step);
+      weight_decay, grad_scale, first_step, hyper_dev);
   return (int)cudaGetLastError();
 }
 
