@@ -96,6 +96,38 @@ def load(filename: str) -> dict:
 
 
 # ------------------------------------------------------------------ tensor-parallel modules
+# A sharded parameter carries three attributes: ``model_parallel`` (True), ``partition_dim``
+# (the dimension that is split: 0 for column-parallel weights and their biases, 1 for
+# row-parallel weights) and ``partition_stride`` (how many independently split blocks are
+# packed along that dimension: 3 for a fused q/k/v projection, 2 for gate/up, default 1).
+# With stride s the full tensor is the sequence of pieces
+#     block 0 rank 0, block 0 rank 1, ..., block 1 rank 0, ...
+# which is the layout the reference builds with ``stride`` in
+# necklace/frmwrk/pytorch/mpnn/layers.py:40-72.
+def tp_concat(shards: list[torch.Tensor], dim: int = 0, stride: int = 1) -> torch.Tensor:
+    """Un-sharded tensor from the per-rank shards (rank order)."""
+    if len(shards) == 1:
+        return shards[0]
+    if stride == 1:
+        return torch.cat(list(shards), dim=dim)
+    pieces = [s.chunk(stride, dim=dim) for s in shards]
+    return torch.cat([pieces[r][j] for j in range(stride) for r in range(len(shards))], dim=dim)
+
+
+def tp_split(full: torch.Tensor, ws: int, rank: int, dim: int = 0, stride: int = 1
+             ) -> torch.Tensor:
+    """Rank ``rank``'s shard of an un-sharded tensor (inverse of ``tp_concat``)."""
+    if ws == 1:
+        return full
+    blocks = full.chunk(stride, dim=dim)
+    return torch.cat([b.chunk(ws, dim=dim)[rank] for b in blocks], dim=dim).contiguous()
+
+
+def _tp_attrs(p):
+    return (getattr(p, "model_parallel", False), getattr(p, "partition_dim", 0),
+            getattr(p, "partition_stride", 1))
+
+
 def gather_tp_state_dict(module: torch.nn.Module, mp_group=None) -> OrderedDict:
     """Un-sharded state dict of a tensor-parallel module (collective over the mp group)."""
     from .comm import fns
@@ -103,25 +135,31 @@ def gather_tp_state_dict(module: torch.nn.Module, mp_group=None) -> OrderedDict:
     out = OrderedDict()
     for name, p in module.named_parameters():
         t = p.detach()
-        if ws > 1 and getattr(p, "model_parallel", False):
-            dim = getattr(p, "partition_dim", 0)
+        sharded, dim, stride = _tp_attrs(p)
+        if ws > 1 and sharded:
             buf = torch.empty((ws,) + tuple(t.shape), dtype=t.dtype, device=t.device)
             fns.all_gather(buf, t.contiguous(), group=mp_group)
-            t = torch.cat(list(buf.unbind(0)), dim=dim)
+            t = tp_concat(list(buf.unbind(0)), dim, stride)
         out[name] = t.float().cpu()
     for name, b in module.named_buffers():
         out[name] = b.detach().cpu()
     return out
 
 
-def load_tp_state_dict(module: torch.nn.Module, full: dict, mp_group=None) -> None:
-    ws = mp_group.world_size if mp_group is not None else 1
-    rank = mp_group.rank if mp_group is not None else 0
+def load_tp_state_dict(module: torch.nn.Module, full: dict, mp_group=None, ws: int | None = None,
+                       rank: int | None = None) -> None:
+    """Load an un-sharded state dict into a module sharded ``ws`` ways (``ws`` / ``rank``
+    default to the mp group's)."""
+    if ws is None:
+        ws = mp_group.world_size if mp_group is not None else 1
+    if rank is None:
+        rank = mp_group.rank if mp_group is not None else 0
     with torch.no_grad():
         for name, p in module.named_parameters():
             t = full[name]
-            if ws > 1 and getattr(p, "model_parallel", False):
-                t = t.chunk(ws, dim=getattr(p, "partition_dim", 0))[rank]
+            sharded, dim, stride = _tp_attrs(p)
+            if ws > 1 and sharded:
+                t = tp_split(t, ws, rank, dim, stride)
             p.copy_(t.to(p.dtype).to(p.device))
 
 

@@ -139,7 +139,9 @@ class SPColumnParallelLinear(nn.Module):
         self.weight = nn.Parameter(full.chunk(p, 0)[r].contiguous().to(dtype).to(device))
         self.bias = nn.Parameter(torch.zeros(out_features // p, dtype=dtype, device=device)) \
             if bias else None
-        self.weight.model_parallel = True
+        self.weight.model_parallel, self.weight.partition_dim = True, 0
+        if self.bias is not None:
+            self.bias.model_parallel, self.bias.partition_dim = True, 0
 
     def forward(self, x_shard):
         return ag_linear(x_shard, self.weight, self.bias, self.group)
@@ -159,7 +161,7 @@ class SPRowParallelLinear(nn.Module):
         self.weight = nn.Parameter(full.chunk(p, 1)[r].contiguous().to(dtype).to(device))
         self.bias = nn.Parameter(torch.zeros(out_features, dtype=dtype, device=device)) \
             if bias else None
-        self.weight.model_parallel = True
+        self.weight.model_parallel, self.weight.partition_dim = True, 1
 
     def forward(self, x, residual=None):
         return linear_rs(x, self.weight, self.bias, residual, self.group)

@@ -1,6 +1,14 @@
 """Message (de)serialisation: msgpack with explicit numpy / torch tensor support,
 plus pickle-inside-msgpack and raw pickle helpers.
 
+``packb`` / ``unpackb`` carry every RPC request and reply, so they never pickle: an object
+they cannot describe raises ``TypeError`` on the sending side and an unknown extension
+record is returned as an opaque ``ExtType`` on the receiving side.  (Unpickling bytes that
+arrive on a socket would let anyone who can reach the port run code in this process.)
+Pickle is only used by the explicit helpers ``pkpackb`` / ``unpkpackb`` / ``pkl_*``, as in
+the reference, for payloads a caller has decided to trust.  ``ALLOW_PICKLE_FALLBACK = True``
+restores the implicit fallback for closed, trusted networks.
+
 The reference relies on the ``msgpack_numpy`` monkey patch
 (necklace/rpc/msgpck.py:14-45); here arrays travel as msgpack ``ExtType`` records
 (dtype, shape, raw bytes), torch tensors are sent as CPU arrays and come back as
@@ -14,6 +22,7 @@ import msgpack
 import numpy as np
 
 _EXT_NDARRAY, _EXT_TENSOR, _EXT_TUPLE, _EXT_PICKLE = 1, 2, 3, 4
+ALLOW_PICKLE_FALLBACK = False
 
 
 def _default(obj):
@@ -39,7 +48,10 @@ def _default(obj):
         return msgpack.ExtType(_EXT_TUPLE, packb(list(obj)))
     if isinstance(obj, (set, frozenset)):
         return sorted(obj)
-    return msgpack.ExtType(_EXT_PICKLE, pickle.dumps(obj, protocol=4))
+    if ALLOW_PICKLE_FALLBACK:
+        return msgpack.ExtType(_EXT_PICKLE, pickle.dumps(obj, protocol=4))
+    raise TypeError(f"cannot serialise {type(obj).__name__} for RPC; send plain data, arrays or "
+                    f"tensors, or use pkpackb() explicitly")
 
 
 def _ext_hook(code, data):
@@ -57,7 +69,7 @@ def _ext_hook(code, data):
         return np.frombuffer(raw, dtype=np.dtype(dt.decode())).reshape(shape).copy()
     if code == _EXT_TUPLE:
         return tuple(unpackb(data))
-    if code == _EXT_PICKLE:
+    if code == _EXT_PICKLE and ALLOW_PICKLE_FALLBACK:
         return pickle.loads(data)
     return msgpack.ExtType(code, data)
 

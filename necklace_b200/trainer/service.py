@@ -17,13 +17,16 @@ What differs:
   workers run every step, collective and optimizer update of that epoch without any
   RPC in between; ``stepwise=True`` replays the reference's per-phase protocol;
 * no fixed sleeps: communicator bring-up is acknowledged like any other phase;
-* failure handling: every phase has a deadline, workers send heartbeats, RPC errors
-  are checked; on a missing worker the scheduler broadcasts ``fn_abort`` and ends with
+* failure handling: every phase has a deadline, workers send heartbeats from a thread of
+  their own (so a long epoch or communicator bring-up does not silence them, and a worker
+  that died or hangs is noticed within ``heartbeat_timeout``, not ``phase_timeout``), RPC
+  errors are checked; on a missing worker the scheduler broadcasts ``fn_abort`` and ends with
   an error status instead of waiting forever (the reference never checks RPC returns
   and waits for registrations indefinitely, tndsnc.py:464-499).
 """
 from __future__ import annotations
 
+import threading
 import time
 import traceback
 
@@ -139,20 +142,39 @@ class SVCWorker(svctmp.TmplService):
         self.reg_deadline = time.time() + float(cfg.get("register_timeout", 120))
         self.exit_status = "running"
         self.q_put_state(Q_STATE_REG)
-        if self.hb_interval > 0:
-            self.register_timer(self.hb_interval, self.send_heartbeat)
+        self._hb_thread = None
+        self._hb_stop = threading.Event()
 
     # --------------------------------------------------------------------- timers
     def tm_to_sleep(self):
         return 0.0  # check_state blocks on the queue instead
 
-    def send_heartbeat(self):
-        if self.exit_status != "registered":
-            return
+    def _heartbeat_loop(self):
+        """Runs in its own daemon thread with its own client socket (ZeroMQ sockets must not
+        be shared between threads): the service thread may sit inside ``run_epoch`` for the
+        whole epoch, and the scheduler must still hear from this process."""
+        cli = self.svr.mk_rpc_cli(self.svr.scheduler_url, rank=self.rank,
+                                  zc_hb_timeout=max(self.hb_interval, 1.0))
         try:
-            self.svr.scheduler_cli().call("fn_heartbeat", self.rank, timeout=self.hb_interval)
-        except zrpc.RpcError:
-            pass
+            while not self._hb_stop.wait(self.hb_interval):
+                if self.exit_status != "registered":
+                    continue
+                try:
+                    cli.call("fn_heartbeat", self.rank, timeout=max(self.hb_interval, 1.0))
+                except zrpc.RpcError:
+                    pass
+        finally:
+            cli.close()
+
+    def start_heartbeats(self):
+        if self.hb_interval > 0 and self._hb_thread is None:
+            self._hb_thread = threading.Thread(target=self._heartbeat_loop, daemon=True,
+                                               name=f"heartbeat-{self.rank}")
+            self._hb_thread.start()
+
+    def stop(self):
+        self._hb_stop.set()
+        super().stop()
 
     def check_state(self, *args, **kwargs):
         state, a, k = self.q_get_state(timeout=0.05)
@@ -190,6 +212,7 @@ class SVCWorker(svctmp.TmplService):
             rep = svr.do_rpc_call(svr.scheduler_cli(), "fn_worker_reg", url=svr.url)
             if rep.get("ret") == "ok":
                 self.exit_status = "registered"
+                self.start_heartbeats()
                 return
         except zrpc.RpcError:
             pass
@@ -267,7 +290,8 @@ class Phase:
 
 class SVCScheduler(svctmp.TmplService):
     """cfg: ``url, workers (count), epochs, nccl_allreduce_typ, net_map, stepwise,
-    nccl_groups_grp_map, phase_timeout, heartbeat_timeout, register_timeout``."""
+    nccl_groups_grp_map, phase_timeout (600 s), heartbeat_timeout (15 s; 0 = off),
+    register_timeout``."""
 
     def __init__(self, cfg):
         super().__init__(cfg)
@@ -277,7 +301,9 @@ class SVCScheduler(svctmp.TmplService):
         self.typ = cfg.get("nccl_allreduce_typ", "grad")
         self.stepwise = bool(cfg.get("stepwise", False))
         self.phase_timeout = float(cfg.get("phase_timeout", 600))
-        self.hb_timeout = float(cfg.get("heartbeat_timeout", 0))  # 0 = heartbeats optional
+        # a worker that has sent a heartbeat once and then stays silent this long is taken
+        # for dead (workers send one every 2 s by default); 0 switches the check off
+        self.hb_timeout = float(cfg.get("heartbeat_timeout", 15))
         self.reg_deadline = time.time() + float(cfg.get("register_timeout", 300))
         self.net_map = cfg.get("net_map")
         self.grp_map = cfg.get("nccl_groups_grp_map") or {}

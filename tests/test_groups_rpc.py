@@ -96,6 +96,21 @@ def test_msgpack_roundtrip_arrays_tensors_tuples():
     assert msgpck.pkl_loads(msgpck.pkl_dumps((1, "a"))) == (1, "a")
 
 
+def test_rpc_serialiser_never_pickles_implicitly():
+    import pickle
+    import msgpack
+
+    class Thing:
+        pass
+
+    with pytest.raises(TypeError):
+        msgpck.packb({"x": Thing()})
+    # a forged pickle extension record is handed back opaque, not executed
+    evil = msgpack.packb(msgpack.ExtType(4, pickle.dumps(print)), use_bin_type=True)
+    out = msgpck.unpackb(evil)
+    assert isinstance(out, msgpack.ExtType)
+
+
 class _Echo(svctmp.TmplServer):
     def fn_echo(self, msg):
         m = self.msg_unpck(msg)

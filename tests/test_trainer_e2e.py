@@ -133,6 +133,8 @@ class _StallTrainer:
             raise RuntimeError("injected failure in the training step")
         if self.cfg.get("mode") == "stall" and msg["cmd"] == "run_epoch" and self.ti == 1:
             time.sleep(30)
+        if self.cfg.get("mode") == "slow" and msg["cmd"] == "run_epoch":
+            time.sleep(3)
         return {"ret": {"weights_sync": "weights_synced", "run_epoch": "epoch_end",
                         "next_epoch": "next_epoch"}[msg["cmd"]]}
 
@@ -170,6 +172,62 @@ def test_worker_failure_mid_step_aborts_everyone(tmp_path, mode, needle):
     ths[0].join(timeout=10)
     assert not ths[0].is_alive()
     assert results[0].exit_status == "aborted"
+
+
+def _worker_proc(tmp, rank, mode):
+    sys.path.insert(0, ROOT)
+    _worker_thread(tmp, rank, mode)
+
+
+@pytest.mark.timeout(120)
+def test_killed_worker_is_noticed_by_missing_heartbeats(tmp_path):
+    """Rank 1 is killed (SIGKILL) while it sits in ``run_epoch``.  The phase deadline is far
+    away (300 s); the scheduler must abort because the heartbeats stopped."""
+    import multiprocessing as mp
+    import threading
+    sys.path.insert(0, ROOT)
+    from necklace_b200.trainer.service import SVCScheduler
+    ctx = mp.get_context("spawn")
+    victim = ctx.Process(target=_worker_proc, args=(str(tmp_path), 1, "stall"), daemon=True)
+    victim.start()
+    results = {}
+    th = threading.Thread(target=lambda: results.__setitem__(0, _worker_thread(tmp_path, 0, "stall")),
+                          daemon=True)
+    th.start()
+    svc = SVCScheduler({"url": f"ipc://{tmp_path}/svr.ipc", "workers": 2, "epochs": 1,
+                        "phase_timeout": 300.0, "heartbeat_timeout": 1.5,
+                        "register_timeout": 60})
+
+    def killer():
+        while not any(fn == "fn_weights_sync_start" for fn, _ in svc.history):
+            time.sleep(0.05)
+        time.sleep(1.0)            # run_epoch has been sent; rank 1 is asleep inside it
+        victim.kill()
+
+    threading.Thread(target=killer, daemon=True).start()
+    t0 = time.time()
+    svc.loop()
+    assert svc.exit_status.startswith("aborted") and "heartbeat" in svc.exit_status, svc.exit_status
+    assert time.time() - t0 < 60
+    th.join(timeout=10)
+    assert results[0].exit_status == "aborted"
+
+
+@pytest.mark.timeout(120)
+def test_slow_but_healthy_epoch_is_not_aborted(tmp_path):
+    """An epoch longer than the heartbeat timeout: the heartbeat thread keeps talking while the
+    service thread is busy, so nobody is aborted."""
+    import threading
+    sys.path.insert(0, ROOT)
+    from necklace_b200.trainer.service import SVCScheduler
+    ths = [threading.Thread(target=_worker_thread, args=(tmp_path, r, "slow"), daemon=True)
+           for r in range(2)]
+    for t in ths:
+        t.start()
+    svc = SVCScheduler({"url": f"ipc://{tmp_path}/svr.ipc", "workers": 2, "epochs": 1,
+                        "phase_timeout": 60.0, "heartbeat_timeout": 1.0, "register_timeout": 30})
+    svc.loop()
+    assert svc.exit_status == "finished", svc.exit_status
 
 
 @pytest.mark.timeout(120)
