@@ -53,6 +53,8 @@ _SIGS = {
                      i64, i64, i64, i64, f32, i32, vp, vp],
     "nkb_comm_barrier": [vp, i64, i32, i32, vp, vp, vp],
     "nkb_comm_allreduce": [vp, i64, i64, i64, i32, f32, i32, i32, vp, vp, i32, vp],
+    "nkb_comm_reduce_scatter": [vp, i64, i64, i64, i32, f32, vp, i32, i32, vp, vp, i32, vp],
+    "nkb_comm_bcast": [vp, i64, i64, i64, i32, i32, i32, vp, vp, i32, vp],
     "nkb_comm_allgather": [vp, i64, i64, i64, i32, i32, vp, vp, i32, vp],
     "nkb_comm_dp_quant_allreduce": [vp, i64, vp, i32, vp, i64, i64, vp, i32, i64, f32, f32, i32,
                                     i32, vp, vp, i32, vp],

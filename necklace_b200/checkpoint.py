@@ -158,6 +158,16 @@ def load_tp_state_dict(module: torch.nn.Module, full: dict, mp_group=None, ws: i
         for name, p in module.named_parameters():
             t = full[name]
             sharded, dim, stride = _tp_attrs(p)
+            if sharded:
+                want = p.shape[dim] * ws
+                if t.shape[dim] != want and stride == 1:
+                    # padded vocabulary tables: the padding depends on the number of ranks
+                    if t.shape[dim] > want:
+                        t = t.narrow(dim, 0, want)
+                    else:
+                        pad = list(t.shape)
+                        pad[dim] = want - t.shape[dim]
+                        t = torch.cat([t, torch.zeros(pad, dtype=t.dtype)], dim=dim)
             if ws > 1 and sharded:
                 t = tp_split(t, ws, rank, dim, stride)
             p.copy_(t.to(p.dtype).to(p.device))

@@ -23,7 +23,7 @@ from .. import _lib
 from ..ops._common import status_word
 
 _FLAG_REGION = 8192          # bytes reserved per group for epoch flags (160 CTAs x 8 ranks)
-_MAX_GROUPS = 16
+_MAX_GROUPS = 32
 
 
 def _align(x: int, a: int) -> int:
@@ -132,6 +132,37 @@ class PeerGroup:
                   nbytes // self.world, *self._tail(max_ctas))
         _lib.count_launch()
         return full
+
+    def reduce_scatter(self, full: torch.Tensor, out: torch.Tensor | None = None,
+                       scale: float = 1.0, max_ctas=None) -> torch.Tensor:
+        """``out`` = this rank's 1/world slice (along dim 0) of the sum over the group of the
+        heap tensor ``full``; ``full`` itself is left untouched."""
+        W = self.world
+        n = full.numel()
+        shape = (full.shape[0] // W,) + tuple(full.shape[1:])
+        if out is None:
+            out = torch.empty(shape, dtype=full.dtype, device=full.device)
+        if W == 1:
+            out.copy_(full if scale == 1.0 else full * scale)
+            return out
+        assert full.is_contiguous() and out.is_contiguous() and out.numel() * W == n
+        assert n % (256 * W) == 0, "reduce_scatter needs numel % (256 * world) == 0"
+        _lib.call("nkb_comm_reduce_scatter", *self._ctx(), self.heap.offset_of(full), n,
+                  int(full.dtype == torch.float32), float(scale), out.data_ptr(),
+                  *self._tail(max_ctas))
+        _lib.count_launch()
+        return out
+
+    def broadcast(self, t: torch.Tensor, root: int = 0, max_ctas=None) -> torch.Tensor:
+        """Heap tensor ``t`` of the group's rank ``root`` is copied to every member's ``t``."""
+        if self.world == 1:
+            return t
+        nbytes = t.numel() * t.element_size()
+        assert t.is_contiguous() and nbytes % 16 == 0
+        _lib.call("nkb_comm_bcast", *self._ctx(), self.heap.offset_of(t), nbytes, int(root),
+                  *self._tail(max_ctas))
+        _lib.count_launch()
+        return t
 
     def dp_quant_allreduce(self, g, residual, codes, counts, out, thr, scale, max_ctas=None):
         """Fused 2-bit compressed all-reduce; ``codes`` / ``counts`` are heap tensors."""
@@ -252,6 +283,28 @@ class TorchGroup:
             dist.all_gather_into_tensor(full.view(-1), shard, group=self.group)
         return full
 
+    def reduce_scatter(self, full, out=None, scale: float = 1.0, max_ctas=None):
+        W = self.world
+        shape = (full.shape[0] // W,) + tuple(full.shape[1:])
+        if out is None:
+            out = torch.empty(shape, dtype=full.dtype, device=full.device)
+        if W == 1:
+            out.copy_(full)
+        else:
+            acc = full.float().contiguous()   # gloo has no reduce-scatter: reduce all, keep mine
+            dist.all_reduce(acc, group=self.group)
+            per = full.shape[0] // W
+            out.copy_(acc[self.rank * per:(self.rank + 1) * per].to(out.dtype))
+        if scale != 1.0:
+            out.mul_(scale)
+        return out
+
+    def broadcast(self, t, root: int = 0, max_ctas=None):
+        if self.world > 1:
+            dist.broadcast(t, src=self.ranks[root] if self.group is not None else root,
+                           group=self.group)
+        return t
+
     def dp_quant_allreduce(self, g, residual, codes, counts, out, thr, scale, max_ctas=None):
         from ..ops.quant import quantize_flat
         n = g.numel()
@@ -264,6 +317,31 @@ class TorchGroup:
             dist.all_reduce(tern, group=self.group)
         out.reshape(-1).copy_((tern * (thr * scale)).to(out.dtype))
         return out
+
+    def ag_gemm(self, x_full, w, *, out=None, bias=None, b_mn=False, ag_ctas=8, bn=0):
+        """Unfused stand-in of ``PeerGroup.ag_gemm``: all-gather the rows, then the GEMM."""
+        from ..ops.gemm import gemm
+        if self.world > 1:
+            R = x_full.shape[0] // self.world
+            mine = x_full[self.rank * R:(self.rank + 1) * R].clone()
+            dist.all_gather_into_tensor(x_full, mine, group=self.group)
+        return gemm(x_full, w, b_mn=b_mn, bias=bias, out=out)
+
+    def gemm_rs(self, x, w, *, out=None, bias=None, res=None, b_mn=False, rs_ctas=16, bn=0):
+        """Unfused stand-in of ``PeerGroup.gemm_rs``: GEMM (fp32 out), reduce-scatter of the
+        rows, then bias and residual."""
+        from ..ops.gemm import gemm
+        part = gemm(x, w, b_mn=b_mn, out_dtype=torch.float32)
+        mine = self.reduce_scatter(part)
+        if bias is not None:
+            mine = mine + bias.float()
+        if res is not None:
+            mine = mine + res.float()
+        mine = mine.to(x.dtype)
+        if out is not None:
+            out.copy_(mine)
+            return out
+        return mine
 
     def rs_opt_ag(self, grads, params, master, s1, s2, *, adam, lr, beta1=0.9, beta2=0.999,
                   eps=1e-8, weight_decay=0.0, step=1, grad_scale=1.0, first_step=False,

@@ -31,9 +31,11 @@ __global__ void __launch_bounds__(COMM_THREADS) barrier_kernel(CommCtx c) {
 // ------------------------------------------------------------ all-reduce (sum)
 // In place on the symmetric buffer at data_off.  Two-shot: rank r reduces shard
 // r from all members and stores the result into every member's buffer.
+// With `scatter_out` set the reduced shard is written there only (element 0 = first element
+// of this rank's shard) and nothing is stored to the peers: a reduce-scatter.
 template <bool FP32>
 __global__ void __launch_bounds__(COMM_THREADS)
-allreduce_kernel(CommCtx c, long long data_off, long long n, float scale) {
+allreduce_kernel(CommCtx c, long long data_off, long long n, float scale, void* scatter_out) {
   const int e = begin_call(c);
   bool ok = cta_barrier(c, 2 * e - 1);
   constexpr int VEC = FP32 ? 4 : 8;  // elements per 16 bytes
@@ -76,9 +78,13 @@ allreduce_kernel(CommCtx c, long long data_off, long long n, float scale) {
                          pack_bf16x2(acc[4] * scale, acc[5] * scale),
                          pack_bf16x2(acc[6] * scale, acc[7] * scale));
         }
-        for (int p = 0; p < c.world; ++p) {
-          const int m = (c.rank + p) % c.world;
-          *reinterpret_cast<uint4*>(static_cast<char*>(c.heap[m]) + data_off + i * esz) = o;
+        if (scatter_out) {
+          *reinterpret_cast<uint4*>(static_cast<char*>(scatter_out) + (i - s_lo) * esz) = o;
+        } else {
+          for (int p = 0; p < c.world; ++p) {
+            const int m = (c.rank + p) % c.world;
+            *reinterpret_cast<uint4*>(static_cast<char*>(c.heap[m]) + data_off + i * esz) = o;
+          }
         }
       } else {
         for (long long j = i; j < hi; ++j) {
@@ -89,8 +95,9 @@ allreduce_kernel(CommCtx c, long long data_off, long long n, float scale) {
                         : __bfloat162float(*reinterpret_cast<const volatile __nv_bfloat16*>(src));
           }
           acc *= scale;
-          for (int m = 0; m < c.world; ++m) {
-            char* dst = static_cast<char*>(c.heap[m]) + data_off + j * esz;
+          for (int m = 0; m < (scatter_out ? 1 : c.world); ++m) {
+            char* dst = scatter_out ? static_cast<char*>(scatter_out) + (j - s_lo) * esz
+                                    : static_cast<char*>(c.heap[m]) + data_off + j * esz;
             if (FP32) *reinterpret_cast<float*>(dst) = acc;
             else *reinterpret_cast<__nv_bfloat16*>(dst) = __float2bfloat16(acc);
           }
@@ -120,6 +127,33 @@ allgather_kernel(CommCtx c, long long data_off, long long shard_bytes) {
       for (int p = 1; p < c.world; ++p) {
         const int m = (c.rank + p) % c.world;
         reinterpret_cast<uint4*>(static_cast<char*>(c.heap[m]) + off)[i] = v;
+      }
+    }
+    cta_barrier(c, 2 * e);
+  }
+  finish_call(c, e);
+}
+
+// ------------------------------------------------------------------ broadcast
+// The root's bytes at data_off are pushed to the same offset of every other member
+// (the input batch / shape broadcast over a tensor-parallel group).
+__global__ void __launch_bounds__(COMM_THREADS)
+bcast_kernel(CommCtx c, long long data_off, long long nbytes, int root) {
+  const int e = begin_call(c);
+  bool ok = cta_barrier(c, 2 * e - 1);  // receivers are done with the previous content
+  if (ok) {
+    if (c.rank == root) {
+      const long long n16 = nbytes >> 4;
+      long long lo, hi;
+      split_range(n16, gridDim.x, blockIdx.x, 1, lo, hi);
+      const uint4* src =
+          reinterpret_cast<const uint4*>(static_cast<char*>(c.heap[c.rank]) + data_off);
+      for (long long i = lo + threadIdx.x; i < hi; i += COMM_THREADS) {
+        uint4 v = src[i];
+        for (int p = 1; p < c.world; ++p) {
+          const int m = (c.rank + p) % c.world;
+          reinterpret_cast<uint4*>(static_cast<char*>(c.heap[m]) + data_off)[i] = v;
+        }
       }
     }
     cta_barrier(c, 2 * e);
@@ -411,8 +445,38 @@ extern "C" int nkb_comm_allreduce(void** heap, long long flag_off, long long dat
   CommCtx c = make_ctx(heap, flag_off, rank, world, epoch, status);
   int grid = comm_grid(max_ctas, n / world / (fp32 ? 4 : 8));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (fp32) allreduce_kernel<true><<<grid, COMM_THREADS, 0, s>>>(c, data_off, n, scale);
-  else allreduce_kernel<false><<<grid, COMM_THREADS, 0, s>>>(c, data_off, n, scale);
+  if (fp32) allreduce_kernel<true><<<grid, COMM_THREADS, 0, s>>>(c, data_off, n, scale, nullptr);
+  else allreduce_kernel<false><<<grid, COMM_THREADS, 0, s>>>(c, data_off, n, scale, nullptr);
+  return (int)cudaGetLastError();
+}
+
+// Reduce-scatter: rank r receives the sum over members of elements [r*n/world, (r+1)*n/world)
+// of the symmetric buffer at data_off, times scale, in `out` (any device memory of this rank).
+// n must be a multiple of world * 256 elements so that the shards are equal.
+extern "C" int nkb_comm_reduce_scatter(void** heap, long long flag_off, long long data_off,
+                                       long long n, int fp32, float scale, void* out, int rank,
+                                       int world, int* epoch, int* status, int max_ctas,
+                                       void* stream) {
+  if (world > COMM_MAX_WORLD) return -4;
+  if ((data_off & 15) || (reinterpret_cast<uintptr_t>(out) & 15) || out == nullptr) return -3;
+  if (n % (256LL * world)) return -3;
+  CommCtx c = make_ctx(heap, flag_off, rank, world, epoch, status);
+  int grid = comm_grid(max_ctas, n / world / (fp32 ? 4 : 8));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (fp32) allreduce_kernel<true><<<grid, COMM_THREADS, 0, s>>>(c, data_off, n, scale, out);
+  else allreduce_kernel<false><<<grid, COMM_THREADS, 0, s>>>(c, data_off, n, scale, out);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int nkb_comm_bcast(void** heap, long long flag_off, long long data_off,
+                              long long nbytes, int root, int rank, int world, int* epoch,
+                              int* status, int max_ctas, void* stream) {
+  if (world > COMM_MAX_WORLD) return -4;
+  if ((data_off & 15) || (nbytes & 15) || root < 0 || root >= world) return -3;
+  CommCtx c = make_ctx(heap, flag_off, rank, world, epoch, status);
+  int grid = comm_grid(max_ctas, nbytes / 16);
+  bcast_kernel<<<grid, COMM_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(c, data_off, nbytes,
+                                                                            root);
   return (int)cudaGetLastError();
 }
 

@@ -125,6 +125,11 @@ int nkb_comm_allreduce(void** heap, long long flag_off, long long data_off, long
                        float scale, int rank, int world, int* epoch, int* status, int max_ctas,
                        void* stream);
 // member r's shard is at data_off + r*shard_bytes; afterwards every member has all shards
+int nkb_comm_reduce_scatter(void** heap, long long flag_off, long long data_off, long long n,
+                            int fp32, float scale, void* out, int rank, int world, int* epoch,
+                            int* status, int max_ctas, void* stream);
+int nkb_comm_bcast(void** heap, long long flag_off, long long data_off, long long nbytes, int root,
+                   int rank, int world, int* epoch, int* status, int max_ctas, void* stream);
 int nkb_comm_allgather(void** heap, long long flag_off, long long data_off, long long shard_bytes,
                        int rank, int world, int* epoch, int* status, int max_ctas, void* stream);
 // 2-bit compressed gradient all-reduce with error feedback, one kernel:

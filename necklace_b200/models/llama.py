@@ -1,7 +1,21 @@
 """Llama-style decoder (RMSNorm, rotary embedding, SwiGLU, no biases) on the native
 operators, with optional tensor parallelism (heads and FFN split over the mp group,
 Megatron column -> row pairs) so the same module serves the ``dp+pp+mp`` and
-``dp+zr+mp`` benchmark configurations.  The reference has no transformer model."""
+``dp+zr+mp`` benchmark configurations.  The reference has no transformer model.
+
+Two tensor-parallel layouts:
+
+``tp_group`` set (a ``PeerGroup``, or a ``TorchGroup`` as its unfused stand-in)
+    Sequence-parallel layout on the fused kernels.  The residual stream between blocks is
+    row-sharded (``[tokens/p, C]`` per rank); every column-parallel projection is one
+    all-gather -> GEMM kernel, every row-parallel projection one GEMM -> reduce-scatter
+    kernel (with the residual add in its epilogue), RMSNorm runs on the shard, the token
+    embedding and the output projection + cross-entropy are vocabulary-parallel.  No NCCL
+    call on the path.
+``mp > 1`` without ``tp_group``
+    The reference's layout (replicated activations, all-reduce after each row-parallel
+    linear through ``mpnn.mappings``); kept as the NCCL baseline.
+"""
 from __future__ import annotations
 
 from dataclasses import dataclass
@@ -25,6 +39,11 @@ class LlamaConfig:
     dtype: torch.dtype = torch.bfloat16
     mp: int = 1          # tensor-parallel ways
     mp_rank: int = 0
+    tp_group: object = None   # fused sequence-parallel path on this group (sets mp, mp_rank)
+
+    def __post_init__(self):
+        if self.tp_group is not None:
+            self.mp, self.mp_rank = self.tp_group.world, self.tp_group.rank
 
     @staticmethod
     def llama7b(**kw):
@@ -63,8 +82,9 @@ class LlamaBlock(nn.Module):
         P = lambda t: nn.Parameter(t.to(dt).to(device) if device is not None else t.to(dt))
         self.w_qkv, self.w_o = P(wqkv), P(wo)
         self.w_gu, self.w_down = P(torch.cat([wg, wu], 0)), P(wd)
-        for p in (self.w_qkv, self.w_o, self.w_gu, self.w_down):
-            p.model_parallel = mp > 1
+        for p, dim, stride in ((self.w_qkv, 0, 3), (self.w_o, 1, 1), (self.w_gu, 0, 2),
+                               (self.w_down, 1, 1)):
+            p.model_parallel, p.partition_dim, p.partition_stride = mp > 1, dim, stride
 
     def _reduce(self, x):
         if self.cfg.mp == 1:
@@ -78,7 +98,21 @@ class LlamaBlock(nn.Module):
         from ..frmwrk.pytorch.mpnn.mappings import copy_to_model_parallel_region
         return copy_to_model_parallel_region(x)
 
-    def forward(self, x):
+    def forward_sp(self, x, batch):
+        """``x``: this rank's ``[T/p, C]`` rows of the residual stream (T = batch * seq)."""
+        from ..ops.rotary import rope
+        from ..parallel.tensor import ag_linear, linear_rs
+        g, cfg = self.cfg.tp_group, self.cfg
+        qkv = ag_linear(self.ln1(x), self.w_qkv, None, g)               # [T, 3C/p]
+        qkv = rope(qkv.view(batch, -1, qkv.shape[-1]), self.n_head_local, cfg.rope_base)
+        a = attention_qkv(qkv, self.n_head_local, True)                 # [B, S, C/p]
+        x = linear_rs(a.view(-1, a.shape[-1]), self.w_o, None, x, g)    # [T/p, C] (+ residual)
+        f = swiglu(ag_linear(self.ln2(x), self.w_gu, None, g))          # [T, F/p]
+        return linear_rs(f, self.w_down, None, x, g)
+
+    def forward(self, x, batch=None):
+        if self.cfg.tp_group is not None:
+            return self.forward_sp(x, batch)
         h = self._copy(self.ln1(x))
         qkv = linear_rope(h, self.w_qkv, self.n_head_local, self.cfg.rope_base)
         a = attention_qkv(qkv, self.n_head_local, True)
@@ -93,27 +127,57 @@ class LlamaBlock(nn.Module):
         return x + self._reduce(linear(f, self.w_down))
 
 
+def _padded_vocab(cfg) -> int:
+    q = 128 * cfg.mp
+    return (cfg.vocab + q - 1) // q * q
+
+
 class LlamaEmbed(nn.Module):
+    """Token embedding; with ``tp_group`` the vocabulary rows are split over the group and the
+    output is this rank's ``[T/p, C]`` rows."""
+
     def __init__(self, cfg, device=None):
         super().__init__()
-        self.emb = Embedding((cfg.vocab + 127) // 128 * 128, cfg.d_model, None, dtype=cfg.dtype,
-                             device=device)
+        self.cfg = cfg
+        vp = _padded_vocab(cfg)
+        full = torch.randn(vp, cfg.d_model, generator=torch.Generator().manual_seed(5)) * 0.02
+        if cfg.tp_group is not None:
+            full = _shard(full, 0, cfg.mp, cfg.mp_rank)
+        self.wte = nn.Parameter(full.to(cfg.dtype).to(device if device is not None else "cpu"))
+        if cfg.tp_group is not None:
+            self.wte.model_parallel, self.wte.partition_dim = cfg.mp > 1, 0
 
     def forward(self, idx):
-        return self.emb(idx)
+        if self.cfg.tp_group is not None:
+            from ..parallel.tensor import vocab_parallel_embed
+            return vocab_parallel_embed(idx, self.wte, self.cfg.tp_group)
+        from ..ops.loss import EmbedFn
+        return EmbedFn.apply(idx, self.wte, None)
 
 
 class LlamaHead(nn.Module):
+    """Final norm, output projection and mean cross-entropy; vocabulary-parallel with
+    ``tp_group`` (reference counterpart: ``VocabParallelEmbedding`` + all-reduce,
+    necklace/frmwrk/pytorch/mpnn/layers.py:75-131)."""
+
     def __init__(self, cfg, device=None):
         super().__init__()
+        self.cfg = cfg
         self.vocab = cfg.vocab
         self.norm = RMSNorm(cfg.d_model, dtype=cfg.dtype, device=device)
-        vp = (cfg.vocab + 127) // 128 * 128
-        self.w_out = nn.Parameter((torch.randn(vp, cfg.d_model, generator=torch.Generator()
-                                               .manual_seed(7)) * 0.02).to(cfg.dtype)
-                                  .to(device if device is not None else "cpu"))
+        vp = _padded_vocab(cfg)
+        full = torch.randn(vp, cfg.d_model, generator=torch.Generator().manual_seed(7)) * 0.02
+        if cfg.tp_group is not None:
+            full = _shard(full, 0, cfg.mp, cfg.mp_rank)
+        self.w_out = nn.Parameter(full.to(cfg.dtype).to(device if device is not None else "cpu"))
+        if cfg.tp_group is not None:
+            self.w_out.model_parallel, self.w_out.partition_dim = cfg.mp > 1, 0
 
     def forward(self, x, targets):
+        if self.cfg.tp_group is not None:
+            from ..parallel.tensor import vocab_parallel_lm_head_loss
+            return vocab_parallel_lm_head_loss(self.norm(x), self.w_out, targets, self.vocab,
+                                               self.cfg.tp_group)
         return lm_head_loss(self.norm(x), self.w_out, targets, self.vocab)
 
 
@@ -128,11 +192,15 @@ class Llama(nn.Module):
         self.blocks = nn.ModuleList(LlamaBlock(cfg, i, device, seed) for i in layers)
         self.head = LlamaHead(cfg, device) if with_head else None
 
-    def forward(self, x, targets=None):
+    def forward(self, x, targets=None, batch=None):
+        """First stage: ``x`` = token ids ``[B, S]``; later stages: the previous stage's
+        activations.  With ``tp_group`` activations are ``[B*S/p, C]`` row shards and
+        ``batch`` (= B) must accompany them on stages without the embedding."""
         if self.embed is not None:
+            batch = x.shape[0]
             x = self.embed(x)
         for b in self.blocks:
-            x = b(x)
+            x = b(x, batch) if self.cfg.tp_group is not None else b(x)
         if self.head is not None and targets is not None:
             return self.head(x, targets)
         return x

@@ -36,6 +36,53 @@ def cross_entropy_fwd_bwd(logits: torch.Tensor, targets: torch.Tensor, vocab: in
     return losses
 
 
+def ce_stats(logits: torch.Tensor, targets: torch.Tensor, vocab_local: int, vocab_start: int
+             ) -> torch.Tensor:
+    """First half of a cross-entropy over a vocabulary that is split over ranks: per row
+    ``(max, sum exp(x - max), logit of the target if this slice owns it else 0)`` of the local
+    slice ``logits[:, :vocab_local]`` (global columns ``vocab_start ...``), fp32 ``[T, 3]``."""
+    T = logits.shape[0]
+    if not on_gpu(logits):
+        lf = logits[:, :vocab_local].float()
+        m = lf.max(1).values
+        s = torch.exp(lf - m[:, None]).sum(1)
+        loc = targets - vocab_start
+        own = (loc >= 0) & (loc < vocab_local)
+        tl = lf.gather(1, loc.clamp(0, vocab_local - 1)[:, None])[:, 0] * own
+        return torch.stack([m, s, tl], 1)
+    assert logits.dtype == torch.bfloat16 and logits.stride(1) == 1
+    stats = torch.empty(T, 3, dtype=torch.float32, device=logits.device)
+    _lib.call("nkb_ce_stats", logits.data_ptr(), targets.data_ptr(), stats.data_ptr(), T,
+              int(vocab_local), logits.stride(0), int(vocab_start), _lib.stream_ptr())
+    _lib.count_launch()
+    return stats
+
+
+def ce_grad(logits: torch.Tensor, targets: torch.Tensor, stats_g: torch.Tensor, vocab_local: int,
+            vocab_start: int, grad_scale: float) -> torch.Tensor:
+    """Second half: with the global ``(max, sumexp)`` per row (fp32 ``[T, 2]``) the local logits
+    are overwritten by ``(softmax - onehot) * grad_scale``."""
+    T = logits.shape[0]
+    if not on_gpu(logits):
+        lf = logits[:, :vocab_local].float()
+        valid = targets >= 0
+        g = torch.exp(lf - stats_g[:, :1]) / stats_g[:, 1:2]
+        loc = targets - vocab_start
+        own = (loc >= 0) & (loc < vocab_local) & valid
+        rows = torch.arange(T)[own]
+        g[rows, loc[own]] -= 1.0
+        g = g * (valid[:, None] * grad_scale)
+        logits.zero_()
+        logits[:, :vocab_local].copy_(g.to(logits.dtype))
+        return logits
+    stats_g = stats_g.contiguous()
+    _lib.call("nkb_ce_grad", logits.data_ptr(), targets.data_ptr(), stats_g.data_ptr(), T,
+              int(vocab_local), logits.stride(0), int(vocab_start), float(grad_scale),
+              _lib.stream_ptr())
+    _lib.count_launch()
+    return logits
+
+
 class LMHeadLossFn(torch.autograd.Function):
     """``mean CE(x @ W^T, targets)`` with the logits kept only as a bf16 scratch that
     is turned into its own gradient in place (no fp32 logits, no softmax tensor)."""
@@ -73,18 +120,25 @@ def lm_head_loss(x, w, targets, vocab):
     return LMHeadLossFn.apply(x, w, targets, vocab)
 
 
-def embed_fwd(idx, wte, wpe, S, vocab_start=0):
+def embed_fwd(idx, wte, wpe, S, vocab_start=0, out=None):
+    """Rows of ``wte`` (which holds vocabulary rows ``vocab_start ...``) for every index;
+    indices outside this slice give zero rows."""
     T = idx.numel()
     Cn = wte.shape[1]
     flat = idx.reshape(-1).contiguous()
     if not on_gpu(wte):
         loc = flat - vocab_start
         own = (loc >= 0) & (loc < wte.shape[0])
-        out = wte.float()[loc.clamp(0, wte.shape[0] - 1)] * own[:, None]
+        res = wte.float()[loc.clamp(0, wte.shape[0] - 1)] * own[:, None]
         if wpe is not None:
-            out = out + wpe.float()[torch.arange(T) % S]
-        return out.to(wte.dtype)
-    out = torch.empty(T, Cn, dtype=wte.dtype, device=wte.device)
+            res = res + wpe.float()[torch.arange(T) % S]
+        if out is not None:
+            out.copy_(res.to(out.dtype))
+            return out
+        return res.to(wte.dtype)
+    if out is None:
+        out = torch.empty(T, Cn, dtype=wte.dtype, device=wte.device)
+    assert out.is_contiguous() and out.shape == (T, Cn)
     _lib.call("nkb_embed_fwd", flat.data_ptr(), wte.data_ptr(), ptr(wpe), out.data_ptr(), T, S, Cn,
               int(vocab_start), wte.shape[0], _lib.stream_ptr())
     _lib.count_launch()

@@ -68,6 +68,29 @@ def _apply(qkv, H, base, backward, pos_offset):
     return qkv
 
 
+class RopeFn(torch.autograd.Function):
+    """Rotation of the q and k parts of a packed ``[B, S, 3C]`` projection, in place."""
+
+    @staticmethod
+    def forward(ctx, qkv, H, base, pos_offset):
+        ctx.H, ctx.base, ctx.pos_offset = H, base, pos_offset
+        ctx.mark_dirty(qkv)
+        return _apply(qkv, H, base, False, pos_offset)
+
+    @staticmethod
+    def backward(ctx, d):
+        d = d.contiguous()
+        if not d.is_cuda:
+            d = d.clone()
+        return _apply(d, ctx.H, ctx.base, True, ctx.pos_offset), None, None, None
+
+
+def rope(qkv, n_head, base=10000.0, pos_offset=0):
+    """Rotary embedding on an already computed packed projection (used where the projection
+    is a fused all-gather + GEMM)."""
+    return RopeFn.apply(qkv, n_head, base, pos_offset)
+
+
 def linear_rope(x, w, n_head, base=10000.0, pos_offset=0):
     """Packed QKV projection (``w`` = ``[q; k; v]`` rows, no bias) with rotary q / k."""
     return LinearRopeFn.apply(x, w, n_head, base, pos_offset)

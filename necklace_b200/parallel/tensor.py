@@ -30,11 +30,15 @@ class _Bufs:
     def __init__(self):
         self.d = {}
 
-    def get(self, group, rows, cols, tag):
-        key = (id(group), rows, cols, tag)
+    def get(self, group, rows, cols, tag, dtype=torch.bfloat16, device=None):
+        key = (id(group), rows, cols, tag, dtype)
         t = self.d.get(key)
         if t is None:
-            t = group.heap.alloc(rows * cols, torch.bfloat16).view(rows, cols)
+            heap = getattr(group, "heap", None)
+            if heap is not None:
+                t = heap.alloc(rows * cols, dtype).view(rows, cols)
+            else:          # torch.distributed stand-in group (CPU tests, NCCL baseline)
+                t = torch.zeros(rows, cols, dtype=dtype, device=device)
             self.d[key] = t
         return t
 
@@ -55,7 +59,7 @@ class AGLinearFn(torch.autograd.Function):
             ctx.save_for_backward(x_shard, w)
             ctx.b_ref = bias
             return y
-        xf = _BUFS.get(group, p * R, K, "ag_fwd")
+        xf = _BUFS.get(group, p * R, K, "ag_fwd", x_shard.dtype, x_shard.device)
         xf[r * R:(r + 1) * R].copy_(x_shard)
         y = group.ag_gemm(xf, w, bias=bias)
         ctx.save_for_backward(xf.clone(), w)   # gathered input, needed by the weight gradient
@@ -102,7 +106,7 @@ class LinearRSFn(torch.autograd.Function):
             dx = gemm(dy_full, w, b_mn=True)
         else:
             R, N = dy_shard.shape
-            dyf = _BUFS.get(group, p * R, N, "ag_bwd")
+            dyf = _BUFS.get(group, p * R, N, "ag_bwd", dy_shard.dtype, dy_shard.device)
             dyf[r * R:(r + 1) * R].copy_(dy_shard)
             dx = group.ag_gemm(dyf, w, b_mn=True)         # [M, K_r]; also fills dyf
             dy_full = dyf
@@ -165,3 +169,200 @@ class SPRowParallelLinear(nn.Module):
 
     def forward(self, x, residual=None):
         return linear_rs(x, self.weight, self.bias, residual, self.group)
+
+
+# --------------------------------------------------------------- vocabulary-parallel ends
+class VocabParallelEmbedFn(torch.autograd.Function):
+    """Token embedding with the vocabulary rows split over the group; output row-sharded.
+
+    Every rank looks the whole index tensor up in its slice (rows it does not own give zeros,
+    as in the reference's masked lookup, necklace/frmwrk/pytorch/mpnn/layers.py:115-131); the
+    reference then all-reduces the full ``[T, C]`` result, here the peer-memory reduce-scatter
+    kernel leaves each rank with its ``[T/p, C]`` rows, which is what the first fused
+    all-gather -> GEMM of the block wants.  Backward: all-gather the row gradients, scatter-add
+    the rows this slice owns."""
+
+    @staticmethod
+    def forward(ctx, idx, wte, group):
+        from ..ops.loss import embed_fwd
+        p, r = group.world, group.rank
+        T, S = idx.numel(), idx.shape[-1]
+        Vl, Cn = wte.shape
+        ctx.group, ctx.S, ctx.wte = group, S, wte
+        ctx.save_for_backward(idx)
+        if p == 1:
+            return embed_fwd(idx, wte, None, S)
+        part = _BUFS.get(group, T, Cn, "emb", wte.dtype, wte.device)
+        embed_fwd(idx, wte, None, S, vocab_start=r * Vl, out=part)
+        return group.reduce_scatter(part)
+
+    @staticmethod
+    def backward(ctx, dout):
+        from ..ops.loss import embed_bwd
+        (idx,) = ctx.saved_tensors
+        group, wte = ctx.group, ctx.wte
+        p, r = group.world, group.rank
+        Vl, Cn = wte.shape
+        dout = dout.contiguous()
+        if p > 1:
+            R = dout.shape[0]
+            full = _BUFS.get(group, p * R, Cn, "emb", dout.dtype, dout.device)
+            full[r * R:(r + 1) * R].copy_(dout)
+            group.all_gather(full)
+            dout = full
+        buf = getattr(wte, "_nkb_grad", None)
+        if buf is not None:
+            if not getattr(wte, "_nkb_grad_has", False):
+                buf.zero_()
+            embed_bwd(idx, dout, buf, None, ctx.S, vocab_start=r * Vl)
+            wte._nkb_grad_has = True
+            cb = getattr(wte, "_nkb_grad_ready", None)
+            if cb is not None:
+                cb(wte)
+            return None, None, None
+        g = torch.zeros_like(wte)
+        embed_bwd(idx, dout, g, None, ctx.S, vocab_start=r * Vl)
+        return None, g, None
+
+
+class VocabParallelLMHeadLossFn(torch.autograd.Function):
+    """Mean cross-entropy of ``all_gather_rows(x) @ W_r^T`` with the vocabulary split over the
+    group.  Logits exist only as this rank's ``[T, V/p]`` bf16 slice; the softmax statistics
+    of the slices (max, sum of exponentials, target logit) are exchanged as a ``[p, T, 3]``
+    fp32 all-gather and combined locally, then every slice turns into its own gradient in
+    place.  Forward: fused all-gather -> GEMM; backward: fused GEMM -> reduce-scatter for
+    dx and a plain GEMM for dW_r."""
+
+    @staticmethod
+    def forward(ctx, x_shard, w, targets, vocab, group):
+        from ..ops.loss import ce_grad, ce_stats
+        p, r = group.world, group.rank
+        R, K = x_shard.shape
+        Vl = w.shape[0]
+        tg = targets.reshape(-1).contiguous()
+        T = tg.numel()
+        if p == 1:
+            x_full = x_shard
+            logits = gemm(x_shard, w)
+        else:
+            xf = _BUFS.get(group, p * R, K, "ag_fwd", x_shard.dtype, x_shard.device)
+            xf[r * R:(r + 1) * R].copy_(x_shard)
+            logits = group.ag_gemm(xf, w)
+            x_full = xf.clone()
+        v_lo = r * Vl
+        v_local = max(0, min(Vl, vocab - v_lo))      # the last slice may hold padding rows
+        st = ce_stats(logits, tg, v_local, v_lo)                      # [T, 3]
+        if p > 1:
+            allst = _BUFS.get(group, p * T, 4, "ce_stats", torch.float32, st.device)
+            allst.view(p, T, 4)[r, :, :3].copy_(st)
+            group.all_gather(allst)
+            a = allst.view(p, T, 4)
+            m = a[:, :, 0].max(0).values
+            ssum = (a[:, :, 1] * torch.exp(a[:, :, 0] - m)).sum(0)
+            tl = a[:, :, 2].sum(0)
+        else:
+            m, ssum, tl = st[:, 0], st[:, 1], st[:, 2]
+        valid = tg >= 0
+        n_valid = valid.sum().clamp(min=1).to(torch.float32)
+        losses = (m + torch.log(ssum) - tl) * valid
+        ce_grad(logits, tg, torch.stack([m, ssum], 1), v_local, v_lo, 1.0 / T)
+        ctx.save_for_backward(x_full, w, logits, n_valid)
+        ctx.group, ctx.T = group, T
+        return losses.sum() / n_valid
+
+    @staticmethod
+    def backward(ctx, dloss):
+        x_full, w, dlogits, n_valid = ctx.saved_tensors
+        group = ctx.group
+        corr = (dloss.float() * (ctx.T / n_valid)).reshape(1)
+        if group.world == 1:
+            dx = gemm(dlogits, w, b_mn=True, alpha_dev=corr)
+        else:
+            # the scalar is folded into dlogits' consumer GEMMs: gemm_rs has no device alpha,
+            # so scale the (small) reduced rows instead
+            dx = group.gemm_rs(dlogits, w, b_mn=True)
+            dx = dx * corr.to(dx.dtype)
+        dw = _deliver_grad(w, lambda out, acc: gemm(dlogits, x_full, a_mn=True, b_mn=True,
+                                                    out=out, accumulate=acc, alpha_dev=corr))
+        return dx, dw, None, None, None
+
+
+def vocab_parallel_embed(idx, wte, group):
+    return VocabParallelEmbedFn.apply(idx, wte, group)
+
+
+def vocab_parallel_lm_head_loss(x_shard, w, targets, vocab, group):
+    return VocabParallelLMHeadLossFn.apply(x_shard, w, targets, vocab, group)
+
+
+# ------------------------------------------ replicated-activation (Megatron) layout, fused
+class ColumnLinearFn(torch.autograd.Function):
+    """Column-parallel linear on a replicated input: ``y_r = x W_r^T (+ b_r)``; the input
+    gradient ``sum_r dy_r W_r`` is the fused GEMM -> reduce-scatter followed by the
+    peer-memory all-gather (the reference all-reduces it over NCCL after a cuBLAS GEMM,
+    necklace/frmwrk/pytorch/mpnn/mappings.py:85-94)."""
+
+    @staticmethod
+    def forward(ctx, x2, w, bias, group):
+        ctx.group, ctx.b_ref = group, bias
+        ctx.save_for_backward(x2, w)
+        return gemm(x2, w, bias=bias)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        group = ctx.group
+        dy = dy.contiguous()
+        M, K = x2.shape
+        p, r = group.world, group.rank
+        dx = None
+        if ctx.needs_input_grad[0]:
+            R = M // p
+            full = _BUFS.get(group, M, K, "col_dx", dy.dtype, dy.device)
+            group.gemm_rs(dy, w, b_mn=True, out=full[r * R:(r + 1) * R])
+            group.all_gather(full)
+            dx = full.clone()
+        dw = _deliver_grad(w, lambda out, acc: gemm(dy, x2, a_mn=True, b_mn=True, out=out,
+                                                    accumulate=acc))
+        db = None
+        if ctx.b_ref is not None:
+            db = _deliver_grad(ctx.b_ref, lambda out, acc: colsum(dy, out, acc))
+        return dx, dw, db, None
+
+
+class RowLinearFn(torch.autograd.Function):
+    """Row-parallel linear with a replicated output: ``y = sum_r x_r W_r^T`` as the fused
+    GEMM -> reduce-scatter plus the peer-memory all-gather; backward needs no collective."""
+
+    @staticmethod
+    def forward(ctx, x2, w, group):
+        ctx.group = group
+        ctx.save_for_backward(x2, w)
+        M, N = x2.shape[0], w.shape[0]
+        p, r = group.world, group.rank
+        R = M // p
+        full = _BUFS.get(group, M, N, "row_y", x2.dtype, x2.device)
+        group.gemm_rs(x2.contiguous(), w, out=full[r * R:(r + 1) * R])
+        group.all_gather(full)
+        return full.clone()
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = gemm(dy, w, b_mn=True) if ctx.needs_input_grad[0] else None
+        dw = _deliver_grad(w, lambda out, acc: gemm(dy, x2, a_mn=True, b_mn=True, out=out,
+                                                    accumulate=acc))
+        return dx, dw, None
+
+
+def fused_group_of(mp_group_info, x: torch.Tensor, rows: int):
+    """The ``PeerGroup`` to run the fused tensor-parallel kernels on, or None when the plain
+    collective path must be taken (no peer heap, CPU tensors, not bf16, or a row count that
+    does not split into 128-row blocks per rank)."""
+    peer = getattr(getattr(mp_group_info, "comm", None), "peer", None)
+    if peer is None or not x.is_cuda or x.dtype != torch.bfloat16:
+        return None
+    if rows % (128 * peer.world):
+        return None
+    return peer

@@ -32,16 +32,17 @@ class Checks:
         assert not self.failed, self.failed[:5]
 
 
-def _worker(rank, world, port, fn_name, q):
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
-                      RANK=str(rank), WORLD_SIZE=str(world))
+def _worker(rank, world, rdv, fn_name, q):
+    os.environ.update(NCCL_NVLS_ENABLE="0", RANK=str(rank), WORLD_SIZE=str(world))
     import datetime
     import torch.distributed as dist
-    torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world,
-                            device_id=torch.device("cuda", rank),
-                            timeout=datetime.timedelta(seconds=60))
     try:
+        torch.cuda.set_device(rank)
+        # rendezvous through a file: a TCP store on a port picked in the parent can lose the
+        # port to another process between the pick and the bind
+        dist.init_process_group("nccl", init_method=f"file://{rdv}", rank=rank, world_size=world,
+                                device_id=torch.device("cuda", rank),
+                                timeout=datetime.timedelta(seconds=60))
         from necklace_b200.comm.symm import SymmetricHeap
         from necklace_b200.ops import check_status
         heap = SymmetricHeap(256 << 20)
@@ -66,10 +67,11 @@ def _worker(rank, world, port, fn_name, q):
 def _run(fn_name, world=None):
     import torch.multiprocessing as mp
     world = world or min(torch.cuda.device_count(), 8)
+    import tempfile
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, fn_name, q)) for r in range(world)]
+    rdv = os.path.join(tempfile.mkdtemp(prefix="nkb_rdv_"), "store")
+    procs = [ctx.Process(target=_worker, args=(r, world, rdv, fn_name, q)) for r in range(world)]
     for p in procs:
         p.start()
     res = []
