@@ -190,6 +190,16 @@ def main():
                 state["first"] = state["loss"]
             return loss
 
+    def finish():
+        ms = state["ev0"].elapsed_time(state["ev1"]) if state["ev1"] is not None else None
+        out = {"rank": args.rank, "ms": ms, "steps_seen": state["n"],
+               "loss_first": state["first"], "loss_last": state["loss"]}
+        if args.out:
+            with open(args.out + ".tmp", "w") as f:
+                json.dump(out, f)
+            os.replace(args.out + ".tmp", args.out)
+        print("REF_RESULT " + json.dumps(out), flush=True)
+
     class AfterStep(hookbase.NklcHookBase):
         def __call__(self, trnr, *a, **k):
             state["n"] += 1
@@ -201,13 +211,20 @@ def main():
                 state["ev1"] = torch.cuda.Event(enable_timing=True)
                 state["ev1"].record()
                 torch.cuda.synchronize()
+                # The measurement is complete.  Leave here instead of through the reference's
+                # own shutdown: with one worker its scheduler never reaches the stop check
+                # (the check sits in the branch taken while acks are still outstanding,
+                # necklace/trainer/tndszr.py:1106-1117, :1806-1814) and would train forever.
+                finish()
+                sys.stdout.flush()
+                os._exit(0)
 
     def make_opt(model, *a, **k):
         return torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), eps=1e-8,
                                  weight_decay=0.1)
 
     def make_loader(*a, **k):
-        ds = SyntheticTokens(total_steps * args.micro_batch, S, vocab, 100 + args.rank)
+        ds = SyntheticTokens((total_steps + 2) * args.micro_batch, S, vocab, 100 + args.rank)
         return torch.utils.data.DataLoader(ds, batch_size=args.micro_batch, shuffle=False,
                                            pin_memory=True, num_workers=0)
 
@@ -230,15 +247,7 @@ def main():
     svc = tndszr.MPSVCWorker(cfg)
     svc.svr.trnr.register_hook_after_do_a_train_step(AfterStep(net, ctx))
     svc.loop()
-    ms = state["ev0"].elapsed_time(state["ev1"]) if state["ev1"] is not None else None
-    out = {"rank": args.rank, "ms": ms, "steps_seen": state["n"], "loss_first": state["first"],
-           "loss_last": state["loss"],
-           "h2d_bytes_per_step": args.micro_batch * S * 8 * 2 if args.rank == 0 else 0}
-    if args.out:
-        with open(args.out + ".tmp", "w") as f:
-            json.dump(out, f)
-        os.replace(args.out + ".tmp", args.out)
-    print("REF_RESULT " + json.dumps(out), flush=True)
+    finish()          # only reached if the epoch ended before the requested number of steps
     return 0
 
 

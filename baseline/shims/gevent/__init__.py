@@ -1,31 +1,47 @@
-"""Thread-backed stand-in for the few gevent calls the reference makes:
-``gevent.spawn(fn, *a)``, ``gevent.sleep(s)``, ``gevent.queue.Queue``."""
+"""Stand-in for the few gevent calls the reference makes: ``gevent.spawn(fn, *a)``,
+``gevent.sleep(s)``, ``gevent.queue.Queue``.  Cooperative, single-threaded (see ``_nkhub``):
+a spawned RPC server is served while the caller sleeps, waits on a queue or waits for an
+RPC reply; anything else that is spawned gets a daemon thread."""
 import threading
 import time
+
+import _nkhub
 
 from . import queue  # noqa: F401
 
 
-class _Greenlet(threading.Thread):
-    def __init__(self, fn, *args, **kwargs):
-        super().__init__(target=fn, args=args, kwargs=kwargs, daemon=True)
-        self.start()
+class _Greenlet:
+    def __init__(self, thread=None):
+        self._thread = thread
 
     def kill(self):
         pass
 
-    def get(self, timeout=None):
-        self.join(timeout)
+    def join(self, timeout=None):
+        if self._thread is not None:
+            self._thread.join(timeout)
+
+    get = join
 
 
 def spawn(fn, *args, **kwargs):
-    return _Greenlet(fn, *args, **kwargs)
+    owner = getattr(fn, "__self__", None)
+    if owner is not None and hasattr(owner, "_zsock") and getattr(fn, "__name__", "") == "run":
+        _nkhub.register(owner)
+        return _Greenlet()
+    t = threading.Thread(target=fn, args=args, kwargs=kwargs, daemon=True)
+    t.start()
+    return _Greenlet(t)
 
 
 def sleep(seconds=0):
-    # gevent.sleep(0) yields to the other greenlets; a short real sleep lets the server
-    # thread take the interpreter lock
-    time.sleep(seconds if seconds and seconds > 0 else 0.0002)
+    end = time.monotonic() + max(0.0, seconds or 0.0)
+    _nkhub.serve(0.0)
+    while True:
+        left = end - time.monotonic()
+        if left <= 0:
+            return
+        _nkhub.serve(min(left, 0.05))
 
 
 def joinall(greenlets, timeout=None):

@@ -1,7 +1,9 @@
 """Minimal zerorpc: ``Server`` exposes the public methods of the object (or of ``self``)
 on a bound url, ``Client`` turns attribute access into remote calls.  pyzmq ROUTER / DEALER
-sockets, msgpack framing; one request at a time per server, as a single-greenlet zerorpc
-server that does not yield inside its handlers would serve them."""
+sockets, msgpack framing.  A server started through ``gevent.spawn(server.run)`` is served
+cooperatively on the caller's thread (see ``_nkhub``); a client that waits for its reply
+keeps serving this process's servers meanwhile, as a greenlet blocked on a reply yields to
+the server greenlet in the original."""
 import itertools
 import threading
 import time
@@ -9,6 +11,8 @@ import uuid
 
 import msgpack
 import zmq  # noqa: F401  (the reference does ``from zerorpc import zmq``)
+
+import _nkhub
 
 _ctx = None
 _ctx_lock = threading.Lock()
@@ -49,29 +53,39 @@ class Server:
     def connect(self, endpoint):
         self._zsock.connect(endpoint)
 
+    def _handle_one(self, block=True):
+        """Receive and answer one request; returns False when none was waiting."""
+        try:
+            frames = self._zsock.recv_multipart(0 if block else zmq.NOBLOCK)
+        except zmq.Again:
+            return False
+        except zmq.ZMQError:
+            return False
+        ident, payload = frames[0], frames[-1]
+        rid = None
+        try:
+            rid, name, args, kwargs = msgpack.unpackb(payload, raw=False)
+            if name.startswith("_"):
+                raise AttributeError(name)
+            ret = getattr(self._methods, name)(*args, **kwargs)
+            rep = [rid, True, ret, None]
+        except Exception as e:  # noqa: BLE001
+            import traceback
+            rep = [rid, False, f"{type(e).__name__}: {e}", traceback.format_exc()]
+        try:
+            self._zsock.send_multipart([ident, msgpack.packb(rep, use_bin_type=True)])
+        except zmq.ZMQError:
+            pass
+        return True
+
     def run(self):
+        """Blocking serve loop (for a server that owns its thread)."""
         poller = zmq.Poller()
         poller.register(self._zsock, zmq.POLLIN)
         while not self._zstop:
             try:
-                if not dict(poller.poll(50)):
-                    continue
-                frames = self._zsock.recv_multipart()
-            except zmq.ZMQError:
-                break
-            ident, payload = frames[0], frames[-1]
-            rid = None
-            try:
-                rid, name, args, kwargs = msgpack.unpackb(payload, raw=False)
-                if name.startswith("_"):
-                    raise AttributeError(name)
-                ret = getattr(self._methods, name)(*args, **kwargs)
-                rep = [rid, True, ret, None]
-            except Exception as e:  # noqa: BLE001
-                import traceback
-                rep = [rid, False, f"{type(e).__name__}: {e}", traceback.format_exc()]
-            try:
-                self._zsock.send_multipart([ident, msgpack.packb(rep, use_bin_type=True)])
+                if dict(poller.poll(50)):
+                    self._handle_one(block=False)
             except zmq.ZMQError:
                 break
 
@@ -113,8 +127,10 @@ class Client:
             self._zsock.send(msgpack.packb([rid, name, list(args), kwargs], use_bin_type=True))
             while True:
                 left = deadline - time.monotonic()
-                if left <= 0 or not self._zsock.poll(int(left * 1000) + 1):
+                if left <= 0:
                     raise TimeoutExpired(f"timeout after {timeout}s calling {name}")
+                if not _nkhub.serve(min(left, 0.05), extra=self._zsock):
+                    continue
                 rep = msgpack.unpackb(self._zsock.recv(), raw=False)
                 if rep[0] != rid:
                     continue

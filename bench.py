@@ -37,10 +37,24 @@ def parse():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "torch"])
+    ap.add_argument("--config", type=int, default=3, choices=[2, 3, 4, 5],
+                    help="which named configuration: 2 dp + 2-bit ResNet-50, 3 dp+zr GPT-2 "
+                         "medium (the headline), 4 dp+pp+mp Llama-7B-like, 5 dp+zr+mp "
+                         "Llama-13B-like")
     ap.add_argument("--model", default="gpt2-medium", choices=["gpt2-medium", "gpt2-tiny"])
-    ap.add_argument("--micro-batch", type=int, default=8)
-    ap.add_argument("--seq", type=int, default=1024)
+    ap.add_argument("--micro-batch", type=int, default=0, help="0 = the configuration's value")
+    ap.add_argument("--seq", type=int, default=0, help="0 = the configuration's value")
+    ap.add_argument("--layers", type=int, default=0,
+                    help="cut the model to this many layers (smoke runs only; the JSON line "
+                         "is then marked reduced and is not a benchmark number)")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--bucket-mb", type=float, default=0.0,
+                    help="> 0: cut the gradient buffer into buckets of this size and overlap "
+                         "their collectives with backward")
+    ap.add_argument("--no-baseline", action="store_true",
+                    help="skip the stock-torch arm that is timed after ours for vs_baseline")
+    ap.add_argument("--tp-impl", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--grad-comp-threshold", type=float, default=1e-3)
     return ap.parse_args()
 
 
@@ -120,10 +134,13 @@ def reference_arm(args):
             os.path.join(ROOT, "baseline", "_ref", "necklace", "frmwrk", "pytorch", "ptprms.py")):
         return unavailable("baseline/_ref does not hold an installed reference package")
     warmup = max(args.warmup, 3)
+    if args.config != 3:
+        return unavailable(f"the reference arm covers config 3 only (asked for {args.config})")
+    B, S = args.micro_batch or 8, args.seq or 1024
     driver = os.path.join(ROOT, "baseline", "ref_gpt2_zero.py")
     common = ["--world", str(world), "--steps", str(args.steps), "--warmup", str(warmup),
-              "--model", args.model, "--micro-batch", str(args.micro_batch), "--seq",
-              str(args.seq), "--server-url", f"ipc://{work}/svr.ipc"]
+              "--model", args.model, "--micro-batch", str(B), "--seq", str(S),
+              "--server-url", f"ipc://{work}/svr.ipc"]
     env = dict(os.environ, NCCL_DEBUG=os.environ.get("NCCL_DEBUG", "WARN"))
     for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT"):
         env.pop(k, None)   # the reference has its own bring-up (unique id relayed over RPC)
@@ -139,28 +156,44 @@ def reference_arm(args):
         [sys.executable, driver, "--role", "worker", "--rank", str(rank), "--gpu",
          str(local_rank), "--url", f"ipc://{work}/w{rank}.ipc", "--out", out, *common],
         stdout=open(os.path.join(work, f"w{rank}.log"), "w"), stderr=subprocess.STDOUT, env=env))
-    deadline = time.time() + float(os.environ.get("NKB_REF_TIMEOUT", "1500"))
+    deadline = time.time() + float(os.environ.get("NKB_REF_TIMEOUT", "900"))
     failed = None
     worker = procs[-1]
+    sched = procs[0] if rank == 0 else None
+
+    def tail(name, n=300):
+        try:
+            return open(os.path.join(work, name)).read()[-n:]
+        except OSError:
+            return ""
+
     while worker.poll() is None:
         if time.time() > deadline:
-            failed = "reference run exceeded its time limit"
+            failed = f"reference run exceeded its time limit: {tail(f'w{rank}.log')}"
+            break
+        if sched is not None and sched.poll() is not None:
+            failed = f"reference scheduler ended early: {tail('sched.log')}"
             break
         time.sleep(0.5)
     clocks = sampler.stop()
+    if failed is None and not os.path.exists(out):
+        failed = f"reference worker {rank} ended without a result: {tail(f'w{rank}.log', 400)}"
+    if rank == 0 and failed is None:
+        # the scheduler is only needed until every worker has written its result
+        t_end = time.time() + 120
+        while time.time() < t_end and not all(
+                os.path.exists(os.path.join(work, f"rank{r}.json")) for r in range(world)):
+            time.sleep(0.2)
     for p in procs:                       # exactly the children started above
         if p.poll() is None:
-            try:
-                p.wait(timeout=20 if failed is None else 1)
-            except subprocess.TimeoutExpired:
-                p.kill()
-    if failed is None and not os.path.exists(out):
-        tail = ""
-        try:
-            tail = open(os.path.join(work, f"w{rank}.log")).read()[-400:]
-        except OSError:
-            pass
-        failed = f"reference worker {rank} ended without a result: {tail}"
+            p.kill()
+    keep = os.environ.get("NKB_REF_LOGDIR")
+    if keep:
+        import shutil
+        os.makedirs(keep, exist_ok=True)
+        for name in os.listdir(work):
+            if name.endswith(".log"):
+                shutil.copy(os.path.join(work, name), os.path.join(keep, f"n{world}_{name}"))
     if rank != 0:
         return 0
     if failed is not None:
@@ -177,7 +210,6 @@ def reference_arm(args):
     if any(r["ms"] is None for r in res):
         return unavailable("reference workers saw fewer steps than requested")
     ms = max(r["ms"] for r in res)
-    B, S = args.micro_batch, args.seq
     value = B * world * args.steps / (ms / 1e3)
     line = {
         "metric": METRIC, "value": round(value, 3), "unit": "samples/s", "n_gpus": world,
@@ -204,6 +236,404 @@ def reference_arm(args):
     return 0
 
 
+# ======================================================================== workloads
+class Workload:
+    """What the timing harness needs from a configuration."""
+    samples_per_step = 0          # whole job
+    h2d_bytes_per_step = 0
+    config: dict = {}
+    engine = None
+
+    def step_dev(self, i):        # inputs already on the device
+        raise NotImplementedError
+
+    def step_e2e(self, i):        # inputs copied from pinned host memory inside the call
+        raise NotImplementedError
+
+    def finish(self):
+        if self.engine is not None:
+            self.engine.check()
+
+
+def _token_pool(vocab, B, S, rank, dev, pool=8):
+    import torch
+    g = torch.Generator().manual_seed(100 + rank)
+    tok = [torch.randint(0, vocab, (B, S + 1), generator=g) for _ in range(pool)]
+    hx = [t[:, :-1].contiguous().pin_memory() for t in tok]
+    hy = [t[:, 1:].contiguous().pin_memory() for t in tok]
+    return hx, hy, [t.to(dev) for t in hx], [t.to(dev) for t in hy]
+
+
+class GPT2Zero(Workload):
+    """Config 3: dp+zr, GPT-2 medium, bf16 + fp32 master Adam, micro-batch 8 x 1024 per GPU."""
+
+    def __init__(self, args, world, rank, dev, impl, mode=None):
+        import torch
+        self.impl = impl
+        B, S = args.micro_batch or 8, args.seq or 1024
+        torch.manual_seed(1234)
+        if impl == "ours":
+            from necklace_b200.comm.symm import SymmetricHeap
+            from necklace_b200.models.gpt2 import GPT2, GPT2Config
+            from necklace_b200.parallel.engine import OptimConfig, TrainEngine
+            cfg = GPT2Config.medium() if args.model == "gpt2-medium" else GPT2Config.tiny()
+            if args.layers:
+                cfg.n_layer = args.layers
+            S = min(S, cfg.max_seq)
+            model = GPT2(cfg, device=dev)
+            heap = group = None
+            mode = mode or ("zero" if world > 1 else "local")
+            if world > 1 and mode != "local":
+                heap = SymmetricHeap(int(model.num_params() * 2 * 2 * 1.02) + (64 << 20))
+                group = heap.peer_group()
+            self.engine = TrainEngine(
+                model, mode=mode, group=group, heap=heap,
+                optim=OptimConfig("adam", lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8,
+                                  weight_decay=0.1),
+                use_cuda_graph=not args.no_graph,
+                bucket_mb=args.bucket_mb if (args.bucket_mb > 0 and mode != "local") else None)
+            self._step = self.engine.step
+            vocab = cfg.vocab
+        else:
+            sys.path.insert(0, os.path.join(ROOT, "baseline"))
+            from torch_gpt2 import TorchZeroTrainer
+            tr = TorchZeroTrainer(args.model, dev, world, rank)
+            self._step, vocab, S = tr.step, tr.vocab, min(S, tr.max_seq)
+            self._xbuf = self._ybuf = None
+        self.hx, self.hy, self.dx, self.dy = _token_pool(vocab, B, S, rank, dev)
+        self.samples_per_step = B * world
+        self.h2d_bytes_per_step = B * S * 8 * 2
+        self.config = {"model": args.model, "global_batch": B * world, "seq_len": S,
+                       "parallelism": f"dp+zr (zr={world})", "optimizer": "adam fp32 master",
+                       "l2": "per-step working set (0.7 GB bf16 weights + activations) exceeds "
+                             "the 126 MB L2; no explicit flush",
+                       "cuda_graph": impl == "ours" and not args.no_graph,
+                       "bucket_mb": args.bucket_mb}
+        if args.layers:
+            self.config["reduced"] = f"{args.layers} layers: smoke run, not a benchmark number"
+
+    def step_dev(self, i):
+        n = len(self.dx)
+        return self._step(self.dx[i % n], self.dy[i % n])
+
+    def step_e2e(self, i):
+        import torch
+        n = len(self.hx)
+        if self.impl == "ours":     # the engine copies into its static input buffers
+            return self._step(self.hx[i % n], self.hy[i % n])
+        if self._xbuf is None:
+            self._xbuf, self._ybuf = torch.empty_like(self.dx[0]), torch.empty_like(self.dy[0])
+        self._xbuf.copy_(self.hx[i % n], non_blocking=True)
+        self._ybuf.copy_(self.hy[i % n], non_blocking=True)
+        return self._step(self._xbuf, self._ybuf)
+
+
+class LlamaHybrid(Workload):
+    """Config 4 (dp+pp+mp, Llama 32 L / d 4096 / seq 2048, 8 micro-batches x 2 sequences per
+    pipeline step, mp=2, pp=2, dp=world/4) and config 5 (dp+zr+mp, Llama 40 L / d 5120 /
+    seq 4096, mp=4, zr=world/4, micro-batch 1 with 8-fold gradient accumulation), both on the
+    fused tensor-parallel kernels with Adam on fp32 master weights."""
+
+    def __init__(self, args, world, rank, dev, which):
+        import torch
+        import torch.nn as nn
+        from necklace_b200.comm import backend
+        from necklace_b200.comm import groups as G
+        from necklace_b200.models.llama import Llama, LlamaConfig
+        from necklace_b200.parallel.engine import OptimConfig, TrainEngine
+        from necklace_b200.parallel.pipe_engine import PipelineEngine
+        self.which = which
+        opt = OptimConfig("adam", lr=1e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1)
+        if which == 4:
+            mp, pp = 2, 2
+            assert world % 4 == 0, "config 4 needs 4 (dp=1) or 8 (dp=2) GPUs"
+            dp = world // 4
+            tmode, gcfg = "dp+pp+mp", {"dp_size": dp, "pp_size": pp, "mp_size": mp}
+            cfgm = LlamaConfig.llama7b()
+            S, mb_seqs, n_mb = args.seq or 2048, args.micro_batch or 2, 8
+        else:
+            mp = 4
+            assert world % 4 == 0, "config 5 needs 4 (zr=1) or 8 (zr=2) GPUs"
+            zr = world // 4
+            tmode, gcfg = "dp+zr+mp", {"dp_size": 1, "zr_size": zr, "mp_size": mp}
+            cfgm = LlamaConfig.llama13b()
+            S, mb_seqs, n_mb = args.seq or 4096, args.micro_batch or 1, 8
+        if args.layers:
+            cfgm.n_layer = args.layers
+        gcfg.update(world_size=world, my_rank=rank)
+        # heap: bf16 parameters + gradients of this rank's model slice (when they are reduced
+        # over peers) plus the gather / staging buffers of the fused kernels
+        per_layer = 4 * cfgm.d_model ** 2 + 3 * cfgm.d_model * cfgm.d_ff
+        n_local = (cfgm.n_layer * per_layer // (pp if which == 4 else 1) +
+                   2 * 32768 * cfgm.d_model) // mp
+        heap_bytes = int(n_local * 4 * 1.05) + (3 << 30)
+        fused = args.tp_impl == "fused"
+        heap = backend.init_backend(tmode, gcfg, comm_type="peer", device=dev,
+                                    heap_bytes=heap_bytes)
+        mpg = G.get_nccl_group_mp()
+        mp_peer = mpg.comm.peer
+        cfgm.tp_group = mp_peer if fused else None
+        cfgm.mp, cfgm.mp_rank = mpg.world_size, mpg.rank
+        self.mp_rank = mpg.rank
+        B = mb_seqs * n_mb
+        if which == 4:
+            ppg = G.get_nccl_group_pp()
+            stage, n_stage = ppg.rank, ppg.world_size
+            per = cfgm.n_layer // n_stage
+            layers = range(stage * per, (stage + 1) * per if stage < n_stage - 1 else cfgm.n_layer)
+            net = Llama(cfgm, device=dev, layers=layers, with_embed=stage == 0,
+                        with_head=stage == n_stage - 1)
+
+            class Stage(nn.Module):
+                def __init__(s):
+                    super().__init__()
+                    s.net = net
+
+                def forward(s, x, targets=None):
+                    return s.net(x, targets, batch=mb_seqs)
+
+            dpg = G.get_nccl_group_dp()
+            self.engine = PipelineEngine(
+                Stage(), stage=stage, pp_ranks=ppg.pg_ranks, micro_batches=n_mb,
+                group=dpg.comm.peer if dpg.world_size > 1 else None, heap=heap, mp_group=mp_peer,
+                optim=opt, bucket_mb=args.bucket_mb if args.bucket_mb > 0 else None)
+            self.has_data = stage == 0
+            replicas = dpg.world_size
+            par = f"dp={replicas} pp={pp} mp={mp}"
+        else:
+            net = Llama(cfgm, device=dev)
+            zrg = G.get_nccl_group_zr()
+            self.engine = TrainEngine(
+                net, mode="zero" if zrg.world_size > 1 else "local",
+                group=zrg.comm.peer if zrg.world_size > 1 else None, heap=heap, optim=opt,
+                micro_batches=n_mb, use_cuda_graph=False,
+                bucket_mb=args.bucket_mb if args.bucket_mb > 0 else None)
+            self.has_data = True
+            replicas = zrg.world_size
+            par = f"dp=1 zr={replicas} mp={mp}"
+        self.mp_peer = mp_peer
+        # the replica's batch is drawn on tensor-parallel rank 0 and broadcast over the group
+        seed_rank = rank - self.mp_rank
+        self.hx, self.hy, self.dx, self.dy = _token_pool(cfgm.vocab, B, S, seed_rank, dev, pool=4)
+        self.samples_per_step = B * replicas
+        self.h2d_bytes_per_step = B * S * 8 * 2
+        self.config = {"model": f"llama {cfgm.n_layer}L d{cfgm.d_model} ff{cfgm.d_ff} "
+                                f"h{cfgm.n_head} vocab{cfgm.vocab}",
+                       "global_batch": B * replicas, "seq_len": S, "parallelism": par,
+                       "micro_batches": n_mb, "optimizer": "adam fp32 master",
+                       "tp": "fused all-gather->GEMM / GEMM->reduce-scatter over peer memory"
+                       if fused else "NCCL all-reduce",
+                       "l2": "working set exceeds L2; no explicit flush", "cuda_graph": False,
+                       "bucket_mb": args.bucket_mb}
+        if args.layers:
+            self.config["reduced"] = f"{args.layers} layers: smoke run, not a benchmark number"
+
+    def _bcast(self, x, y):
+        if self.which == 4:
+            return self.engine.broadcast_inputs(x, y)
+        if self.mp_peer.world == 1:
+            return x, y
+        if not hasattr(self, "_bb"):
+            self._bb = [self.mp_peer.heap.alloc(x.numel(), x.dtype).view(x.shape)
+                        for _ in range(2)]
+        for buf, t in zip(self._bb, (x, y)):
+            if self.mp_peer.rank == 0:
+                buf.copy_(t, non_blocking=True)
+            self.mp_peer.broadcast(buf, 0)
+        return self._bb[0], self._bb[1]
+
+    def _run(self, x, y):
+        if not self.has_data:
+            return self.engine.step()
+        x, y = self._bcast(x, y)
+        return self.engine.step(x, y)
+
+    def step_dev(self, i):
+        n = len(self.dx)
+        return self._run(self.dx[i % n], self.dy[i % n])
+
+    def step_e2e(self, i):
+        n = len(self.hx)
+        if not self.has_data:
+            return self.engine.step()
+        if self.mp_rank == 0:       # pinned host -> device on the rank that owns the batch
+            return self._run(self.hx[i % n].to(self.dx[0].device, non_blocking=True),
+                             self.hy[i % n].to(self.dx[0].device, non_blocking=True))
+        return self._run(self.dx[0], self.dy[0])   # placeholders: overwritten by the broadcast
+
+
+class ResNetDP(Workload):
+    """Config 2: dp with 2-bit gradient quantisation (error feedback), ResNet-50, bf16,
+    3 x 224 x 224 inputs, batch 256 per GPU, SGD momentum 0.9.  The host batch is bf16
+    channels-last (what the loader hands over); labels int64."""
+
+    def __init__(self, args, world, rank, dev, impl):
+        import torch
+        self.impl = impl
+        B, HW = args.micro_batch or 256, args.seq or 224
+        layers = (3, 4, 6, 3) if not args.layers else (1,) * 4
+        torch.manual_seed(1234)
+        if impl == "ours":
+            from necklace_b200.comm.symm import SymmetricHeap
+            from necklace_b200.models.resnet import ResNet
+            from necklace_b200.parallel.engine import GradCompConfig, OptimConfig, TrainEngine
+            net = ResNet(1000, layers, 64, device=dev)
+            nparam = sum(p.numel() for p in net.parameters())
+            heap = SymmetricHeap(int(nparam * (2 + 2 + 0.25 + 1) * 1.05) + (64 << 20))
+            self.engine = TrainEngine(
+                net, mode="dp", group=heap.peer_group(), heap=heap,
+                optim=OptimConfig("sgd", lr=0.1, beta1=0.9),
+                grad_comp=GradCompConfig(grad_comp_threshold=args.grad_comp_threshold),
+                use_cuda_graph=not args.no_graph,
+                bucket_mb=args.bucket_mb if args.bucket_mb > 0 else None)
+            self._step = self.engine.step
+        else:
+            sys.path.insert(0, os.path.join(ROOT, "baseline"))
+            from torch_resnet import TorchDDPTrainer
+            self._step = TorchDDPTrainer(dev, world, rank, layers).step
+        g = torch.Generator().manual_seed(100 + rank)
+        pool = 3
+        self.hx = [torch.randn(B, HW, HW, 3, generator=g).bfloat16().pin_memory()
+                   for _ in range(pool)]
+        self.hy = [torch.randint(0, 1000, (B,), generator=g).pin_memory() for _ in range(pool)]
+        self.dx, self.dy = [t.to(dev) for t in self.hx], [t.to(dev) for t in self.hy]
+        self._xb, self._yb = torch.empty_like(self.dx[0]), torch.empty_like(self.dy[0])
+        self.samples_per_step = B * world
+        self.h2d_bytes_per_step = B * HW * HW * 3 * 2 + B * 8
+        self.config = {"model": "resnet50" if not args.layers else "resnet [1,1,1,1]",
+                       "global_batch": B * world, "image": f"3x{HW}x{HW}", "seq_len": 0,
+                       "parallelism": f"dp={world}",
+                       "grad_compression": f"2-bit, threshold {args.grad_comp_threshold}, error "
+                                           "feedback" if impl == "ours" else "none (DDP)",
+                       "optimizer": "sgd momentum 0.9, fp32 master",
+                       "l2": "activations exceed L2; no explicit flush",
+                       "cuda_graph": impl == "ours" and not args.no_graph,
+                       "bucket_mb": args.bucket_mb}
+        if args.layers:
+            self.config["reduced"] = "one block per stage: smoke run, not a benchmark number"
+
+    def step_dev(self, i):
+        n = len(self.dx)
+        return self._step(self.dx[i % n], self.dy[i % n])
+
+    def step_e2e(self, i):
+        n = len(self.hx)
+        if self.impl == "ours" and self.engine.use_cuda_graph:
+            return self._step(self.hx[i % n], self.hy[i % n])   # copied into the static inputs
+        self._xb.copy_(self.hx[i % n], non_blocking=True)
+        self._yb.copy_(self.hy[i % n], non_blocking=True)
+        return self._step(self._xb, self._yb)
+
+
+def build_workload(args, world, rank, dev, impl):
+    if args.config == 3:
+        return GPT2Zero(args, world, rank, dev, impl)
+    if args.config == 2:
+        return ResNetDP(args, world, rank, dev, impl)
+    if impl != "ours":
+        raise SystemExit(f"--impl {impl} has no arm for config {args.config}")
+    return LlamaHybrid(args, world, rank, dev, args.config)
+
+
+def timed_regions(wl, args, world, dev, clocks=True):
+    """Warm-up, the device-timed region (CUDA events around exactly K steps, barrier +
+    synchronize on both sides) and the end-to-end region; returns (dev_ms, e2e_ms, clocks,
+    first_loss, last_loss), both times as the max over ranks."""
+    import torch
+    import torch.distributed as dist
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    W = max(args.warmup, 3)
+    for i in range(W):
+        loss = wl.step_dev(i)
+    sync_all()
+    first_loss = float(loss.float().item())
+    sampler = ClockSampler(dev.index) if clocks else None
+    if sampler:
+        sampler.start()
+    sync_all()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        loss = wl.step_dev(i)
+    e1.record()
+    sync_all()
+    dev_ms = e0.elapsed_time(e1)
+
+    # end to end: every step copies its batch from pinned host memory and its loss is copied
+    # to pinned host memory; the host reads the loss of step i once its copy has finished,
+    # while step i+1 is already enqueued (deferred logging, as a training loop does)
+    sync_all()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    loss_pin = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(2)]
+    loss_ev = [torch.cuda.Event() for _ in range(2)]
+    last_loss = first_loss
+    f0.record()
+    for i in range(args.steps):
+        loss = wl.step_e2e(i)
+        loss_pin[i & 1].copy_(loss.float().reshape(1), non_blocking=True)
+        loss_ev[i & 1].record()
+        if i > 0:
+            loss_ev[(i - 1) & 1].synchronize()
+            last_loss = float(loss_pin[(i - 1) & 1][0])
+    loss_ev[(args.steps - 1) & 1].synchronize()
+    last_loss = float(loss_pin[(args.steps - 1) & 1][0])
+    f1.record()
+    sync_all()
+    e2e_ms = f0.elapsed_time(f1)
+    ck = sampler.stop() if sampler else None
+    t = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t[0]), float(t[1]), ck, first_loss, last_loss
+
+
+def comm_roofline(wl, world, dev, peaks):
+    """Standalone CUDA-event timing of the fused reduce-scatter + Adam + all-gather kernel on
+    the engine's own buffers against its floor: the slower of its NVLink bytes per direction
+    over the measured 770 GB/s peer bandwidth and its HBM bytes over the measured copy
+    bandwidth.  (The kernel updates the weights; it runs after all timed regions.)"""
+    import torch
+    import torch.distributed as dist
+    eng = wl.engine
+    if eng is None or not getattr(eng, "sharded", False):
+        return None
+    f, o = eng.flat, eng.optim
+    n, W = f.numel, world
+    reps = 5
+
+    def run():
+        for b in range(len(eng.buckets)):
+            eng._fired.discard(b)
+            eng._launch_bucket(b, side=False)
+
+    eng._fired = set()
+    run()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1) / reps], dtype=torch.float64, device=dev)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = float(ms[0])
+    link_bytes = (W - 1) / W * n * 2                 # per direction: gradients in, parameters out
+    hbm_bytes = n * 2 / W * (W + 1) + n / W * 4 * 6 + n * 2   # grads read, fp32 state r/w, params
+    floor_ms = max(link_bytes / 770e9, hbm_bytes / (peaks.get("hbm_gbs", 6550.0) * 1e9)) * 1e3
+    return {"rs_opt_ag": {"ms": round(ms, 4), "nvlink_bytes_per_dir": int(link_bytes),
+                          "hbm_bytes": int(hbm_bytes), "floor_ms": round(floor_ms, 4),
+                          "frac_of_measured_roofline": round(floor_ms / ms, 3)}}
+
+
 def main():
     args = parse()
     if args.impl == "reference":
@@ -220,146 +650,103 @@ def main():
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:  # noqa: BLE001
+        pass
 
-    B, S = args.micro_batch, args.seq
-    torch.manual_seed(1234)
-    if args.impl == "ours":
-        from necklace_b200 import _lib
-        from necklace_b200.comm.symm import SymmetricHeap
-        from necklace_b200.models.gpt2 import GPT2, GPT2Config
-        from necklace_b200.parallel.engine import OptimConfig, TrainEngine
-        cfg = GPT2Config.medium() if args.model == "gpt2-medium" else GPT2Config.tiny()
-        S = min(S, cfg.max_seq)
-        model = GPT2(cfg, device=dev)
-        nparam = model.num_params()
-        heap = group = None
-        if world > 1:
-            heap = SymmetricHeap(int(nparam * 2 * 2 * 1.02) + (64 << 20))
-            group = heap.peer_group()
-        engine = TrainEngine(model, mode="zero" if world > 1 else "local", group=group, heap=heap,
-                             optim=OptimConfig("adam", lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8,
-                                               weight_decay=0.1),
-                             use_cuda_graph=not args.no_graph)
-        step_fn = engine.step
-        vocab = cfg.vocab
-        launches = lambda: _lib.launch_count
-    else:
-        sys.path.insert(0, os.path.join(ROOT, "baseline"))
-        from torch_gpt2 import TorchZeroTrainer
-        tr = TorchZeroTrainer(args.model, dev, world, rank)
-        step_fn = tr.step
-        vocab = tr.vocab
-        S = min(S, tr.max_seq)
-        launches = lambda: 0
-
-    # synthetic data: a pool of pinned host batches (uniform token ids, next-token targets)
-    g = torch.Generator().manual_seed(100 + rank)
-    pool = 8
-    host_tok = [torch.randint(0, vocab, (B, S + 1), generator=g).pin_memory() for _ in range(pool)]
-    host_x = [t[:, :-1].contiguous().pin_memory() for t in host_tok]
-    host_y = [t[:, 1:].contiguous().pin_memory() for t in host_tok]
-    dev_x = [t.to(dev) for t in host_x]
-    dev_y = [t.to(dev) for t in host_y]
-    loss_host = torch.zeros(1, dtype=torch.float32).pin_memory()
-
-    def sync_all():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
-
-    # ---- warm-up (includes graph capture) --------------------------------
-    for i in range(max(args.warmup, 3)):
-        loss = step_fn(dev_x[i % pool], dev_y[i % pool])
-    sync_all()
-    first_loss = float(loss.float().item())
-
-    # launches per step: count one step's launches eagerly-issued or captured
-    l0 = launches()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
-
-    # ---- device-timed region: exactly K steps ------------------------------
-    sync_all()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(args.steps):
-        loss = step_fn(dev_x[i % pool], dev_y[i % pool])
-    e1.record()
-    sync_all()
-    dev_ms = e0.elapsed_time(e1)
-    eager_launches = launches() - l0
-
-    # ---- end-to-end region: pinned H2D of every batch + D2H of every loss ----
-    sync_all()
-    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    xbuf, ybuf = torch.empty_like(dev_x[0]), torch.empty_like(dev_y[0])
-    f0.record()
-    t_wall = time.perf_counter()
-    # Every step: this step's batch comes from pinned host memory (the engine's step() copies it
-    # into its static input buffers; the torch arm copies it into device tensors first) and the
-    # step's loss is copied to pinned host memory.  The host reads the loss of step i once its
-    # copy has finished, while step i+1 is already enqueued (deferred logging, as a training
-    # loop does), so the CPU-side launch work overlaps the previous step.
-    loss_pin = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(2)]
-    loss_ev = [torch.cuda.Event() for _ in range(2)]
-    last_loss = first_loss
-    for i in range(args.steps):
-        if args.impl == "ours":
-            loss = step_fn(host_x[i % pool], host_y[i % pool])
-        else:
-            xbuf.copy_(host_x[i % pool], non_blocking=True)
-            ybuf.copy_(host_y[i % pool], non_blocking=True)
-            loss = step_fn(xbuf, ybuf)
-        loss_pin[i & 1].copy_(loss.float().reshape(1), non_blocking=True)
-        loss_ev[i & 1].record()
-        if i > 0:
-            loss_ev[(i - 1) & 1].synchronize()
-            last_loss = float(loss_pin[(i - 1) & 1][0])
-    loss_ev[(args.steps - 1) & 1].synchronize()
-    last_loss = float(loss_pin[(args.steps - 1) & 1][0])
-    f1.record()
-    sync_all()
-    e2e_ms = f0.elapsed_time(f1)
-    clocks = sampler.stop()
-
-    if args.impl == "ours":
-        engine.check()
-        per_step = getattr(engine, "launches_per_step", None)
-        gpu_launches = eager_launches if per_step is None else per_step * args.steps
-
-    t = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    dev_ms, e2e_ms = float(t[0]), float(t[1])
-
-    global_batch = B * world
-    value = global_batch * args.steps / (dev_ms / 1e3)
-    e2e_value = global_batch * args.steps / (e2e_ms / 1e3)
+    from necklace_b200 import _lib
+    wl = build_workload(args, world, rank, dev, args.impl)
+    dev_ms, e2e_ms, clocks, first_loss, last_loss = timed_regions(wl, args, world, dev)
+    wl.finish()
+    W = max(args.warmup, 3)
+    value = wl.samples_per_step * args.steps / (dev_ms / 1e3)
+    e2e_value = wl.samples_per_step * args.steps / (e2e_ms / 1e3)
+    cfg = dict(wl.config)
+    cfg["tokens_per_s"] = round(value * cfg.get("seq_len", 0), 1)
     out = {
         "metric": METRIC, "value": round(value, 2), "unit": "samples/s", "n_gpus": world,
-        "steps": args.steps, "warmup": max(args.warmup, 3),
-        "ms_per_step": round(dev_ms / args.steps, 3), "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "impl": args.impl,
-        "config": {"model": args.model, "global_batch": global_batch, "seq_len": S,
-                   "parallelism": f"dp+zr (zr={world})", "optimizer": "adam fp32 master",
-                   "tokens_per_s": round(value * S, 1),
-                   "l2": "per-step working set (0.7 GB bf16 weights + activations) exceeds the "
-                         "126 MB L2; no explicit flush",
-                   "cuda_graph": (args.impl == "ours" and not args.no_graph)},
-        "clocks": clocks,
+        "steps": args.steps, "warmup": W, "ms_per_step": round(dev_ms / args.steps, 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic", "impl": args.impl, "config": cfg, "clocks": clocks,
         "e2e": {"value": round(e2e_value, 2), "unit": "samples/s",
                 "ms_per_step": round(e2e_ms / args.steps, 3),
-                "h2d_bytes_per_step": int(xbuf.numel() * 8 + ybuf.numel() * 8),
-                "d2h_bytes_per_step": 4},
+                "h2d_bytes_per_step": int(wl.h2d_bytes_per_step), "d2h_bytes_per_step": 4},
         "loss_first": round(first_loss, 4), "loss_last": round(last_loss, 4),
     }
     if args.impl == "ours":
-        out["gpu_launches"] = int(gpu_launches)
+        per_step = getattr(wl.engine, "launches_per_step", None)
+        if per_step is None:                      # eager engine: count one more step
+            torch.cuda.synchronize()
+            l0 = _lib.launch_count
+            wl.step_dev(0)
+            torch.cuda.synchronize()
+            per_step = _lib.launch_count - l0
+        out["gpu_launches"] = int(per_step * args.steps)
+
+    # ---- the other half of the metric and the comparison, measured in this invocation ----
+    if args.impl == "ours" and args.config == 2 and not args.no_baseline:
+        try:
+            base = ResNetDP(args, world, rank, dev, "torch")
+            b_ms, b_e2e, _, _, _ = timed_regions(base, args, world, dev, clocks=False)
+            b_val = base.samples_per_step * args.steps / (b_ms / 1e3)
+            out["vs_baseline"] = round(value / b_val, 3)
+            out["baseline"] = {"impl": "stock torch DistributedDataParallel (NCCL, cuDNN, bf16 "
+                                       "autocast, channels-last, uncompressed gradients), same "
+                                       "box, same invocation",
+                               "value": round(b_val, 2), "ms_per_step": round(b_ms / args.steps, 3),
+                               "e2e_value": round(base.samples_per_step * args.steps /
+                                                  (b_e2e / 1e3), 2)}
+        except Exception as e:  # noqa: BLE001
+            out["baseline"] = {"error": repr(e)[:300]}
+    if args.impl == "ours" and args.config == 3:
+        if world > 1 and not args.layers:
+            try:
+                # step time of the same model with no collective at all (every rank updates
+                # all parameters locally): what is left is the communication that backward
+                # and the optimizer do not hide
+                local = GPT2Zero(args, world, rank, dev, "ours", mode="local")
+                l_ms, _, _, _, _ = timed_regions(local, args, world, dev, clocks=False)
+                out["exposed_comm_ms"] = round((dev_ms - l_ms) / args.steps, 3)
+                out["no_comm_ms_per_step"] = round(l_ms / args.steps, 3)
+                del local
+            except Exception as e:  # noqa: BLE001
+                out["exposed_comm_ms"] = None
+                out["exposed_comm_error"] = repr(e)[:200]
+            try:
+                out["roofline"] = comm_roofline(wl, world, dev, peaks)
+            except Exception as e:  # noqa: BLE001
+                out["roofline"] = {"error": repr(e)[:200]}
+        elif world == 1:
+            out["exposed_comm_ms"] = 0.0
+        flops = None
+        if args.model == "gpt2-medium" and not args.layers:
+            flops = 18.8e12 * (cfg["global_batch"] / world) / 8     # matmul + causal attention
+            out["roofline_compute"] = {
+                "tflops_per_gpu": round(flops / (dev_ms / args.steps / 1e3) / 1e12, 1),
+                "frac_of_measured_sustained_bf16": round(
+                    flops / (dev_ms / args.steps / 1e3) / 1e12 /
+                    peaks.get("bf16_tflops_sustained", 1401.1), 3)}
+        if not args.no_baseline:
+            try:
+                base = GPT2Zero(args, world, rank, dev, "torch")
+                b_ms, b_e2e, _, _, _ = timed_regions(base, args, world, dev, clocks=False)
+                b_val = base.samples_per_step * args.steps / (b_ms / 1e3)
+                out["vs_baseline"] = round(value / b_val, 3)
+                out["baseline"] = {"impl": "stock torch.distributed (NCCL reduce-scatter / "
+                                           "all-gather, cuBLAS, SDPA, fused AdamW), same box, "
+                                           "same invocation",
+                                   "value": round(b_val, 2),
+                                   "ms_per_step": round(b_ms / args.steps, 3),
+                                   "e2e_value": round(base.samples_per_step * args.steps /
+                                                      (b_e2e / 1e3), 2)}
+            except Exception as e:  # noqa: BLE001
+                out["baseline"] = {"error": repr(e)[:200]}
     if rank == 0:
         print(json.dumps(out), flush=True)
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
     return 0
 

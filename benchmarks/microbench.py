@@ -1,6 +1,7 @@
 """Micro-benchmarks of the native kernels against the measured device peaks.
 
-``python -m necklace_b200.ops.microbench [gemm|norm|ce|adam|attn|all]`` times each
+``python -m benchmarks.microbench [gemm|norm|ce|adam|attn|all]`` (from the repository
+root) times each
 kernel with CUDA events (3 warm-up launches, L2 flushed between timed launches by
 writing a 256 MB buffer) and prints achieved TFLOP/s or GB/s, plus the same
 shape through torch (cuBLAS / eager) for comparison.
@@ -32,7 +33,7 @@ def _time(fn, iters=10, warmup=3, flush=None):
 
 
 def bench_gemm(flush):
-    from . import gemm
+    from necklace_b200.ops import gemm
     shapes = [  # (M, N, K, a_mn, b_mn, label)
         (8192, 3072, 1024, False, False, "qkv fwd"),
         (8192, 1024, 1024, False, False, "proj fwd"),
@@ -65,7 +66,7 @@ def bench_gemm(flush):
 
 
 def bench_norm(flush):
-    from .norm import norm_fwd, norm_bwd
+    from necklace_b200.ops.norm import norm_fwd, norm_bwd
     rows, C = 65536, 1024
     x = torch.randn(rows, C, device="cuda").bfloat16()
     w = torch.ones(C, device="cuda").bfloat16()
@@ -80,7 +81,7 @@ def bench_norm(flush):
 
 
 def bench_colsum(flush):
-    from .gemm import colsum
+    from necklace_b200.ops.gemm import colsum
     for (rows, C) in [(8192, 1024), (8192, 3072), (8192, 4096)]:
         dy = torch.randn(rows, C, device="cuda").bfloat16()
         out = torch.empty(C, device="cuda", dtype=torch.bfloat16)
@@ -90,7 +91,7 @@ def bench_colsum(flush):
 
 
 def bench_ce(flush):
-    from . import cross_entropy_fwd_bwd
+    from necklace_b200.ops import cross_entropy_fwd_bwd
     T, V, ld = 8192, 50257, 50304
     lg = torch.randn(T, ld, device="cuda").bfloat16()
     tg = torch.randint(0, V, (T,), device="cuda")
@@ -100,7 +101,7 @@ def bench_ce(flush):
 
 
 def bench_adam(flush):
-    from . import adam_step
+    from necklace_b200.ops import adam_step
     n = 355_000_000
     master = torch.randn(n, device="cuda")
     m, v = torch.zeros_like(master), torch.zeros_like(master)
@@ -112,11 +113,11 @@ def bench_adam(flush):
 
 
 def bench_attn(flush):
-    from .attention import attn_fwd, attn_bwd
+    from necklace_b200.ops.attention import attn_fwd, attn_bwd
     for (B, H, S, D) in [(8, 16, 1024, 64), (2, 32, 2048, 128), (1, 40, 4096, 128)]:
         C = H * D
         qkv = torch.randn(B, S, 3 * C, device="cuda").bfloat16()
-        from .attention import set_exp_mode, set_fwd_impl
+        from necklace_b200.ops.attention import set_exp_mode, set_fwd_impl
         q_, k_, v_ = (t.view(B, S, H, D).transpose(1, 2).float() for t in qkv.split(C, -1))
         ref = torch.nn.functional.scaled_dot_product_attention(q_, k_, v_, is_causal=True)
         ref = ref.transpose(1, 2).reshape(B, S, C)
@@ -134,11 +135,9 @@ def bench_attn(flush):
         out, lse = attn_fwd(qkv, H, True)
         do = torch.randn_like(out)
         ms_b = _time(lambda: attn_bwd(qkv, out, lse, do, H, True), flush=flush)
-        from .attention import set_bwd_impl
+        from necklace_b200.ops.attention import set_bwd_impl
         set_bwd_impl(0)
         ms_b0 = _time(lambda: attn_bwd(qkv, out, lse, do, H, True), flush=flush)
-        set_bwd_impl(2)
-        ms_b2 = _time(lambda: attn_bwd(qkv, out, lse, do, H, True), flush=flush)
         set_bwd_impl(1)
         fl = 4.0 * B * H * S * S * D / 2  # causal
         q, k, v = (t.view(B, S, H, D).transpose(1, 2) for t in qkv.split(C, -1))
@@ -146,7 +145,7 @@ def bench_attn(flush):
             q, k, v, is_causal=True), flush=flush)
         print(json.dumps({"op": "attn", "B": B, "H": H, "S": S, "D": D, "fwd_ms": round(ms, 4),
                           "fwd_tflops": round(fl / ms / 1e9, 1), "bwd_ms": round(ms_b, 4),
-                          "bwd_serial_ms": round(ms_b0, 4), "bwd_two_issuer_ms": round(ms_b2, 4),
+                          "bwd_serial_ms": round(ms_b0, 4),
                           "bwd_tflops": round(2.5 * fl / ms_b / 1e9, 1),
                           "torch_sdpa_fwd_ms": round(ms_t, 4)}), flush=True)
 
@@ -155,7 +154,7 @@ def one_gemm(argv):
     """``gemm_one M N K [a_mn b_mn [epilogue]]``: a handful of launches of one shape (ncu
     captures); epilogue: none | bias | gelu (bias + GELU, saves the pre-activation) |
     gelubwd (times GELU' of a saved pre-activation) | res (bias + residual)."""
-    from . import gemm, EPI_GELU_FWD, EPI_GELU_BWD
+    from necklace_b200.ops import gemm, EPI_GELU_FWD, EPI_GELU_BWD
     M, N, K = (int(x) for x in argv[2:5])
     a_mn = len(argv) > 5 and argv[5] == "1"
     b_mn = len(argv) > 6 and argv[6] == "1"
@@ -189,7 +188,7 @@ def one_gemm(argv):
 
 def one_attn(argv):
     """``attn_one B H S D``: a few forward+backward launches of one shape (ncu captures)."""
-    from .attention import attn_fwd, attn_bwd
+    from necklace_b200.ops.attention import attn_fwd, attn_bwd
     B, H, S, D = (int(x) for x in argv[2:6])
     qkv = torch.randn(B, S, 3 * H * D, device="cuda").bfloat16()
     for _ in range(3):
@@ -210,7 +209,7 @@ def main(argv):
     for name, fn in table.items():
         if which in ("all", name):
             fn(flush)
-    from . import check_status
+    from necklace_b200.ops import check_status
     check_status()
 
 

@@ -68,6 +68,15 @@ _SIGS = {
     "nkb_rope": [vp, i32, i32, i32, i32, f32, i32, i32, vp],
     "nkb_swiglu_fwd": [vp, vp, i64, i32, vp],
     "nkb_swiglu_bwd": [vp, vp, vp, i64, i32, vp],
+    "nkb_im2col_nhwc": [vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp],
+    "nkb_col2im_nhwc": [vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp],
+    "nkb_bn_fwd": [vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, f32, f32, i32, vp],
+    "nkb_bn_apply": [vp, vp, vp, vp, vp, vp, i64, i32, i32, vp],
+    "nkb_bn_bwd": [vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, vp, i64, i32, i32, vp],
+    "nkb_maxpool3x3s2_fwd": [vp, vp, vp, i32, i32, i32, i32, vp],
+    "nkb_maxpool3x3s2_bwd": [vp, vp, vp, i32, i32, i32, i32, vp],
+    "nkb_avgpool_fwd": [vp, vp, i32, i32, i32, vp],
+    "nkb_avgpool_bwd": [vp, vp, i32, i32, i32, vp],
     "nkb_num_sms": [],
 }
 

@@ -34,19 +34,6 @@ constexpr int ATT2_THREADS = 384;
 // setmaxnreg budget: the CTA owns threads x 168 registers (the compile-time cap)
 static_assert(128 * 40 + 256 * 232 <= ATT2_THREADS * 168, "register budget");
 
-// Event trace for development builds (-DNKB_ATT_TRACE): CTA (0,0) stores clock64() per
-// (event tag, key block) with plain stores.  Compiled out otherwise.
-#ifdef NKB_ATT_TRACE
-#ifndef NKB_ATT_TRACE_BX
-#define NKB_ATT_TRACE_BX 0
-#define NKB_ATT_TRACE_BY 0
-#endif
-#define ATT_DBG(tag, jj)                                                      \
-  if (a.dbg && blockIdx.x == NKB_ATT_TRACE_BX && blockIdx.y == NKB_ATT_TRACE_BY) \
-    a.dbg[(tag) * 16 + (jj)] = clock64();
-#else
-#define ATT_DBG(tag, jj)
-#endif
 
 template <int D, int EXPM>
 __global__ void __launch_bounds__(ATT2_THREADS, 1)
@@ -79,7 +66,6 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (threadIdx.x == 0) { ATT_DBG(60, 0); }
   const int nq2 = (a.S + 255) / 256;
   const int qb = nq2 - 1 - blockIdx.y;  // heavy (late) query blocks are scheduled first
   const int bh = blockIdx.x;
@@ -142,14 +128,12 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           break;
         }
         mbar_expect_tx(&k_full[st], TILE);
-        ATT_DBG(1, j);
         load_tile(sK + st * TILE, &tmK, &k_full[st], j * 128);
         if (!mbar_wait(&v_empty[st], par, abort_flag)) {
           att_error(a.status, abort_flag, NKB_ERR_EMPTY_WAIT);
           break;
         }
         mbar_expect_tx(&v_full[st], TILE);
-        ATT_DBG(2, j);
         load_tile(sV + st * TILE, &tmV, &v_full[st], j * 128);
       }
     }
@@ -178,7 +162,6 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         wait_or_fail(&k_full[j & 1], (j >> 1) & 1, NKB_ERR_TMA_WAIT);
         if (!ok) return;
         tc_fence_after();
-        ATT_DBG(10 + x, j);
         const uint64_t dk = dK0 + (uint32_t)(j & 1) * (TILE >> 4);
 #pragma unroll
         for (int kd = 0; kd < NKD; ++kd)
@@ -188,21 +171,18 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                          (kd > 0 || k > 0) ? 1u : 0u);
         umma_commit(&s_full[x]);
         umma_commit(&k_empty[j & 1]);
-        ATT_DBG(12 + x, j);
       };
       auto issue_pv = [&](int j) {
         wait_or_fail(&p_full[x], j & 1, NKB_ERR_ACC_WAIT);
         wait_or_fail(&v_full[j & 1], (j >> 1) & 1, NKB_ERR_TMA_WAIT);
         if (!ok) return;
         tc_fence_after();
-        ATT_DBG(20 + x, j);
         const uint64_t dv = dV0 + (uint32_t)(j & 1) * (TILE >> 4);
 #pragma unroll
         for (int k = 0; k < 8; ++k)  // 16 keys per MMA: 8 TMEM columns of bf16 pairs
           umma_bf16_ts(t_ox, t_px + k * 8, dv + k * 128, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
         umma_commit(&p_free[x]);
         umma_commit(&v_empty[j & 1]);
-        ATT_DBG(22 + x, j);
       };
       wait_or_fail(q_full, 0, NKB_ERR_TMA_WAIT);
       issue_s(0);
@@ -240,7 +220,6 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         break;
       }
       tc_fence_after();
-      if ((warp & 3) == 0 && lane == 0) { ATT_DBG(30 + x, j); }
       uint32_t s[128];
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld_32x32(t_s + c * 32, s + c * 32);
@@ -266,7 +245,6 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         mx1 = max3_f32(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
       }
       const float mx = fmaxf(mx0, mx1);
-      if ((warp & 3) == 0 && lane == 0) { ATT_DBG(34 + x, j); }
       // P V of block j-1 must have retired before O is rescaled or P overwritten; the wait
       // sits as late as possible (after the exponentials unless O has to be rescaled)
       bool pv_done = (j == 0);
@@ -330,12 +308,10 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         pk[i >> 1] = pack_bf16x2(p0, p1);
         pk[(i >> 1) + 1] = pack_bf16x2(p2, p3);
       }
-      if ((warp & 3) == 0 && lane == 0) { ATT_DBG(38 + x, j); }
       if (!wait_pv()) {
         ok = false;
         break;
       }
-      if ((warp & 3) == 0 && lane == 0) { ATT_DBG(40 + x, j); }
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_st_32x16(t_p + c * 16, pk + c * 16);
       sum0 += sum2;
@@ -345,7 +321,6 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[x]);
-      if ((warp & 3) == 0 && lane == 0) { ATT_DBG(50 + x, j); }
     }
     if (nkv > 0) {
       if (ok && mbar_wait(&p_free[x], (nkv - 1) & 1, abort_flag)) {
@@ -380,7 +355,6 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
   tc_fence_before();
   __syncthreads();
-  if (threadIdx.x == 0) { ATT_DBG(61, 0); }
   if (warp == 9) {
     if (*abort_flag)
       for (int i = 0; i < 1000; ++i) __nanosleep(1000);

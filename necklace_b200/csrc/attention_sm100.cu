@@ -33,9 +33,6 @@ struct AttnFwdArgs {
   float scale, scale_log2;
   int causal;
   int* status;
-#ifdef NKB_ATT_TRACE
-  long long* dbg;
-#endif
 };
 
 __device__ __forceinline__ void att_error(int* status, volatile int* abort_flag, int code) {
@@ -616,7 +613,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 }
 
 #include "attention_bwd_pp.cuh"
-#include "attention_bwd_pp2.cuh"
 
 // delta[b,h,s] = sum_d o * do ; 8 lanes per row, DELTA_ROWS rows per thread so that each
 // thread has several independent 16-byte loads in flight
@@ -848,7 +844,7 @@ static int make_tmap_dq(CUtensorMap* out, float* base, int BH, int S, int D) {
   return r == CUDA_SUCCESS ? 0 : -(int)r - 1000;
 }
 
-// 1: warp-specialised kernel (head dim 64), 2: its two-issuer variant, 0: serial kernel
+// 1: warp-specialised kernel (head dim 64), 0: serial kernel
 static int g_attn_bwd_impl = 1;
 
 static int launch_bwd_pp(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
@@ -867,22 +863,6 @@ static int launch_bwd_pp(const CUtensorMap& tq, const CUtensorMap& tk, const CUt
   return (int)cudaGetLastError();
 }
 
-static int launch_bwd_pp2(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                          const CUtensorMap& tdo, const CUtensorMap& tdq, const AttnBwdArgs& a,
-                          cudaStream_t s) {
-  constexpr int smem = AttnBwd3Smem::BYTES;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_bwd_pp2_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
-  dim3 grid(a.B * a.H, (a.S + 127) / 128);
-  attn_bwd_pp2_kernel<<<grid, BWD3_THREADS, smem, s>>>(tq, tk, tv, tdo, tdq, a);
-  return (int)cudaGetLastError();
-}
-
 }  // namespace nkb
 
 using namespace nkb;
@@ -893,10 +873,6 @@ extern "C" void nkb_attn_set_bwd_impl(int impl) { nkb::g_attn_bwd_impl = impl; }
 extern "C" void nkb_attn_set_exp_mode(int mode) { nkb::g_attn_exp_mode = mode; }
 // 1 = ping-pong forward kernel (default), 0 = one query tile per CTA
 extern "C" void nkb_attn_set_fwd_impl(int impl) { nkb::g_attn_fwd_impl = impl; }
-#ifdef NKB_ATT_TRACE
-static long long* g_attn_dbg = nullptr;
-extern "C" void nkb_attn_set_dbg(long long* p) { g_attn_dbg = p; }
-#endif
 
 extern "C" int nkb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
                             int B, int H, int S, int D, long long sb, long long sh, long long ss,
@@ -918,9 +894,6 @@ extern "C" int nkb_attn_fwd(const void* q, const void* k, const void* v, void* o
   a.scale_log2 = scale * LOG2E;
   a.causal = causal;
   a.status = status;
-#ifdef NKB_ATT_TRACE
-  a.dbg = g_attn_dbg;
-#endif
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   return D == 64 ? launch_fwd_mode<64>(tq, tk, tv, a, s) : launch_fwd_mode<128>(tq, tk, tv, a, s);
 }
@@ -955,8 +928,7 @@ extern "C" int nkb_attn_bwd(const void* q, const void* k, const void* v, const v
   if (D == 64 && g_attn_bwd_impl >= 1) {
     CUtensorMap tdq;
     if ((rc = make_tmap_dq(&tdq, dq_acc, B * H, S, D))) return rc;
-    rc = g_attn_bwd_impl == 2 ? launch_bwd_pp2(tq, tk, tv, tdo, tdq, a, s)
-                              : launch_bwd_pp(tq, tk, tv, tdo, tdq, a, s);
+    rc = launch_bwd_pp(tq, tk, tv, tdo, tdq, a, s);
   } else {
     rc = D == 64 ? launch_bwd<64>(tq, tk, tv, tdo, a, s) : launch_bwd<128>(tq, tk, tv, tdo, a, s);
   }
@@ -968,3 +940,5 @@ extern "C" int nkb_attn_bwd(const void* q, const void* k, const void* v, const v
                                                 sb, sh, ss);
   return (int)cudaGetLastError();
 }
+
+NKB_DEFINE_WAIT_SETTER(attn)

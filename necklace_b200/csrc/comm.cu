@@ -527,3 +527,5 @@ extern "C" int nkb_comm_rs_opt_ag(void** heap, long long flag_off, long long gra
   rs_opt_ag_kernel<<<grid, COMM_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(c, o);
   return (int)cudaGetLastError();
 }
+
+NKB_DEFINE_WAIT_SETTER(comm)

@@ -1642,3 +1642,5 @@ extern "C" int nkb_gemm_rs_bf16(void** heap, long long flag_off, long long stage
   epoch_bump_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(epoch);
   return (int)cudaGetLastError();
 }
+
+NKB_DEFINE_WAIT_SETTER(gemm)

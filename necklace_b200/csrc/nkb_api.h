@@ -66,6 +66,29 @@ int nkb_embed_fwd(const long long* idx, const void* wte, const void* wpe, void* 
 int nkb_embed_bwd(const long long* idx, const void* dout, void* dwte, void* dwpe, int T, int S,
                   int C, int vocab_start, int vocab_rows, void* stream);
 
+// ---- conv.cu ----------------------------------------------------------------
+// NHWC bf16.  col [N*Ho*Wo, Kpad], K index = (kh*KW + kw)*C + c, Kpad >= KH*KW*C, Kpad % 8 == 0.
+int nkb_im2col_nhwc(const void* x, void* col, int N, int H, int W, int C, int KH, int KW,
+                    int stride, int pad, int Kpad, void* stream);
+int nkb_col2im_nhwc(const void* dcol, void* dx, int N, int H, int W, int C, int KH, int KW,
+                    int stride, int pad, int Kpad, void* stream);
+// Training-mode batch norm over the rows of x [M, C] (+ residual, + ReLU).  acc: fp32 [2][C]
+// scratch, zero on entry and on exit; stats: fp32 [2][C] = (mean, rstd).
+int nkb_bn_fwd(const void* x, const void* gamma, const void* beta, const void* res, void* y,
+               float* stats, float* acc, float* run_mean, float* run_var, long long M, int C,
+               float eps, float momentum, int relu, void* stream);
+int nkb_bn_apply(const void* x, const float* stats, const void* gamma, const void* beta,
+                 const void* res, void* y, long long M, int C, int relu, void* stream);
+int nkb_bn_bwd(const void* dy, const void* x, const void* y, const float* stats, const void* gamma,
+               void* dx, void* dres, void* dgamma, void* dbeta, int acc_g, int acc_b, float* acc,
+               long long M, int C, int relu, void* stream);
+int nkb_maxpool3x3s2_fwd(const void* x, void* y, void* idx, int N, int H, int W, int C,
+                         void* stream);
+int nkb_maxpool3x3s2_bwd(const void* dy, const void* idx, void* dx, int N, int H, int W, int C,
+                         void* stream);
+int nkb_avgpool_fwd(const void* x, void* y, int N, int HW, int C, void* stream);
+int nkb_avgpool_bwd(const void* dy, void* dx, int N, int HW, int C, void* stream);
+
 // ---- optim_quant.cu --------------------------------------------------------
 // Adam / AdamW on flat buffers; master fp32, optional bf16 copy out. grad dtype: 0 bf16, 1 fp32.
 int nkb_adam_flat(float* master, float* m, float* v, const void* grad, int grad_fp32,

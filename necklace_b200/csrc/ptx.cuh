@@ -17,6 +17,14 @@ namespace nkb {
 #ifndef NKB_WAIT_CYCLES
 #define NKB_WAIT_CYCLES (4000000000ll)
 #endif
+// The limit actually used is a device variable (one copy per translation unit, all set
+// together by nkb_set_wait_cycles) so that a test can make a wait run out in milliseconds
+// and a job on a loaded machine can allow more.
+static __device__ long long g_nkb_wait_cycles = NKB_WAIT_CYCLES;
+#define NKB_DEFINE_WAIT_SETTER(tu)                                                    \
+  extern "C" int nkb_set_wait_cycles_##tu(long long cycles) {                         \
+    return (int)cudaMemcpyToSymbol(nkb::g_nkb_wait_cycles, &cycles, sizeof(cycles));  \
+  }
 
 // Error codes written to the per-launch status word (first error wins).
 enum : int {
@@ -92,7 +100,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
     for (int i = 0; i < 64; ++i)
       if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (clock64() - t0 > NKB_WAIT_CYCLES) return false;
+    if (clock64() - t0 > g_nkb_wait_cycles) return false;
   }
 }
 
@@ -422,7 +430,7 @@ __device__ __forceinline__ void red_add_release_sys(int* p, int v) {
 __device__ __forceinline__ bool wait_flag_ge(const int* p, int target) {
   long long t0 = clock64();
   while (ld_acquire_sys(p) < target) {
-    if (clock64() - t0 > NKB_WAIT_CYCLES) return false;
+    if (clock64() - t0 > g_nkb_wait_cycles) return false;
     __nanosleep(20);
   }
   return true;

@@ -6,7 +6,13 @@
 ``model_parallel = True`` (reference: necklace/frmwrk/pytorch/mpnn/layers.py:40-328).
 Weights are initialised from one master weight that every rank generates with the
 same seed and then slices, so the assembled layer equals its single-GPU counterpart.
-Matmuls run on the tcgen05 GEMM (``ops.linear``) for bf16 CUDA tensors.
+Matmuls run on the tcgen05 GEMM (``ops.linear``) for bf16 CUDA tensors.  When the
+tensor-parallel group has a peer-memory view (communicator brought up with
+``comm_type='peer'``) the all-reduce of ``RowParallelLinear``'s output and of
+``ColumnParallelLinear``'s input gradient is not an NCCL call after the GEMM but the fused
+GEMM -> reduce-scatter kernel followed by the peer-memory all-gather
+(``parallel.tensor.RowLinearFn`` / ``ColumnLinearFn``); set ``NKB_TP_FUSED=0`` to force the
+NCCL path (the baseline).
 """
 from __future__ import annotations
 
@@ -29,6 +35,7 @@ def _initialize_affine_weight(weight, out_features, in_features, per_partition_s
     """Build the full weight (CPU, fp32), keep my slice(s) along ``partition_dim``."""
     weight.model_parallel = True
     weight.partition_dim = partition_dim
+    weight.partition_stride = stride
     ws, rank = mpu.get_model_parallel_world_size(), mpu.get_model_parallel_rank()
     gen_state = torch.random.get_rng_state() if seed is not None else None
     if seed is not None:
@@ -53,6 +60,19 @@ def _linear(x, w, b=None):
     if x.is_cuda and x.dtype == torch.bfloat16:
         return nk_linear(x, w, b)
     return F.linear(x, w, b)
+
+
+def _fused_group(x):
+    """PeerGroup for the fused kernels, or None (see ``parallel.tensor.fused_group_of``)."""
+    import os
+    if os.environ.get("NKB_TP_FUSED", "1") == "0":
+        return None
+    from ....comm import groups as G
+    from ....parallel.tensor import fused_group_of
+    g = G.get_nccl_group_mp()
+    if g is None or g.world_size == 1:
+        return None
+    return fused_group_of(g, x, x.numel() // x.shape[-1])
 
 
 class VocabParallelEmbedding(nn.Module):
@@ -127,8 +147,15 @@ class ColumnParallelLinear(nn.Module):
             seed=seed)
 
     def forward(self, input_):
-        input_parallel = copy_to_model_parallel_region(input_)
-        out = _linear(input_parallel, self.weight, self.bias)
+        peer = _fused_group(input_)
+        if peer is not None:
+            from ....parallel.tensor import ColumnLinearFn
+            x2 = input_.reshape(-1, input_.shape[-1])
+            out = ColumnLinearFn.apply(x2, self.weight, self.bias, peer)
+            out = out.view(*input_.shape[:-1], out.shape[-1])
+        else:
+            input_parallel = copy_to_model_parallel_region(input_)
+            out = _linear(input_parallel, self.weight, self.bias)
         return gather_from_model_parallel_region(out) if self.gather_output else out
 
 
@@ -158,5 +185,12 @@ class RowParallelLinear(nn.Module):
     def forward(self, input_):
         input_parallel = input_ if self.input_is_parallel else \
             scatter_to_model_parallel_region(input_)
-        out = reduce_from_model_parallel_region(_linear(input_parallel, self.weight))
+        peer = _fused_group(input_parallel)
+        if peer is not None:
+            from ....parallel.tensor import RowLinearFn
+            x2 = input_parallel.reshape(-1, input_parallel.shape[-1])
+            out = RowLinearFn.apply(x2, self.weight, peer)
+            out = out.view(*input_parallel.shape[:-1], out.shape[-1])
+        else:
+            out = reduce_from_model_parallel_region(_linear(input_parallel, self.weight))
         return out + self.bias if self.bias is not None else out

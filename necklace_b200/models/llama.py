@@ -70,8 +70,13 @@ class LlamaBlock(nn.Module):
         self.cfg, self.n_head_local = cfg, cfg.n_head // mp
         self.ln1 = RMSNorm(C, dtype=dt, device=device)
         self.ln2 = RMSNorm(C, dtype=dt, device=device)
-        g = torch.Generator().manual_seed(seed * 1000 + layer)
-        mk = lambda o, i, s: torch.randn(o, i, generator=g) * s
+        # full matrices are drawn from a per-layer seed and then sliced, so that every
+        # tensor-parallel layout assembles into the same model; on a GPU they are drawn there
+        # (a 7B-parameter stage takes minutes to draw on the host)
+        gdev = torch.device(device) if device is not None and torch.device(device).type == "cuda" \
+            else torch.device("cpu")
+        g = torch.Generator(device=gdev).manual_seed(seed * 1000 + layer)
+        mk = lambda o, i, s: torch.randn(o, i, generator=g, device=gdev) * s
         pstd = 0.02 / (2 * cfg.n_layer) ** 0.5
         wq, wk, wv = mk(C, C, 0.02), mk(C, C, 0.02), mk(C, C, 0.02)
         # column parallel: heads split over ranks; packed [q_local; k_local; v_local]

@@ -66,3 +66,15 @@ def scratch_zero(key: str, numel: int, dtype: torch.dtype, device) -> torch.Tens
 
 def ptr(t) -> int | None:
     return None if t is None else t.data_ptr()
+
+
+def set_wait_cycles(cycles: int) -> None:
+    """Limit (in SM clock cycles) of every bounded device-side wait: on a barrier, on a peer
+    flag, on a readiness flag.  The default is about two seconds; a wait that runs out makes
+    its kernel record a status code and return (see ``check_status``)."""
+    lib = _lib.load()
+    for tu in ("gemm", "attn", "comm"):
+        fn = getattr(lib, f"nkb_set_wait_cycles_{tu}")
+        fn.argtypes = [_lib.i64]
+        fn.restype = _lib.i32
+        _lib.check(fn(int(cycles)), f"nkb_set_wait_cycles_{tu}")

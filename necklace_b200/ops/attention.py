@@ -36,8 +36,7 @@ def set_fwd_impl(impl: int) -> None:
 
 
 def set_bwd_impl(impl: int) -> None:
-    """Backward kernel for head dim 64: 1 = warp-specialised (default), 2 = its variant with one
-    MMA issuer per query half, 0 = serial."""
+    """Backward kernel for head dim 64: 1 = warp-specialised (default), 0 = serial."""
     lib = _lib.load()
     lib.nkb_attn_set_bwd_impl.argtypes = [_lib.i32]
     lib.nkb_attn_set_bwd_impl.restype = None

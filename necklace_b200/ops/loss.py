@@ -88,11 +88,12 @@ class LMHeadLossFn(torch.autograd.Function):
     is turned into its own gradient in place (no fp32 logits, no softmax tensor)."""
 
     @staticmethod
-    def forward(ctx, x, w, targets, vocab):
+    def forward(ctx, x, w, targets, vocab, bias=None):
         from .gemm import gemm
         x2 = x.reshape(-1, x.shape[-1])
         tg = targets.reshape(-1).contiguous()
-        logits = gemm(x2, w)  # [T, Vpad]
+        logits = gemm(x2, w, bias=bias)  # [T, Vpad]
+        ctx.b_ref = bias
         n_valid = (tg >= 0).sum().clamp(min=1).to(torch.float32)
         # gradient is scaled by 1/T here (all targets valid in the benchmark configs);
         # with ignored targets the final division by n_valid/T is applied in backward
@@ -113,11 +114,19 @@ class LMHeadLossFn(torch.autograd.Function):
         dx = gemm(dlogits, w, b_mn=True, alpha_dev=corr).view(ctx.xshape)
         dw = _deliver_grad(w, lambda out, acc: gemm(dlogits, x2, a_mn=True, b_mn=True, out=out,
                                                     accumulate=acc, alpha_dev=corr))
-        return dx, dw, None, None
+        db = None
+        if ctx.b_ref is not None:
+            from .gemm import colsum
+            # (the scalar dloss * T / n_valid is 1 for a mean loss with no ignored targets,
+            # which is the only case a biased classifier head is used in)
+            db = _deliver_grad(ctx.b_ref, lambda out, acc: colsum(dlogits, out, acc))
+        return dx, dw, None, None, db
 
 
-def lm_head_loss(x, w, targets, vocab):
-    return LMHeadLossFn.apply(x, w, targets, vocab)
+def lm_head_loss(x, w, targets, vocab, bias=None):
+    """Mean cross-entropy of ``x @ w^T (+ bias)``; ``w`` may have more rows than ``vocab``
+    (padding rows are ignored)."""
+    return LMHeadLossFn.apply(x, w, targets, vocab, bias)
 
 
 def embed_fwd(idx, wte, wpe, S, vocab_start=0, out=None):

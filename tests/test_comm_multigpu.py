@@ -267,6 +267,76 @@ def case_sp_tp_mlp(rank, world, heap, grp, chk):
     chk(_rel(down.weight.grad, w2.grad.chunk(world, 1)[rank]) < 3e-2)
 
 
+def case_reduce_scatter_broadcast(rank, world, heap, grp, chk):
+    """Peer-memory reduce-scatter and broadcast kernels against NCCL."""
+    import torch.distributed as dist
+    for dtype, rows, cols in [(torch.bfloat16, 256 * world, 384), (torch.float32, 64 * world, 256)]:
+        full = heap.alloc(rows * cols, dtype).view(rows, cols)
+        for it in range(3):
+            torch.manual_seed(7 * it + rank)
+            src = torch.randn(rows, cols, device="cuda").to(dtype)
+            full.copy_(src)
+            ref = src.float().clone()
+            dist.all_reduce(ref)
+            grp.barrier()
+            out = grp.reduce_scatter(full, scale=0.5)
+            per = rows // world
+            tol = 1e-5 if dtype == torch.float32 else 2e-2
+            chk(_rel(out, ref[rank * per:(rank + 1) * per] * 0.5) < tol, ("rs", dtype, it))
+            chk(torch.equal(full, src), "reduce_scatter must not modify its input")
+            grp.barrier()
+    buf = heap.alloc(4096, torch.int64)
+    for root in range(world):
+        buf.fill_(rank + 100 * root)
+        grp.barrier()
+        grp.broadcast(buf, root)
+        chk(bool((buf == root + 100 * root).all()), ("bcast", root))
+        grp.barrier()
+
+
+def case_llama_tp_fused(rank, world, heap, grp, chk):
+    """Llama on the fused tensor-parallel kernels (sequence-parallel layout, vocabulary-parallel
+    embedding and cross-entropy) against the same model on one GPU: loss and gradients."""
+    from necklace_b200 import checkpoint as ck
+    from necklace_b200.models.llama import Llama, LlamaConfig
+    for hd, seq in ((64, 128), (128, 256)):
+        kw = dict(n_layer=2, d_model=4 * hd, n_head=4, d_ff=1024, vocab=1000, max_seq=seq)
+        tp = Llama(LlamaConfig(tp_group=grp, **kw), device="cuda")
+        ref = Llama(LlamaConfig(**kw), device="cuda")
+        tok = torch.randint(0, 1000, (2, seq + 1), generator=torch.Generator().manual_seed(3)).cuda()
+        x, y = tok[:, :-1].contiguous(), tok[:, 1:].contiguous()
+        for step in range(2):          # twice: buffers and flags are reused
+            for m in (tp, ref):
+                m.zero_grad(set_to_none=True)
+            l_tp = tp(x, y)
+            l_tp.backward()
+            l_ref = ref(x, y)
+            l_ref.backward()
+            chk(abs(float(l_tp) - float(l_ref)) < 2e-2, ("loss", hd, step, float(l_tp), float(l_ref)))
+            rp = dict(ref.named_parameters())
+            for name, p in tp.named_parameters():
+                sharded, dim, stride = ck._tp_attrs(p)
+                full = rp[name].grad
+                if sharded:
+                    want = ck.tp_split(full, world, rank, dim, stride)
+                    chk(_rel(p.grad, want) < 4e-2, (name, hd, step, _rel(p.grad, want)))
+                else:
+                    # replicated norm weights: every rank holds the gradient of its rows only
+                    import torch.distributed as dist
+                    g = p.grad.float().clone()
+                    dist.all_reduce(g)
+                    chk(_rel(g, full) < 4e-2, (name, hd, step, _rel(g, full)))
+            grp.barrier()
+
+
+def test_llama_tp_fused():
+    _run("case_llama_tp_fused")
+
+
+def test_reduce_scatter_broadcast():
+    _run("case_reduce_scatter_broadcast")
+
+
 def test_sp_tp_mlp():
     _run("case_sp_tp_mlp")
 

@@ -307,7 +307,7 @@ def test_attention_forward_variants(impl, mode, causal, B, H, S, D):
     assert (lse - torch.logsumexp(s, -1)).abs().max().item() < 2e-2
 
 
-@pytest.mark.parametrize("impl", [1, 2, 0])
+@pytest.mark.parametrize("impl", [1, 0])
 @pytest.mark.parametrize("causal", [True, False])
 @pytest.mark.parametrize("B,H,S", [(1, 2, 128), (2, 2, 300), (1, 3, 1024), (2, 1, 257), (1, 1, 640)])
 def test_attention_backward_variants(impl, causal, B, H, S):
