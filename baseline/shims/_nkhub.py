@@ -27,7 +27,8 @@ def unregister(server):
 def serve(timeout=0.0, extra=None):
     """Wait up to ``timeout`` seconds for a request on any registered server socket (or for
     ``extra``, a client socket waiting for its reply, to become readable), then run the
-    handlers of all requests that are ready.  Returns True if ``extra`` is readable."""
+    handler of the oldest request on each ready socket.  Returns True if ``extra`` is
+    readable."""
     socks = [s for s in _servers if not s._zstop]
     if not socks and extra is None:
         if timeout > 0:
@@ -44,7 +45,9 @@ def serve(timeout=0.0, extra=None):
         return False
     for s in socks:
         if s._zsock in ready:
-            # drain what is queued on this socket, oldest first
-            while s._handle_one(block=False):
-                pass
+            # One request per socket per call: the caller (a queue ``get``, a sleep, a reply
+            # wait) then looks at its own condition again, so a job that this request queued
+            # is taken up before a request that arrives later is handled, which is the
+            # order a gevent hub gives (the woken greenlet runs before later I/O events).
+            s._handle_one(block=False)
     return extra is not None and extra in ready

@@ -37,6 +37,8 @@ def spawn(fn, *args, **kwargs):
 def sleep(seconds=0):
     end = time.monotonic() + max(0.0, seconds or 0.0)
     _nkhub.serve(0.0)
+    if not seconds or seconds <= 0:
+        return
     while True:
         left = end - time.monotonic()
         if left <= 0:

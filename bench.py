@@ -55,6 +55,9 @@ def parse():
                     help="skip the stock-torch arm that is timed after ours for vs_baseline")
     ap.add_argument("--tp-impl", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--grad-comp-threshold", type=float, default=1e-3)
+    ap.add_argument("--launcher", default="torchrun", choices=["torchrun", "necklace"],
+                    help="necklace: run config 3 through the framework's own scheduler + "
+                         "worker processes (examples/gpt2/train_gpt2_necklace.py)")
     return ap.parse_args()
 
 
@@ -396,7 +399,8 @@ class LlamaHybrid(Workload):
             self.engine = PipelineEngine(
                 Stage(), stage=stage, pp_ranks=ppg.pg_ranks, micro_batches=n_mb,
                 group=dpg.comm.peer if dpg.world_size > 1 else None, heap=heap, mp_group=mp_peer,
-                optim=opt, bucket_mb=args.bucket_mb if args.bucket_mb > 0 else None)
+                optim=opt, bucket_mb=args.bucket_mb if args.bucket_mb > 0 else None,
+                grad_sync=net.make_grad_sync())
             self.has_data = stage == 0
             replicas = dpg.world_size
             par = f"dp={replicas} pp={pp} mp={mp}"
@@ -407,7 +411,8 @@ class LlamaHybrid(Workload):
                 net, mode="zero" if zrg.world_size > 1 else "local",
                 group=zrg.comm.peer if zrg.world_size > 1 else None, heap=heap, optim=opt,
                 micro_batches=n_mb, use_cuda_graph=False,
-                bucket_mb=args.bucket_mb if args.bucket_mb > 0 else None)
+                bucket_mb=args.bucket_mb if args.bucket_mb > 0 else None,
+                grad_sync=net.make_grad_sync())
             self.has_data = True
             replicas = zrg.world_size
             par = f"dp=1 zr={replicas} mp={mp}"
@@ -634,10 +639,99 @@ def comm_roofline(wl, world, dev, peaks):
                           "frac_of_measured_roofline": round(floor_ms / ms, 3)}}
 
 
+def necklace_launcher_arm(args):
+    """Config 3 through the framework's own process model: every rank of the launch starts
+    one worker of ``examples/gpt2/train_gpt2_necklace.py`` (scheduler / worker services over
+    ZeroMQ, ZeRO trainer with the native engine, peer-memory communicator), rank 0 also the
+    scheduler.  The workers time K steps with CUDA events from a trainer hook; every step
+    copies its batch from pinned host memory, so the number is an end-to-end one."""
+    import subprocess
+    import tempfile
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    tag = os.environ.get("MASTER_PORT", str(os.getpid())) if world > 1 else str(os.getpid())
+    work = os.path.join(tempfile.gettempdir(), f"nkb-launch-{tag}")
+    os.makedirs(work, exist_ok=True)
+    script = os.path.join(ROOT, "examples", "gpt2", "train_gpt2_necklace.py")
+    W, K = max(args.warmup, 3), args.steps
+    B = args.micro_batch or 8
+    env = dict(os.environ)
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT"):
+        env.pop(k, None)      # the workers rendezvous through the scheduler, not torchrun
+    svr = f"ipc://{work}/svr.ipc"
+    procs = []
+    if rank == 0:
+        procs.append(subprocess.Popen(
+            [sys.executable, script, "-r", "scheduler", "-w", str(world), "-u", svr, "-e", "1",
+             "--model", "medium" if args.model == "gpt2-medium" else "tiny"],
+            stdout=open(os.path.join(work, "sched.log"), "w"), stderr=subprocess.STDOUT, env=env))
+    out = os.path.join(work, f"rank{rank}.json")
+    cmd = [sys.executable, script, "-r", "worker", "-w", str(world), "-k", str(rank), "-g",
+           str(local_rank), "-u", f"ipc://{work}/w{rank}.ipc", "-s", svr, "-x", "peer",
+           "--model", "medium" if args.model == "gpt2-medium" else "tiny", "--micro-batch", str(B),
+           "--time-steps", str(K), "--time-warmup", str(W), "--out", out]
+    if world > 1:
+        cmd += ["-t", "dp+zr", "-dpsz", "1", "-zrsz", str(world)]
+    if not args.no_graph:
+        cmd.append("--graph")
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    procs.append(subprocess.Popen(cmd, stdout=open(os.path.join(work, f"w{rank}.log"), "w"),
+                                  stderr=subprocess.STDOUT, env=env))
+    try:
+        procs[-1].wait(timeout=600)
+    except subprocess.TimeoutExpired:
+        pass
+    clocks = sampler.stop()
+    for p in procs:                 # exactly the children started above
+        if p.poll() is None:
+            try:
+                p.wait(timeout=30)
+            except subprocess.TimeoutExpired:
+                p.kill()
+    if rank != 0:
+        return 0
+    res = []
+    for r in range(world):
+        f = os.path.join(work, f"rank{r}.json")
+        t_end = time.time() + 60
+        while not os.path.exists(f) and time.time() < t_end:
+            time.sleep(0.2)
+        if not os.path.exists(f):
+            tail = open(os.path.join(work, f"w{r if r == 0 else 0}.log")).read()[-300:]
+            print(json.dumps({"impl": "ours", "launcher": "necklace",
+                              "error": f"worker {r} wrote no result: {tail}"}))
+            return 1
+        res.append(json.load(open(f)))
+    ms = max(r["ms"] for r in res)
+    S = 1024 if args.model == "gpt2-medium" else 128
+    value = B * world * K / (ms / 1e3)
+    print(json.dumps({
+        "metric": METRIC, "value": round(value, 2), "unit": "samples/s", "n_gpus": world,
+        "steps": K, "warmup": W, "ms_per_step": round(ms / K, 3), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "impl": "ours", "launcher": "necklace",
+        "config": {"model": args.model, "global_batch": B * world, "seq_len": S,
+                   "parallelism": f"dp+zr (zr={world})", "optimizer": "adam fp32 master",
+                   "process_model": "scheduler + one worker per GPU over ZeroMQ, "
+                                    "trainer zroppd.TrainerMPOPPytorch(engine='native'), "
+                                    "comm_type peer", "cuda_graph": not args.no_graph,
+                   "l2": "working set exceeds L2; no explicit flush"},
+        "clocks": clocks,
+        "e2e": {"value": round(value, 2), "unit": "samples/s", "ms_per_step": round(ms / K, 3),
+                "h2d_bytes_per_step": B * S * 8 * 2, "d2h_bytes_per_step": 0,
+                "note": "same run: the trainer copies every batch from pinned host memory"},
+        "loss_last": res[0]["loss"]}), flush=True)
+    return 0
+
+
 def main():
     args = parse()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.launcher == "necklace":
+        return necklace_launcher_arm(args)
 
     import torch
     import torch.distributed as dist

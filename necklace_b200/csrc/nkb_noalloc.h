@@ -34,7 +34,9 @@ extern "C" {
 //
 // First call on each device: looks the array's device address up with
 // cudaGetSymbolAddress (with that device current) and caches it.  Make that first
-// call before starting any stream capture on that device.
+// call before starting any stream capture on that device.  The cached address is an
+// atomic pointer: host threads may race on the first call (both look up and store the
+// same value).
 //
 // The scratch is shared by every call in the process and keeps the previous call's
 // contents; each call clears the part it uses on `stream` before accumulating.

@@ -429,7 +429,11 @@ static __device__ __align__(256) float g_noalloc_colsum_scratch[2 * NKB_NOALLOC_
 // Device address of the scratch array per device ordinal.  The array's name is only
 // a host-side handle; kernels must be given the address cudaGetSymbolAddress returns
 // while the owning device is current.
-static float* g_noalloc_scratch_ptr[64] = {nullptr};
+// Filled on the first call per device.  Two host threads making that first call at the
+// same time both store the same address, so the slot is an atomic pointer (no lock needed:
+// the look-up is idempotent) and readers never see a torn value.
+#include <atomic>
+static std::atomic<float*> g_noalloc_scratch_ptr[64];
 
 extern "C" int nkb_colsum_bf16_noalloc(const void* dy, void* out, int rows, int C, long long ld,
                                        void* stream) {
@@ -440,13 +444,14 @@ extern "C" int nkb_colsum_bf16_noalloc(const void* dy, void* out, int rows, int 
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
   if (dev < 0 || dev >= 64) return -5;
-  if (!g_noalloc_scratch_ptr[dev]) {
+  float* acc = g_noalloc_scratch_ptr[dev].load(std::memory_order_acquire);
+  if (!acc) {
     void* p = nullptr;
     e = cudaGetSymbolAddress(&p, g_noalloc_colsum_scratch);
     if (e != cudaSuccess) return (int)e;
-    g_noalloc_scratch_ptr[dev] = static_cast<float*>(p);
+    acc = static_cast<float*>(p);
+    g_noalloc_scratch_ptr[dev].store(acc, std::memory_order_release);
   }
-  float* acc = g_noalloc_scratch_ptr[dev];
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   // only the plain-sum half [C, 2C) is used; it must start at zero for every call
   e = cudaMemsetAsync(acc + C, 0, sizeof(float) * (size_t)C, s);

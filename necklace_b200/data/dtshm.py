@@ -1,5 +1,4 @@
-"""Shared-memory ring loader under the reference's module name
-(necklace/data/dtshm.py exports DataLoaderSharedMemory; the pickled-object,
-numpy and MXNet shared-memory variants of the reference collapse into the one
-torch-tensor ring implementation)."""
-from .loaders import ShmRingDataLoader as DataLoaderSharedMemory  # noqa: F401
+"""Shared-memory loader for batches of arbitrary picklable objects, under the reference's
+module name (necklace/data/dtshm.py exports ``DataLoaderSharedMemory``): worker processes
+pickle each collated batch into a ring of POSIX shared-memory slots (``data.shmem``)."""
+from .loaders import ShmObjectRingDataLoader as DataLoaderSharedMemory  # noqa: F401

@@ -263,5 +263,104 @@ class ShmRingDataLoader(_LoaderBase):
         return self._to_device_iter(self._raw_iter())
 
 
+def _object_ring_worker(dataset, collate, q_ctl, q_msg, ring_name, slot_bytes, part_num):
+    from .shmem import SharedMemArray
+    ring = SharedMemArray(ring_name, slot_bytes, part_num)
+    free = list(range(part_num))
+    while True:
+        msg = q_ctl.get()
+        if msg[0] == _STOP:
+            ring.close()
+            return
+        if msg[0] == _FREE:
+            free.append(msg[1])
+            continue
+        if msg[0] != _EPOCH:
+            continue
+        free = list(range(part_num))
+        for batch in msg[1]:
+            while not free:
+                m = q_ctl.get()
+                if m[0] == _STOP:
+                    ring.close()
+                    return
+                if m[0] == _FREE:
+                    free.append(m[1])
+            slot = free.pop(0)
+            try:
+                ring[slot] = collate([dataset[i] for i in batch])
+                q_msg.put(("batch", slot, 0))
+            except Exception as e:  # noqa: BLE001
+                q_msg.put(("error", repr(e), 0))
+                break
+        q_msg.put(("end", -1, 0))
+
+
+def _samples_as_they_are(samples):
+    return samples
+
+
+class ShmObjectRingDataLoader(_LoaderBase):
+    """Ring of pickled batches in POSIX shared memory: a batch may be any picklable object
+    (nested lists, dicts, numpy arrays, variable shapes), up to ``slot_bytes`` per batch.
+    This is the design of the reference's ``dtmem`` / ``dtshm`` / ``dtshmp`` loaders
+    (necklace/data/dtmem.py:19-396 over necklace/data/shmem.py); the default collate function
+    here returns the list of samples unchanged."""
+
+    def __init__(self, dataset, batch_size, slot_bytes: int = 1 << 20, **kw):
+        kw.setdefault("inter_batchify_fn", _samples_as_they_are)
+        super().__init__(dataset, batch_size, **kw)
+        self.slot_bytes = int(slot_bytes)
+
+    def _start(self):
+        from .shmem import SharedMemArray
+        self.qs_ctl = [self._ctx.Queue() for _ in range(self.num_workers)]
+        self.qs_msg = [self._ctx.Queue() for _ in range(self.num_workers)]
+        self.rings = []
+        for w in range(self.num_workers):
+            ring = SharedMemArray(None, self.slot_bytes, self.part_num)
+            self.rings.append(ring)
+            p = self._ctx.Process(target=_object_ring_worker, daemon=True,
+                                  args=(self.dataset, self.collate, self.qs_ctl[w], self.qs_msg[w],
+                                        ring.name, self.slot_bytes, self.part_num))
+            p.start()
+            self._procs.append(p)
+        self._started = True
+
+    def _raw_iter(self):
+        if not self._started:
+            self._start()
+        batches = self._epoch_batches()
+        for w in range(self.num_workers):
+            self.qs_ctl[w].put((_EPOCH, _batches_for(w, self.num_workers, batches)))
+        live = [True] * self.num_workers
+        w = 0
+        while any(live):
+            if live[w]:
+                try:
+                    kind, slot, _ = self.qs_msg[w].get(timeout=self.timeout)
+                except pyqueue.Empty:
+                    raise RuntimeError(f"data worker {w} produced nothing for {self.timeout}s")
+                if kind == "end":
+                    live[w] = False
+                elif kind == "error":
+                    raise RuntimeError(f"data worker {w} failed: {slot}")
+                else:
+                    item = self.rings[w][slot]
+                    self.qs_ctl[w].put((_FREE, slot))
+                    yield self._finish(item)
+            w = (w + 1) % self.num_workers
+
+    def __iter__(self):
+        return self._raw_iter()
+
+    def clear(self):
+        super().clear()
+        for ring in getattr(self, "rings", []):
+            ring.close()
+            ring.unlink()
+        self.rings = []
+
+
 # the class name every loader module of the reference exports
 DataLoaderSharedMemory = ShmRingDataLoader

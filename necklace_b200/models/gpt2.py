@@ -95,6 +95,8 @@ class GPT2Head(nn.Module):
     both live in the same process; a pipeline stage that holds only the head owns
     its own copy."""
 
+    computes_loss = True      # forward(x, targets) -> loss (see zroppt's native engine)
+
     def __init__(self, cfg: GPT2Config, wte: nn.Parameter | None = None, device=None):
         super().__init__()
         self.vocab = cfg.vocab

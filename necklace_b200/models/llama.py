@@ -212,3 +212,14 @@ class Llama(nn.Module):
 
     def num_params(self):
         return sum(p.numel() for p in self.parameters())
+
+    def make_grad_sync(self):
+        """Callable for ``TrainEngine(grad_sync=...)``: with the fused tensor-parallel layout
+        the norm weights' gradients must be summed over the group once per step (see
+        ``parallel.tensor.ReplicatedGradSync``).  None when there is nothing to do."""
+        g = self.cfg.tp_group
+        if g is None or g.world == 1:
+            return None
+        from ..parallel.tensor import ReplicatedGradSync
+        rep = [p for p in self.parameters() if not getattr(p, "model_parallel", False)]
+        return ReplicatedGradSync(rep, g)

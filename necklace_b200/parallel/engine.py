@@ -72,7 +72,7 @@ class TrainEngine:
                  optim: OptimConfig | None = None, grad_comp: GradCompConfig | None = None,
                  use_cuda_graph: bool = False, grad_average: bool = True,
                  micro_batches: int = 1, bucket_mb: float | None = None, comm_ctas: int = 32,
-                 clip_grad_norm: float | None = None):
+                 clip_grad_norm: float | None = None, grad_sync=None):
         assert mode in ("local", "dp", "zero")
         self.model, self.mode, self.group, self.heap = model, mode, group, heap
         self.optim = optim or OptimConfig()
@@ -83,6 +83,10 @@ class TrainEngine:
         self.grad_scale = ((1.0 / self.world) if grad_average else 1.0) / self.micro_batches
         self.clip = clip_grad_norm
         self.comm_ctas = comm_ctas
+        # optional callable run once per step after the last backward and before any bucket
+        # that holds the parameters it touches is reduced (``grad_sync.params``): used for
+        # gradients that another parallel dimension has to combine first
+        self.grad_sync = grad_sync
         alloc = None
         if heap is not None and self.world > 1:
             alloc = lambda n, dt: heap.alloc(n, dt)
@@ -210,6 +214,8 @@ class TrainEngine:
         last = {}
         for k, i in enumerate(seq):
             last[i] = k
+        for p in getattr(self.grad_sync, "params", ()):   # their buckets wait for grad_sync
+            last.pop(self._pidx.get(id(p)), None)
         fire: dict[int, list[int]] = {}
         for b, (lo, hi) in enumerate(self.buckets):
             need = -1
@@ -341,6 +347,8 @@ class TrainEngine:
         learn = self._comm_stream is not None and self._order is None
         self._recording = [] if learn else None
         loss = self._fwd_bwd(*inputs)
+        if self.grad_sync is not None:
+            self.grad_sync()
         side = self._comm_stream is not None and not learn
         for b in range(len(self.buckets)):
             self._launch_bucket(b, side=side)

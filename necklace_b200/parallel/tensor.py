@@ -295,6 +295,49 @@ def vocab_parallel_lm_head_loss(x_shard, w, targets, vocab, group):
     return VocabParallelLMHeadLossFn.apply(x_shard, w, targets, vocab, group)
 
 
+class ReplicatedGradSync:
+    """Sums, over the tensor-parallel group, the gradients of the parameters that are
+    replicated on every rank of it (norm weights).  In the sequence-parallel layout each rank
+    normalises only its own rows, so each rank holds only its rows' share of those gradients.
+    One call per optimizer step, after the last backward: the gradients (views into the flat
+    gradient buffer, or ``.grad``) are packed into one staging buffer in the symmetric heap,
+    reduced by the peer-memory all-reduce kernel and unpacked, i.e. three launches however
+    many norm layers there are."""
+
+    def __init__(self, params, group):
+        self.params = [p for p in params if p.requires_grad]
+        self.group = group
+        self.sizes = [p.numel() for p in self.params]
+        n = sum(self.sizes)
+        self.n = n
+        self.buf = None
+        if self.params and group.world > 1:
+            p0 = self.params[0]
+            heap = getattr(group, "heap", None)
+            npad = (n + 127) // 128 * 128
+            self.buf = heap.alloc(npad, p0.dtype) if heap is not None else \
+                torch.zeros(npad, dtype=p0.dtype, device=p0.device)
+
+    def _grads(self):
+        out = []
+        for p in self.params:
+            g = getattr(p, "_nkb_grad", None)
+            if g is None:
+                g = p.grad
+            out.append(g)
+        return out
+
+    def __call__(self):
+        if self.buf is None:
+            return
+        grads = self._grads()
+        if any(g is None for g in grads):
+            return
+        torch.cat([g.reshape(-1) for g in grads], out=self.buf[:self.n])
+        self.group.all_reduce(self.buf)
+        torch._foreach_copy_([g.reshape(-1) for g in grads], list(self.buf[:self.n].split(self.sizes)))
+
+
 # ------------------------------------------ replicated-activation (Megatron) layout, fused
 class ColumnLinearFn(torch.autograd.Function):
     """Column-parallel linear on a replicated input: ``y_r = x W_r^T (+ b_r)``; the input

@@ -276,9 +276,14 @@ class TrainerMPOPPytorch(TrainerOPPytorch):
 
                 def forward(s, data, target):
                     x = data
-                    for m in s.parts:
+                    for m in s.parts[:-1]:
                         x = m(x)
-                    return loss_fn(x, target)
+                    last = s.parts[-1]
+                    # a last unit that fuses its projection with the loss (no logits
+                    # tensor) takes the target itself
+                    if getattr(last, "computes_loss", False):
+                        return last(x, target)
+                    return loss_fn(last(x), target)
 
             whole = _Whole(self.nets).to(self.ctx)
             ok = self.cfg.get("optimizer_params") or {}
@@ -290,7 +295,9 @@ class TrainerMPOPPytorch(TrainerOPPytorch):
             comm = getattr(grp, "comm", None)
             peer = getattr(comm, "peer", None)
             group = peer if peer is not None else comm
-            self.native = TrainEngine(whole, mode="zero", group=group, heap=get_heap(), optim=oc)
+            ek = dict(self.cfg.get("engine_kwargs") or {})   # use_cuda_graph, bucket_mb, ...
+            self.native = TrainEngine(whole, mode="zero", group=group, heap=get_heap(), optim=oc,
+                                      **ek)
         return self.native
 
     def _run_steps_native(self, typ, n):

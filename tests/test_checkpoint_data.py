@@ -173,3 +173,46 @@ def test_hook_order_and_return_override():
     assert t.one_step() == "overridden"
     for ev in ("train", "epoch", "data_batch", "batch", "do_a_batch_grads", "do_a_train_step"):
         assert hasattr(t, f"register_hook_before_{ev}") and hasattr(t, f"register_hook_after_{ev}")
+
+
+def test_posix_shared_memory_object_lists():
+    from necklace_b200.data.shmem import SharedMemArray, SharedMemList
+    lst = SharedMemList(obj_size=256, obj_cnt=4)
+    lst[2] = {"a": [1, 2, 3]}
+    other = SharedMemList(lst.name, 256, 4)
+    assert other[2] == {"a": [1, 2, 3]}
+    other.close()
+    lst.close()
+    lst.unlink()
+    arr = SharedMemArray(obj_size=512, obj_cnt=3)
+    arr[0] = "x" * 100
+    arr[1] = (1, 2.5, None)
+    att = SharedMemArray(arr.name, 512, 3)
+    assert att[0] == "x" * 100 and att[1] == (1, 2.5, None) and att[2] is None
+    with pytest.raises(ValueError):
+        arr[2] = "y" * 1000
+    att.close()
+    arr.close()
+    arr.unlink()
+
+
+class _RaggedDataset:
+    def __len__(self):
+        return 10
+
+    def __getitem__(self, i):
+        return {"idx": i, "tokens": list(range(i % 4 + 1))}
+
+
+def test_object_ring_loader_yields_arbitrary_batches_in_order():
+    from necklace_b200.data.dtmem import DataLoaderSharedMemory
+    from necklace_b200.cuda.ncclwrp import PYNCCL_DTYPE_MAP, torch_dtype
+    dl = DataLoaderSharedMemory(_RaggedDataset(), 3, num_workers=2, part_num=2, last_batch="keep")
+    try:
+        for _ in range(2):
+            got = [b for b in dl]
+            assert [s["idx"] for b in got for s in b] == list(range(10))
+            assert got[1][0]["tokens"] == [0, 1, 2, 3]
+    finally:
+        dl.clear()
+    assert PYNCCL_DTYPE_MAP["float"] == 7 and torch_dtype("half") == torch.float16

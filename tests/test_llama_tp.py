@@ -115,3 +115,61 @@ def test_tp_checkpoint_reshards_between_mp_sizes():
         ck.load_tp_state_dict(got, full, ws=4, rank=r)
         for (n, a), (_, b) in zip(got.named_parameters(), want.named_parameters()):
             assert torch.equal(a, b), (n, r)
+
+
+def _zr_mp_worker(rank, world, port, q):
+    """dp+zr+mp with zr=2 (outer), mp=2 (inner): mp groups [0,1] [2,3], zr groups [0,2] [1,3]."""
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from necklace_b200.comm.symm import TorchGroup
+    from necklace_b200.models.llama import Llama
+    from necklace_b200.parallel.engine import OptimConfig, TrainEngine
+    mp_groups, zr_groups = [[0, 1], [2, 3]], [[0, 2], [1, 3]]
+    mp_pg = [dist.new_group(g) for g in mp_groups]
+    zr_pg = [dist.new_group(g) for g in zr_groups]
+    tp = TorchGroup(mp_pg[rank // 2], ranks=mp_groups[rank // 2])
+    zr = TorchGroup(zr_pg[rank % 2], ranks=zr_groups[rank % 2])
+    net = Llama(_cfg(tp_group=tp))
+    eng = TrainEngine(net, mode="zero", group=zr, optim=OptimConfig("adam", lr=1e-2),
+                      micro_batches=2, grad_sync=net.make_grad_sync())
+    tok = torch.randint(0, 200, (8, 33), generator=torch.Generator().manual_seed(9))
+    mine = tok[(rank // 2) * 4:(rank // 2) * 4 + 4]      # each zr rank is a data-parallel replica
+    losses = [float(eng.step(mine[:, :-1].contiguous(), mine[:, 1:].contiguous())) for _ in range(2)]
+    q.put((rank, losses, {n: p.detach().numpy().copy() for n, p in net.named_parameters()}))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_zero_over_tensor_parallel_llama_with_accumulation_matches_single_process():
+    import torch.multiprocessing as mp
+    from necklace_b200 import checkpoint as ck
+    from necklace_b200.models.llama import Llama
+    from necklace_b200.parallel.engine import OptimConfig, TrainEngine
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_zr_mp_worker, args=(r, 4, port, q)) for r in range(4)]
+    for p in procs:
+        p.start()
+    res = {r: (l, sd) for r, l, sd in (q.get(timeout=250) for _ in procs)}
+    for p in procs:
+        p.join(60)
+    ref_net = Llama(_cfg())
+    ref = TrainEngine(ref_net, optim=OptimConfig("adam", lr=1e-2), micro_batches=4)
+    tok = torch.randint(0, 200, (8, 33), generator=torch.Generator().manual_seed(9))
+    # global batch = 2 replicas x 2 micro-batches of 2 sequences; same order of micro-batches
+    for _ in range(2):
+        ref.step(tok[:, :-1].contiguous(), tok[:, 1:].contiguous())
+    tp_model = Llama(_cfg(mp=2, mp_rank=0))
+    rel = lambda a, b: float((a - b).norm() / (b.norm() + 1e-12))
+    for name, want in ref_net.named_parameters():
+        sharded, dim, stride = ck._tp_attrs(dict(tp_model.named_parameters())[name])
+        if name in ("embed.wte", "head.w_out"):
+            sharded, dim, stride = True, 0, 1
+        shards = [torch.from_numpy(res[m][1][name]) for m in range(2)]
+        got = ck.tp_concat(shards, dim, stride) if sharded else shards[0]
+        assert rel(got, want.detach()) < 2e-3, (name, rel(got, want.detach()))
+        other = [torch.from_numpy(res[2 + m][1][name]) for m in range(2)]
+        assert torch.equal(shards[0], other[0]), name      # the two zr ranks agree

@@ -266,3 +266,31 @@ def test_protocol_phases_against_fake_trainer(tmp_path):
                    "fn_nccl_all_reduce_start", "fn_one_step_start", "fn_nccl_all_reduce_start",
                    "fn_one_step_start", "fn_next_epoch_start"]
     assert svc.history[-2][1] == {0: "epoch_end", 1: "epoch_end"}
+
+
+@pytest.mark.timeout(300)
+def test_gpt2_zero_through_scheduler_and_workers_cpu(tmp_path):
+    """The headline's process model on CPU: scheduler + 2 workers over ipc, ZeRO trainer with
+    the native engine (gloo stand-in group), timed by the trainer hook."""
+    script = os.path.join(ROOT, "examples", "gpt2", "train_gpt2_necklace.py")
+    svr = f"ipc://{tmp_path}/svr.ipc"
+    procs = [subprocess.Popen([sys.executable, script, "-r", "scheduler", "-w", "2", "-u", svr,
+                               "-e", "1"], stdout=open(tmp_path / "s.log", "w"),
+                              stderr=subprocess.STDOUT, cwd=ROOT)]
+    for r in range(2):
+        procs.append(subprocess.Popen(
+            [sys.executable, script, "-r", "worker", "-w", "2", "-k", str(r), "-u",
+             f"ipc://{tmp_path}/w{r}.ipc", "-s", svr, "-t", "dp+zr", "-dpsz", "1", "-zrsz", "2",
+             "--no-cuda", "--time-steps", "3", "--time-warmup", "2", "--micro-batch", "2",
+             "--out", str(tmp_path / f"o{r}.json")],
+            stdout=open(tmp_path / f"w{r}.log", "w"), stderr=subprocess.STDOUT, cwd=ROOT))
+    codes = []
+    for p in procs:
+        try:
+            codes.append(p.wait(timeout=240))
+        except subprocess.TimeoutExpired:
+            p.kill()
+            codes.append(-9)
+    assert codes == [0, 0, 0], open(tmp_path / "w0.log").read()[-2000:]
+    outs = [json.load(open(tmp_path / f"o{r}.json")) for r in range(2)]
+    assert all(o["steps"] == 3 and o["ms"] > 0 and o["loss"] < 7.5 for o in outs)
