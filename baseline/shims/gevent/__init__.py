@@ -35,6 +35,15 @@ def spawn(fn, *args, **kwargs):
 
 
 def sleep(seconds=0):
+    # The reference sprinkles sub-millisecond sleeps ("wait the zrpc call to return") so that
+    # the server greenlet can finish sending a reply before the service loop goes on.  Here a
+    # reply has always been sent when its handler returns, and serving NEW requests inside
+    # such a sleep would let a request that the original stack delivers a millisecond later
+    # (zerorpc's per-call latency) overtake the job that the service loop has just taken from
+    # its queue.  So sleeps below a millisecond only sleep; longer ones serve requests.
+    if seconds and 0 < seconds < 1e-3:
+        time.sleep(seconds)
+        return
     end = time.monotonic() + max(0.0, seconds or 0.0)
     _nkhub.serve(0.0)
     if not seconds or seconds <= 0:

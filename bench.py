@@ -145,8 +145,10 @@ def reference_arm(args):
               "--model", args.model, "--micro-batch", str(B), "--seq", str(S),
               "--server-url", f"ipc://{work}/svr.ipc"]
     env = dict(os.environ, NCCL_DEBUG=os.environ.get("NCCL_DEBUG", "WARN"))
-    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT"):
-        env.pop(k, None)   # the reference has its own bring-up (unique id relayed over RPC)
+    for k in list(env):    # the reference has its own bring-up (unique id relayed over RPC)
+        if k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT") or \
+                k.startswith("TORCHELASTIC_"):
+            env.pop(k)
     procs = []
     if rank == 0:
         procs.append(subprocess.Popen(
@@ -657,8 +659,11 @@ def necklace_launcher_arm(args):
     W, K = max(args.warmup, 3), args.steps
     B = args.micro_batch or 8
     env = dict(os.environ)
-    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT"):
-        env.pop(k, None)      # the workers rendezvous through the scheduler, not torchrun
+    for k in list(env):           # the workers rendezvous through the scheduler, not torchrun
+        if k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT", "GROUP_RANK",
+                 "ROLE_RANK", "LOCAL_WORLD_SIZE", "ROLE_WORLD_SIZE", "GROUP_WORLD_SIZE") or \
+                k.startswith("TORCHELASTIC_"):
+            env.pop(k)
     svr = f"ipc://{work}/svr.ipc"
     procs = []
     if rank == 0:

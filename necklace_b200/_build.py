@@ -18,6 +18,9 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 BUILD = os.path.join(os.path.dirname(HERE), "build", "nkb200")
 LIB = os.path.join(HERE, "_nkb200.so")
+# the bounds-checked debug variant (-DNKB_DEBUG_BOUNDS): ``--debug-bounds``
+BUILD_DBG = os.path.join(os.path.dirname(HERE), "build", "nkb200_dbg")
+LIB_DBG = os.path.join(HERE, "_nkb200_dbg.so")
 
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--use_fast_math",
@@ -40,12 +43,14 @@ def _headers_mtime() -> float:
     return max((os.path.getmtime(h) for h in hs), default=0.0)
 
 
-def _compile_one(src: str, force: bool, verbose: bool) -> tuple[str, str]:
-    obj = os.path.join(BUILD, os.path.basename(src)[:-3] + ".o")
+def _compile_one(src: str, force: bool, verbose: bool, debug_bounds: bool = False
+                 ) -> tuple[str, str]:
+    obj = os.path.join(BUILD_DBG if debug_bounds else BUILD, os.path.basename(src)[:-3] + ".o")
     newest = max(os.path.getmtime(src), _headers_mtime())
     if not force and os.path.exists(obj) and os.path.getmtime(obj) >= newest:
         return obj, ""
-    cmd = [_nvcc(), *ARCH_FLAGS, *NVCC_FLAGS, "-I", CSRC, "-c", src, "-o", obj]
+    extra = ["-DNKB_DEBUG_BOUNDS"] if debug_bounds else []
+    cmd = [_nvcc(), *ARCH_FLAGS, *NVCC_FLAGS, *extra, "-I", CSRC, "-c", src, "-o", obj]
     p = subprocess.run(cmd, capture_output=True, text=True)
     log = p.stdout + p.stderr
     if p.returncode != 0:
@@ -57,22 +62,24 @@ def _compile_one(src: str, force: bool, verbose: bool) -> tuple[str, str]:
     return obj, log
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    """Compile and link; returns the path of the shared library."""
-    os.makedirs(BUILD, exist_ok=True)
+def build(force: bool = False, verbose: bool = False, debug_bounds: bool = False) -> str:
+    """Compile and link; returns the path of the shared library.  ``debug_bounds`` builds the
+    variant whose hand-indexed kernels check every index against the tensor extents."""
+    bdir, lib = (BUILD_DBG, LIB_DBG) if debug_bounds else (BUILD, LIB)
+    os.makedirs(bdir, exist_ok=True)
     srcs = sources()
     with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
-        results = list(ex.map(lambda s: _compile_one(s, force, verbose), srcs))
+        results = list(ex.map(lambda s: _compile_one(s, force, verbose, debug_bounds), srcs))
     objs = [o for o, _ in results]
-    relink = force or not os.path.exists(LIB) or any(
-        os.path.getmtime(o) > os.path.getmtime(LIB) for o in objs)
+    relink = force or not os.path.exists(lib) or any(
+        os.path.getmtime(o) > os.path.getmtime(lib) for o in objs)
     if relink:
-        cmd = [_nvcc(), *ARCH_FLAGS, "-shared", "-Xcompiler", "-fPIC", "-o", LIB, *objs,
+        cmd = [_nvcc(), *ARCH_FLAGS, "-shared", "-Xcompiler", "-fPIC", "-o", lib, *objs,
                "-lcudart"]
         p = subprocess.run(cmd, capture_output=True, text=True)
         if p.returncode != 0:
             raise RuntimeError(f"link failed:\n{p.stdout}{p.stderr}")
-    return LIB
+    return lib
 
 
 def resource_report() -> str:
@@ -89,5 +96,6 @@ def resource_report() -> str:
 
 
 if __name__ == "__main__":
-    lib = build(force="--force" in sys.argv, verbose="-v" in sys.argv)
+    lib = build(force="--force" in sys.argv, verbose="-v" in sys.argv,
+                debug_bounds="--debug-bounds" in sys.argv)
     print(lib)

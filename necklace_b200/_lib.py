@@ -14,7 +14,9 @@ import os
 import threading
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "_nkb200.so")
+# NKB_DEBUG_BOUNDS=1 selects the bounds-checked debug build (see ``debug_bounds``)
+DEBUG_BOUNDS = os.environ.get("NKB_DEBUG_BOUNDS", "0") not in ("", "0")
+LIB_PATH = os.path.join(_HERE, "_nkb200_dbg.so" if DEBUG_BOUNDS else "_nkb200.so")
 
 _lock = threading.Lock()
 _lib = None
@@ -87,7 +89,29 @@ class NativeLibraryError(RuntimeError):
 
 def _try_build() -> None:
     from . import _build
-    _build.build()
+    _build.build(debug_bounds=DEBUG_BOUNDS)
+
+
+def debug_bounds(raise_on_error: bool = True) -> dict:
+    """Debug build only: read and clear the index-check records of every translation unit.
+    Returns ``{tu: (count, source line, first bad index)}`` for units with failures and raises
+    ``NativeLibraryError`` (device-side error 6, "index check failed") when there are any."""
+    lib = load()
+    import torch
+    torch.cuda.synchronize()
+    bad = {}
+    for tu in ("conv", "loss", "optim", "comm"):
+        fn = getattr(lib, f"nkb_debug_bounds_{tu}", None)
+        if fn is None:
+            continue
+        rec = (C.c_int * 4)()
+        fn.argtypes, fn.restype = [C.c_void_p], i32
+        check(fn(C.cast(rec, C.c_void_p)), f"nkb_debug_bounds_{tu}")
+        if rec[0]:
+            bad[tu] = (rec[0], rec[1], (rec[3] << 32) | (rec[2] & 0xffffffff))
+    if bad and raise_on_error:
+        raise NativeLibraryError(f"device-side error 6 (index check failed): {bad}")
+    return bad
 
 
 def load(build_if_missing: bool = True):

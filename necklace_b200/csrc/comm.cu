@@ -49,6 +49,7 @@ allreduce_kernel(CommCtx c, long long data_off, long long n, float scale, void* 
   if (ok) {
     for (long long i = lo + (long long)threadIdx.x * VEC; i < hi; i += COMM_THREADS * VEC) {
       if (i + VEC <= hi) {
+        if (!NKB_IN_BOUNDS(i + VEC - 1, n)) continue;
         float acc[VEC];
 #pragma unroll
         for (int k = 0; k < VEC; ++k) acc[k] = 0.f;
@@ -332,6 +333,7 @@ rs_opt_ag_kernel(CommCtx c, OptArgs o) {
     const long long i_first = lo + (long long)threadIdx.x * 8;
     if (i_first < hi) load_all(i_first, nxt);
     for (long long i = i_first; i < hi; i += COMM_THREADS * 8) {
+      if (!NKB_IN_BOUNDS(s_lo + i + 7, o.n_total)) break;
       uint4 cur[COMM_MAX_PEER_UNROLL];
 #pragma unroll
       for (int p = 0; p < COMM_MAX_PEER_UNROLL; ++p) cur[p] = nxt[p];
@@ -529,3 +531,4 @@ extern "C" int nkb_comm_rs_opt_ag(void** heap, long long flag_off, long long gra
 }
 
 NKB_DEFINE_WAIT_SETTER(comm)
+NKB_DEFINE_BOUNDS_GETTER(comm)

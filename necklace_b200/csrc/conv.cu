@@ -54,6 +54,9 @@ im2col_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ c
       ok = h >= 0 && h < g.H && w >= 0 && w < g.W;
       src = (((long long)n * g.H + h) * g.W + w) * g.C + c;
     }
+    const long long x_elems = (long long)g.N * g.H * g.W * g.C;
+    if (ok && !NKB_IN_BOUNDS(src + VEC - 1, x_elems)) ok = false;
+    if (!NKB_IN_BOUNDS(m * g.Kpad + k + VEC - 1, M * g.Kpad)) continue;
     if (VEC == 8) {
       uint4 v = make_uint4(0, 0, 0, 0);
       if (ok) v = *reinterpret_cast<const uint4*>(x + src);
@@ -95,6 +98,7 @@ col2im_kernel(const __nv_bfloat16* __restrict__ dcol, __nv_bfloat16* __restrict_
         if (wo >= g.Wo) continue;
         const long long src = (((long long)n * g.Ho + ho) * g.Wo + wo) * g.Kpad +
                               (long long)(kh * g.KW + kw) * g.C + c;
+        if (!NKB_IN_BOUNDS(src + VEC - 1, (long long)g.N * g.Ho * g.Wo * g.Kpad)) continue;
         if (VEC == 8) {
           uint4 v = *reinterpret_cast<const uint4*>(dcol + src);
           uint32_t u[4] = {v.x, v.y, v.z, v.w};
@@ -354,7 +358,9 @@ maxpool_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restric
       for (int kw = 0; kw < 3; ++kw) {
         const int w = wo * 2 - 1 + kw;
         if (w < 0 || w >= W) continue;
-        uint4 v = *reinterpret_cast<const uint4*>(x + (((long long)n * H + h) * W + w) * C + c);
+        const long long src = (((long long)n * H + h) * W + w) * C + c;
+        if (!NKB_IN_BOUNDS(src + 7, (long long)N * H * W * C)) continue;
+        uint4 v = *reinterpret_cast<const uint4*>(x + src);
         uint32_t u[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -401,6 +407,7 @@ maxpool_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const uint8_t* __restri
         const int wo = wn >> 1;
         if (wo >= Wo) continue;
         const long long src = (((long long)n * Ho + ho) * Wo + wo) * C + c;
+        if (!NKB_IN_BOUNDS(src + 7, (long long)N * Ho * Wo * C)) continue;
         uint2 iv = *reinterpret_cast<const uint2*>(idx + src);
         uint4 v = *reinterpret_cast<const uint4*>(dy + src);
         uint32_t u[4] = {v.x, v.y, v.z, v.w};
@@ -637,3 +644,19 @@ extern "C" int nkb_avgpool_bwd(const void* dy, void* dx, int N, int HW, int C, v
       static_cast<const __nv_bfloat16*>(dy), static_cast<__nv_bfloat16*>(dx), N, HW, C);
   return (int)cudaGetLastError();
 }
+
+NKB_DEFINE_BOUNDS_GETTER(conv)
+
+#ifdef NKB_DEBUG_BOUNDS
+// Exercises the reporting path of the debug build without touching memory: one failing
+// check (index 5 of an extent of 4) is evaluated and nothing is accessed.
+namespace nkb {
+__global__ void bounds_selftest_kernel(int* sink) {
+  if (NKB_IN_BOUNDS(5, 4)) *sink = 1;
+}
+}  // namespace nkb
+extern "C" int nkb_debug_bounds_selftest(int* sink, void* stream) {
+  nkb::bounds_selftest_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(sink);
+  return (int)cudaGetLastError();
+}
+#endif

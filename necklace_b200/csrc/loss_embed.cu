@@ -171,6 +171,7 @@ __global__ void embed_fwd_kernel(const long long* __restrict__ idx,
                                  __nv_bfloat16* __restrict__ out, int T, int S, int C,
                                  int vocab_start, int vocab_rows) {
   const int t = blockIdx.x;
+  if (!NKB_IN_BOUNDS(t, T)) return;
   const long long id = idx[t] - vocab_start;
   const bool owned = id >= 0 && id < vocab_rows;
   const uint4* tp = reinterpret_cast<const uint4*>(wte + (owned ? id : 0) * C);
@@ -282,3 +283,5 @@ extern "C" int nkb_embed_bwd(const long long* idx, const void* dout, void* dwte,
                                            static_cast<__nv_bfloat16*>(dwpe), T, S, C);
   return (int)cudaGetLastError();
 }
+
+NKB_DEFINE_BOUNDS_GETTER(loss)

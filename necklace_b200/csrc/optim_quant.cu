@@ -28,6 +28,7 @@ adam_flat_kernel(float* __restrict__ master, float* __restrict__ m, float* __res
   const long long n4 = n >> 2;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+    if (!NKB_IN_BOUNDS(4 * i + 3, n)) continue;
     float4 p = reinterpret_cast<float4*>(master)[i];
     float4 mm = reinterpret_cast<float4*>(m)[i];
     float4 vv = reinterpret_cast<float4*>(v)[i];
@@ -379,3 +380,5 @@ extern "C" int nkb_num_sms(void) {
 extern "C" const char* nkb_build_info(void) {
   return "necklace_b200 native library, sm_100a, built " __DATE__ " " __TIME__;
 }
+
+NKB_DEFINE_BOUNDS_GETTER(optim)

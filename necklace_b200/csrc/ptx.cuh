@@ -37,6 +37,39 @@ enum : int {
   NKB_ERR_BOUNDS = 6,      // an index check failed (debug builds)
 };
 
+// ---------------------------------------------------------------- debug bounds checks
+// With -DNKB_DEBUG_BOUNDS every kernel that computes global-memory indices by hand checks
+// them against the extents it was told (NKB_IN_BOUNDS).  A failing check records how many
+// failed, the source line and the index of the first one in a per-translation-unit device
+// record and makes the kernel SKIP that access (nothing traps, nothing is read or written
+// out of range); the host reads and clears the records through nkb_debug_bounds_<tu>() and
+// reports NKB_ERR_BOUNDS.  Kernels whose global accesses go through TMA tensor maps (GEMM,
+// attention) are bounded by the maps themselves.  In normal builds the macro is `true` and
+// compiles away.
+#ifdef NKB_DEBUG_BOUNDS
+static __device__ int g_nkb_bounds_rec[4];  // count, line, index low word, index high word
+__device__ __forceinline__ bool nkb_in_bounds(long long i, long long n, int line) {
+  if (i >= 0 && i < n) return true;
+  if (atomicAdd(&g_nkb_bounds_rec[0], 1) == 0) {
+    g_nkb_bounds_rec[1] = line;
+    g_nkb_bounds_rec[2] = (int)(i & 0xffffffffll);
+    g_nkb_bounds_rec[3] = (int)(i >> 32);
+  }
+  return false;
+}
+#define NKB_IN_BOUNDS(i, n) nkb::nkb_in_bounds((long long)(i), (long long)(n), __LINE__)
+#define NKB_DEFINE_BOUNDS_GETTER(tu)                                                       \
+  extern "C" int nkb_debug_bounds_##tu(int* out4) {                                        \
+    int z[4] = {0, 0, 0, 0};                                                               \
+    cudaError_t e = cudaMemcpyFromSymbol(out4, nkb::g_nkb_bounds_rec, sizeof(z));          \
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(nkb::g_nkb_bounds_rec, z, sizeof(z));     \
+    return (int)e;                                                                         \
+  }
+#else
+#define NKB_IN_BOUNDS(i, n) true
+#define NKB_DEFINE_BOUNDS_GETTER(tu)
+#endif
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

@@ -113,3 +113,109 @@ class FlatParams:
 
     def state_dict_flat(self) -> dict:
         return {"names": self.names, "offsets": self.offsets, "numel": self.numel}
+
+
+class HeapGradReducer:
+    """Data-parallel gradient reduction for an ordinary ``nn.Module`` + ``torch.optim``
+    optimizer (the trainer API of the reference) on the fused peer-memory kernels.
+
+    The module's parameters and ``.grad`` tensors are re-pointed at two flat buffers in the
+    symmetric heap.  The gradient buffer is cut into buckets from its end; a
+    post-accumulate-grad hook per parameter counts a bucket down and, when its last gradient
+    has been written, launches the bucket's collective on a side stream (capped CTA count),
+    so it runs under the rest of backward.  The collective is the fused 2-bit kernel
+    (quantise + error feedback + exchange + decode, ``grad_comp_cfg`` as in the reference's
+    ``grad_comp_threshold`` / ``grad_size_threshold`` keys) or the plain peer all-reduce, both
+    with the 1/world scale folded in.  ``finish()`` launches what is left and joins the stream;
+    the optimizer then steps on the reduced ``.grad`` views.
+
+    Replaces flatten -> NCCL all-reduce -> divide -> unflatten -> copy after the whole backward
+    (necklace/frmwrk/pytorch/ptprms.py:256-299)."""
+
+    def __init__(self, module: nn.Module, peer, heap, grad_comp_cfg: dict | None = None,
+                 bucket_mb: float = 25.0, overlap: bool = True, average: bool = True,
+                 comm_ctas: int = 32):
+        self.peer, self.world = peer, peer.world
+        q = 8 * self.world * 64
+        self.flat = FlatParams(module, alloc=lambda n, dt: heap.alloc(n, dt), pad_multiple=q,
+                               direct_grads=False)
+        f = self.flat
+        self.scale = (1.0 / self.world) if average else 1.0
+        self.cfg = grad_comp_cfg
+        n = f.numel
+        esz = f.grad.element_size()
+        per = max(q, int(bucket_mb * (1 << 20) / esz) // q * q)
+        self.buckets, hi = [], n
+        while hi > 0:
+            lo = max(0, hi - per)
+            if lo < per // 2:
+                lo = 0
+            self.buckets.append((lo, hi))
+            hi = lo
+        self.compress = bool(grad_comp_cfg) and n >= int(grad_comp_cfg.get("grad_size_threshold", 0))
+        if self.compress:
+            self.thr = float(grad_comp_cfg.get("grad_comp_threshold", 0.5))
+            self.residual = torch.zeros(n, dtype=torch.float32, device=f.device)
+            self.codes = heap.alloc((n + 15) // 16, torch.int32)
+            self.counts = heap.alloc((n + 15) // 16 * 16, torch.int8)
+        # parameters per bucket (a parameter that straddles a boundary belongs to both)
+        self._members = [[i for i, (p, o) in enumerate(zip(f.params, f.offsets))
+                          if o < hi and o + p.numel() > lo] for lo, hi in self.buckets]
+        self._of_param = {}
+        for b, mem in enumerate(self._members):
+            for i in mem:
+                self._of_param.setdefault(i, []).append(b)
+        self.overlap = overlap and len(self.buckets) > 1 and f.device.type == "cuda"
+        self.comm_ctas = comm_ctas
+        self._stream = torch.cuda.Stream(device=f.device, priority=-1) if self.overlap else None
+        self._left, self._fired = [], set()
+        if self.overlap:
+            for i, p in enumerate(f.params):
+                p.register_post_accumulate_grad_hook(self._make_hook(i))
+        self.begin_backward()
+
+    def _make_hook(self, i):
+        def hook(_p):
+            for b in self._of_param.get(i, ()):
+                self._left[b] -= 1      # (a second backward of the same step goes negative)
+                if self._left[b] == 0:
+                    self._launch(b, side=True)
+        return hook
+
+    def begin_backward(self):
+        self._left = [len(m) for m in self._members]
+        self._fired = set()
+
+    def _work(self, b, ctas):
+        lo, hi = self.buckets[b]
+        g = self.flat.grad[lo:hi]
+        if self.compress:
+            self.peer.dp_quant_allreduce(g, self.residual[lo:hi], self.codes[lo // 16:hi // 16],
+                                         self.counts[lo:hi], g, self.thr, self.scale,
+                                         max_ctas=ctas)
+        else:
+            self.peer.all_reduce(g, scale=self.scale, max_ctas=ctas)
+
+    def _launch(self, b, side):
+        if b in self._fired:
+            return
+        self._fired.add(b)
+        if side and self._stream is not None:
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream())
+            self._stream.wait_event(ev)
+            with torch.cuda.stream(self._stream):
+                self._work(b, self.comm_ctas)
+        else:
+            self._work(b, None)
+
+    def finish(self):
+        """Reduce every bucket that has not been launched yet and wait for the side stream
+        (stream-ordered: the caller's stream continues after all buckets are done)."""
+        for b in range(len(self.buckets)):
+            self._launch(b, side=self._stream is not None)
+        if self._stream is not None:
+            ev = torch.cuda.Event()
+            ev.record(self._stream)
+            torch.cuda.current_stream().wait_event(ev)
+        self.begin_backward()

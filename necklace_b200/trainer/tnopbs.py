@@ -180,9 +180,28 @@ class TrainerOPBase(ModelWrapperHooks):
             tmode, pg_cfg, comm_type=self.cfg.get("comm_type", "nccl"), device=dev,
             master_addr=nuid.get("master_addr", "127.0.0.1"),
             master_port=int(nuid.get("master_port", 29400)),
-            heap_bytes=int(self.cfg.get("heap_bytes", 0)),
+            heap_bytes=int(self.cfg.get("heap_bytes") or self._default_heap_bytes()),
             timeout_s=float(self.cfg.get("comm_timeout_s", 120)))
         return "ok"
+
+    def _default_heap_bytes(self) -> int:
+        """Symmetric-heap size when the user gives none: room for the parameters and gradients
+        of this worker's module(s) (the data-parallel / ZeRO buffers live there), the 2-bit
+        code and count buffers, plus 256 MiB for the fused kernels' staging buffers."""
+        if self.cfg.get("comm_type", "nccl") != "peer":
+            return 0
+        n = 0
+        mods = []
+        if getattr(self, "net", None) is not None:
+            mods.append(self.net)
+        for v in (self.cfg.get("net_map") or {}).values():
+            if v.get("net") is not None:
+                mods.append(v["net"])
+        for m in mods:
+            for mod in (m if isinstance(m, (list, tuple)) else [m]):
+                if hasattr(mod, "parameters"):
+                    n += sum(p.numel() * p.element_size() for p in mod.parameters())
+        return int(n * 2.6) + (256 << 20)
 
     def del_nccl_comm(self, msg=None, *args, **kwargs):
         comm_backend.shutdown_backend()

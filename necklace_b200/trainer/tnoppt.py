@@ -191,9 +191,38 @@ class TrainerOPPytorch(TrainerOPBase):
         if grp is not None and grp.world_size > 1 and self._dp_applies():
             ptprms.params_do_nccl_allreduce(grp, grp.world_size, self.net)
 
+    def init_nccl_comm(self, msg=None, *args, **kwargs):
+        r = super().init_nccl_comm(msg, *args, **kwargs)
+        self._setup_heap_grads()
+        return r
+
+    def _setup_heap_grads(self):
+        """With the peer-memory communicator the data-parallel gradients live in the
+        symmetric heap and are reduced by the fused kernels, bucket by bucket under backward
+        (``parallel.flat.HeapGradReducer``); ``grad_comp_cfg`` then means the fused 2-bit
+        kernel.  Without it (NCCL / gloo communicator, CPU) the bucketed collective path of
+        ``ptprms`` is used."""
+        self.heap_grads = None
+        grp = G.get_nccl_group_dp_or_main()
+        peer = getattr(getattr(grp, "comm", None), "peer", None) if grp is not None else None
+        if peer is None or peer.world == 1 or self.net is None or not self._dp_applies():
+            return
+        params = [p for p in self.net.parameters() if p.requires_grad]
+        if not params or not params[0].is_cuda or len({p.dtype for p in params}) != 1 or \
+                params[0].dtype not in (torch.float32, torch.bfloat16):
+            return
+        from ..parallel.flat import HeapGradReducer
+        self.heap_grads = HeapGradReducer(
+            self.net, peer, self.heap, self.grad_comp_cfg,
+            bucket_mb=float(self.cfg.get("grad_bucket_mb", 25.0)),
+            overlap=bool(self.cfg.get("grad_overlap", True)))
+
     def do_grads_nccl_all_reduce(self, *args, **kwargs):
         grp = G.get_nccl_group_dp_or_main()
         if grp is not None and grp.world_size > 1 and self._dp_applies():
+            if getattr(self, "heap_grads", None) is not None:
+                self.heap_grads.finish()
+                return
             ptprms.opt_grads_do_nccl_allreduce(grp, grp.world_size, self.opt,
                                                grad_comp_cfg=self.grad_comp_cfg)
 

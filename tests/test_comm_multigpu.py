@@ -329,6 +329,62 @@ def case_llama_tp_fused(rank, world, heap, grp, chk):
             grp.barrier()
 
 
+def case_heap_grad_reducer(rank, world, heap, grp, chk):
+    """Trainer-API data parallelism on the fused kernels: gradients of an ordinary module in
+    the heap, reduced bucket by bucket under backward, plain and 2-bit compressed, against
+    the unfused codec + NCCL path (bit-equal residuals) and an NCCL all-reduce."""
+    import torch.distributed as dist
+    import torch.nn as nn
+    from necklace_b200.frmwrk.pytorch import ptprms
+    from necklace_b200.ops.quant import dequantize_flat, quantize_flat
+    from necklace_b200.parallel.flat import HeapGradReducer
+
+    def make():
+        torch.manual_seed(0)
+        return nn.Sequential(nn.Linear(300, 700), nn.ReLU(), nn.Linear(700, 700), nn.ReLU(),
+                             nn.Linear(700, 10)).cuda()
+
+    for comp in (None, {"grad_comp_threshold": 0.002, "grad_size_threshold": 0}):
+        net, ref = make(), make()
+        red = HeapGradReducer(net, grp, heap, comp, bucket_mb=0.5, overlap=True)
+        chk(len(red.buckets) > 1, "want several buckets")
+        ref_res = torch.zeros(red.flat.numel, device="cuda")
+        for step in range(3):
+            torch.manual_seed(100 * step + rank)
+            x = torch.randn(64, 300, device="cuda")
+            for m in (net, ref):
+                for p in m.parameters():
+                    if p.grad is not None:
+                        p.grad.zero_()
+            net(x).square().mean().backward()
+            red.finish()
+            ref(x).square().mean().backward()
+            flat_ref = torch.zeros(red.flat.numel, device="cuda")
+            for p, o in zip(ref.parameters(), red.flat.offsets):
+                flat_ref[o:o + p.numel()] = p.grad.reshape(-1)
+            if comp is None:
+                dist.all_reduce(flat_ref)
+                flat_ref /= world
+                chk(_rel(red.flat.grad, flat_ref) < 1e-5, ("plain", step))
+            else:
+                thr = comp["grad_comp_threshold"]
+                codes = quantize_flat(flat_ref, ref_res, thr)
+                allc = torch.empty(world, codes.numel(), dtype=codes.dtype, device="cuda")
+                dist.all_gather_into_tensor(allc, codes)
+                out = torch.zeros_like(flat_ref)
+                for r in range(world):
+                    dequantize_flat(allc[r].contiguous(), out, thr, accumulate=True)
+                out /= world
+                chk(torch.equal(red.residual, ref_res), ("residual", step))
+                chk(_rel(red.flat.grad, out) < 1e-6, ("quant", step, _rel(red.flat.grad, out)))
+            torch.cuda.synchronize()
+            grp.barrier()
+
+
+def test_heap_grad_reducer():
+    _run("case_heap_grad_reducer")
+
+
 def test_llama_tp_fused():
     _run("case_llama_tp_fused")
 
