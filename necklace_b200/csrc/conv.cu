@@ -67,6 +67,50 @@ im2col_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ c
   }
 }
 
+// Channel counts that are not a multiple of 8 (the 3-channel stem): one thread builds 8
+// consecutive K entries (each with its own tap / channel, scalar 2-byte loads that hit the
+// small, heavily reused input in cache) and writes them with one 16-byte store.
+__global__ void __launch_bounds__(256)
+im2col_gather8_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ col,
+                      ConvGeom g) {
+  const long long M = (long long)g.N * g.Ho * g.Wo;
+  const int kchunks = g.Kpad / 8;
+  const int Kreal = g.KH * g.KW * g.C;
+  const long long total = M * kchunks;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += stride) {
+    const long long m = idx / kchunks;
+    const int k0 = (int)(idx % kchunks) * 8;
+    const int wo = (int)(m % g.Wo);
+    const long long t = m / g.Wo;
+    const int ho = (int)(t % g.Ho);
+    const int n = (int)(t / g.Ho);
+    const int h0 = ho * g.stride - g.pad, w0 = wo * g.stride - g.pad;
+    unsigned short v[8];
+    int tap = k0 / g.C, c = k0 % g.C;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      unsigned short e = 0;
+      if (k0 + j < Kreal) {
+        const int kh = tap / g.KW, kw = tap % g.KW;
+        const int h = h0 + kh, w = w0 + kw;
+        if (h >= 0 && h < g.H && w >= 0 && w < g.W) {
+          const long long src = (((long long)n * g.H + h) * g.W + w) * g.C + c;
+          if (NKB_IN_BOUNDS(src, (long long)g.N * g.H * g.W * g.C))
+            e = reinterpret_cast<const unsigned short*>(x)[src];
+        }
+      }
+      v[j] = e;
+      if (++c == g.C) { c = 0; ++tap; }
+    }
+    if (!NKB_IN_BOUNDS(m * g.Kpad + k0 + 7, M * g.Kpad)) continue;
+    *reinterpret_cast<uint4*>(col + m * g.Kpad + k0) =
+        make_uint4(v[0] | ((uint32_t)v[1] << 16), v[2] | ((uint32_t)v[3] << 16),
+                   v[4] | ((uint32_t)v[5] << 16), v[6] | ((uint32_t)v[7] << 16));
+  }
+}
+
 // dx[n,h,w,c] = sum over taps (kh,kw) with (h + pad - kh) % stride == 0 (same for w) of
 // dcol[(n, (h+pad-kh)/stride, (w+pad-kw)/stride), (kh*KW+kw)*C + c]
 template <int VEC>
@@ -228,24 +272,35 @@ __global__ void bn_finalize_kernel(float* __restrict__ acc, float* __restrict__ 
   acc[C + c] = 0.f;
 }
 
-// y = act((x - mean) * rstd * gamma + beta (+ res))
+// y = act((x - mean) * rstd * gamma + beta (+ res)).  Thread layout as in bn_sums_kernel: a
+// thread owns 8 fixed channels (its per-channel constants stay in registers) and walks rows.
 __global__ void __launch_bounds__(256)
 bn_apply_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ stats,
                 const __nv_bfloat16* __restrict__ gamma, const __nv_bfloat16* __restrict__ beta,
                 const __nv_bfloat16* __restrict__ res, __nv_bfloat16* __restrict__ y, long long M,
-                int C, int relu) {
-  const int cch = C / 8;
-  const long long total = M * cch;
-  const long long stride = (long long)gridDim.x * blockDim.x;
-  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
-       idx += stride) {
-    const int c = (int)(idx % cch) * 8;
-    const long long off = (idx / cch) * C + c;
-    uint4 vx = *reinterpret_cast<const uint4*>(x + off);
-    uint32_t ux[4] = {vx.x, vx.y, vx.z, vx.w};
+                int C, int cx, int relu) {
+  const int ry = 256 / cx;
+  const int tx = threadIdx.x % cx, ty = threadIdx.x / cx;
+  const int c = (blockIdx.x * cx + tx) * 8;
+  if (c >= C) return;
+  float sc[8], sh[8];
+  {
     uint4 vg = *reinterpret_cast<const uint4*>(gamma + c);
     uint4 vb = *reinterpret_cast<const uint4*>(beta + c);
     uint32_t ug[4] = {vg.x, vg.y, vg.z, vg.w}, ub[4] = {vb.x, vb.y, vb.z, vb.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 fg = unpack_bf16x2(ug[j]), fb = unpack_bf16x2(ub[j]);
+      sc[2 * j] = stats[C + c + 2 * j] * fg.x;
+      sc[2 * j + 1] = stats[C + c + 2 * j + 1] * fg.y;
+      sh[2 * j] = fb.x - stats[c + 2 * j] * sc[2 * j];
+      sh[2 * j + 1] = fb.y - stats[c + 2 * j + 1] * sc[2 * j + 1];
+    }
+  }
+  for (long long r = (long long)blockIdx.y * ry + ty; r < M; r += (long long)gridDim.y * ry) {
+    const long long off = r * C + c;
+    uint4 vx = *reinterpret_cast<const uint4*>(x + off);
+    uint32_t ux[4] = {vx.x, vx.y, vx.z, vx.w};
     uint32_t ur[4] = {0, 0, 0, 0};
     if (res) {
       uint4 vr = *reinterpret_cast<const uint4*>(res + off);
@@ -254,10 +309,9 @@ bn_apply_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ s
     uint32_t o[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      float2 fx = unpack_bf16x2(ux[j]), fg = unpack_bf16x2(ug[j]), fb = unpack_bf16x2(ub[j]);
-      float2 fr = unpack_bf16x2(ur[j]);
-      float a = (fx.x - stats[c + 2 * j]) * stats[C + c + 2 * j] * fg.x + fb.x + fr.x;
-      float b = (fx.y - stats[c + 2 * j + 1]) * stats[C + c + 2 * j + 1] * fg.y + fb.y + fr.y;
+      float2 fx = unpack_bf16x2(ux[j]), fr = unpack_bf16x2(ur[j]);
+      float a = fx.x * sc[2 * j] + sh[2 * j] + fr.x;
+      float b = fx.y * sc[2 * j + 1] + sh[2 * j + 1] + fr.y;
       if (relu) { a = fmaxf(a, 0.f); b = fmaxf(b, 0.f); }
       o[j] = pack_bf16x2(a, b);
     }
@@ -266,51 +320,60 @@ bn_apply_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ s
 }
 
 // dx = gamma * rstd * (dy' - s0/M - xhat * s1/M);  dres = dy' (optional);
-// sums = [2][C] from bn_sums_kernel<1>.
+// sums = [2][C] from bn_sums_kernel<1>.  Same thread layout.
 __global__ void __launch_bounds__(256)
 bn_bwd_apply_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                     const __nv_bfloat16* __restrict__ y, const float* __restrict__ stats,
                     const float* __restrict__ sums, const __nv_bfloat16* __restrict__ gamma,
                     __nv_bfloat16* __restrict__ dx, __nv_bfloat16* __restrict__ dres, long long M,
-                    int C, int relu) {
-  const int cch = C / 8;
-  const long long total = M * cch;
-  const long long stride = (long long)gridDim.x * blockDim.x;
+                    int C, int cx, int relu) {
+  const int ry = 256 / cx;
+  const int tx = threadIdx.x % cx, ty = threadIdx.x / cx;
+  const int c = (blockIdx.x * cx + tx) * 8;
+  if (c >= C) return;
   const float invM = 1.f / (float)M;
-  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
-       idx += stride) {
-    const int c = (int)(idx % cch) * 8;
-    const long long off = (idx / cch) * C + c;
+  // dx = k1 * dy' + k2 * x + k3 with k1 = gamma rstd, k2 = -k1 rstd s1/M,
+  // k3 = -k1 (s0/M - mean rstd s1/M)
+  float k1[8], k2[8], k3[8];
+  {
+    uint4 vg = *reinterpret_cast<const uint4*>(gamma + c);
+    uint32_t ug[4] = {vg.x, vg.y, vg.z, vg.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float2 fg = unpack_bf16x2(ug[j >> 1]);
+      const float g = (j & 1) ? fg.y : fg.x;
+      const float mean = stats[c + j], rstd = stats[C + c + j];
+      const float a0 = sums[c + j] * invM, a1 = sums[C + c + j] * invM;
+      k1[j] = g * rstd;
+      k2[j] = -k1[j] * rstd * a1;
+      k3[j] = -k1[j] * (a0 - mean * rstd * a1);
+    }
+  }
+  for (long long r = (long long)blockIdx.y * ry + ty; r < M; r += (long long)gridDim.y * ry) {
+    const long long off = r * C + c;
     uint4 vd = *reinterpret_cast<const uint4*>(dy + off);
     uint4 vx = *reinterpret_cast<const uint4*>(x + off);
-    uint4 vg = *reinterpret_cast<const uint4*>(gamma + c);
     uint32_t ud[4] = {vd.x, vd.y, vd.z, vd.w}, ux[4] = {vx.x, vx.y, vx.z, vx.w};
-    uint32_t ug[4] = {vg.x, vg.y, vg.z, vg.w};
     uint32_t uy[4] = {0, 0, 0, 0};
     if (relu) {
       uint4 vy = *reinterpret_cast<const uint4*>(y + off);
-      uint4 t = vy;
-      uy[0] = t.x; uy[1] = t.y; uy[2] = t.z; uy[3] = t.w;
+      uy[0] = vy.x; uy[1] = vy.y; uy[2] = vy.z; uy[3] = vy.w;
     }
-    uint32_t o[4], r[4];
+    uint32_t o[4], rr[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      float2 fd = unpack_bf16x2(ud[j]), fx = unpack_bf16x2(ux[j]), fg = unpack_bf16x2(ug[j]);
+      float2 fd = unpack_bf16x2(ud[j]), fx = unpack_bf16x2(ux[j]);
       if (relu) {
         float2 fy = unpack_bf16x2(uy[j]);
         if (!(fy.x > 0.f)) fd.x = 0.f;
         if (!(fy.y > 0.f)) fd.y = 0.f;
       }
-      const int c0 = c + 2 * j, c1 = c0 + 1;
-      const float xh0 = (fx.x - stats[c0]) * stats[C + c0];
-      const float xh1 = (fx.y - stats[c1]) * stats[C + c1];
-      const float a = fg.x * stats[C + c0] * (fd.x - sums[c0] * invM - xh0 * sums[C + c0] * invM);
-      const float b = fg.y * stats[C + c1] * (fd.y - sums[c1] * invM - xh1 * sums[C + c1] * invM);
-      o[j] = pack_bf16x2(a, b);
-      r[j] = pack_bf16x2(fd.x, fd.y);
+      o[j] = pack_bf16x2(k1[2 * j] * fd.x + k2[2 * j] * fx.x + k3[2 * j],
+                         k1[2 * j + 1] * fd.y + k2[2 * j + 1] * fx.y + k3[2 * j + 1]);
+      rr[j] = pack_bf16x2(fd.x, fd.y);
     }
     *reinterpret_cast<uint4*>(dx + off) = make_uint4(o[0], o[1], o[2], o[3]);
-    if (dres) *reinterpret_cast<uint4*>(dres + off) = make_uint4(r[0], r[1], r[2], r[3]);
+    if (dres) *reinterpret_cast<uint4*>(dres + off) = make_uint4(rr[0], rr[1], rr[2], rr[3]);
   }
 }
 
@@ -506,6 +569,9 @@ extern "C" int nkb_im2col_nhwc(const void* x, void* col, int N, int H, int W, in
   if (vec)
     im2col_kernel<8><<<conv_grid(M * (Kpad / 8), 256), 256, 0, s>>>(
         static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(col), g);
+  else if (!(reinterpret_cast<uintptr_t>(col) & 15))
+    im2col_gather8_kernel<<<conv_grid(M * (Kpad / 8), 256), 256, 0, s>>>(
+        static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(col), g);
   else
     im2col_kernel<1><<<conv_grid(M * Kpad, 256), 256, 0, s>>>(
         static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(col), g);
@@ -561,10 +627,10 @@ extern "C" int nkb_bn_fwd(const void* x, const void* gamma, const void* beta, co
                                          nullptr, acc, M, C, cx, 0);
   bn_finalize_kernel<<<(C + 127) / 128, 128, 0, s>>>(acc, stats, run_mean, run_var, M, C, eps,
                                                      momentum);
-  bn_apply_kernel<<<conv_grid(M * (C / 8), 256), 256, 0, s>>>(
+  bn_apply_kernel<<<grid, 256, 0, s>>>(
       static_cast<const __nv_bfloat16*>(x), stats, static_cast<const __nv_bfloat16*>(gamma),
       static_cast<const __nv_bfloat16*>(beta), static_cast<const __nv_bfloat16*>(res),
-      static_cast<__nv_bfloat16*>(y), M, C, relu);
+      static_cast<__nv_bfloat16*>(y), M, C, cx, relu);
   return (int)cudaGetLastError();
 }
 
@@ -572,10 +638,13 @@ extern "C" int nkb_bn_fwd(const void* x, const void* gamma, const void* beta, co
 extern "C" int nkb_bn_apply(const void* x, const float* stats, const void* gamma, const void* beta,
                             const void* res, void* y, long long M, int C, int relu, void* stream) {
   if (C % 8) return -3;
-  bn_apply_kernel<<<conv_grid(M * (C / 8), 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  int cx;
+  dim3 grid;
+  bn_sums_dims(M, C, cx, grid);
+  bn_apply_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), stats, static_cast<const __nv_bfloat16*>(gamma),
       static_cast<const __nv_bfloat16*>(beta), static_cast<const __nv_bfloat16*>(res),
-      static_cast<__nv_bfloat16*>(y), M, C, relu);
+      static_cast<__nv_bfloat16*>(y), M, C, cx, relu);
   return (int)cudaGetLastError();
 }
 
@@ -597,10 +666,10 @@ extern "C" int nkb_bn_bwd(const void* dy, const void* x, const void* y, const fl
                                          static_cast<const __nv_bfloat16*>(x),
                                          static_cast<const __nv_bfloat16*>(y), stats, acc, M, C,
                                          cx, relu);
-  bn_bwd_apply_kernel<<<conv_grid(M * (C / 8), 256), 256, 0, s>>>(
+  bn_bwd_apply_kernel<<<grid, 256, 0, s>>>(
       static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
       static_cast<const __nv_bfloat16*>(y), stats, acc, static_cast<const __nv_bfloat16*>(gamma),
-      static_cast<__nv_bfloat16*>(dx), static_cast<__nv_bfloat16*>(dres), M, C, relu);
+      static_cast<__nv_bfloat16*>(dx), static_cast<__nv_bfloat16*>(dres), M, C, cx, relu);
   bn_param_grad_kernel<<<(C + 127) / 128, 128, 0, s>>>(acc, static_cast<__nv_bfloat16*>(dgamma),
                                                        static_cast<__nv_bfloat16*>(dbeta), C,
                                                        acc_g, acc_b);

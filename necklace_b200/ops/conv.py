@@ -82,12 +82,24 @@ class Conv2dFn(torch.autograd.Function):
         ctx.direct = direct
         a = x.reshape(-1, C) if direct else im2col(x, KH, KW, stride, pad)
         y = gemm(a, w)
-        ctx.save_for_backward(x, w)     # col is rebuilt in backward (it is KH*KW times x)
+        # the gathered matrix is kept for the weight gradient unless it would be very large
+        # (then it is rebuilt in backward): KH*KW times the input, which 180 GB of HBM affords
+        keep = (not direct) and a.numel() * a.element_size() <= Conv2dFn.KEEP_COL_BYTES
+        ctx.keep_col = keep
+        if keep:
+            ctx.save_for_backward(x, w, a)
+        else:
+            ctx.save_for_backward(x, w)
         return y.view(N, Ho, Wo, w.shape[0])
+
+    KEEP_COL_BYTES = 2 << 30
 
     @staticmethod
     def backward(ctx, dy):
-        x, w = ctx.saved_tensors
+        if ctx.keep_col:
+            x, w, col = ctx.saved_tensors
+        else:
+            (x, w), col = ctx.saved_tensors, None
         KH, KW, stride, pad = ctx.geom
         N, H, W, C = ctx.xshape
         dy2 = dy.reshape(-1, dy.shape[-1])
@@ -97,7 +109,8 @@ class Conv2dFn(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             d = gemm(dy2, w, b_mn=True)                       # [M, Kpad]
             dx = d.view(N, H, W, C) if ctx.direct else col2im(d, ctx.xshape, KH, KW, stride, pad)
-        a = x.reshape(-1, C) if ctx.direct else im2col(x, KH, KW, stride, pad)
+        a = x.reshape(-1, C) if ctx.direct else \
+            (col if col is not None else im2col(x, KH, KW, stride, pad))
         dw = _deliver_grad(w, lambda out, acc: gemm(dy2, a, a_mn=True, b_mn=True, out=out,
                                                     accumulate=acc))
         return dx, dw, None, None, None, None
