@@ -66,7 +66,13 @@ class SymmetricHeap:
         if end > self.nbytes:
             raise MemoryError(f"symmetric heap exhausted: need {end} of {self.nbytes} bytes")
         self._top = end
-        return self.buf[off:end].view(dtype)
+        # Not a view of ``self.buf``: views share one autograd version counter, so an in-place
+        # write to ANY heap tensor would invalidate every heap tensor that some autograd
+        # function saved for backward (token ids, gathered activations).  A fresh tensor over
+        # the same storage has a counter of its own.
+        t = torch.empty(0, dtype=dtype, device=self.device)
+        t.set_(self.buf.untyped_storage(), (self.buf.storage_offset() + off) // esz, (numel,))
+        return t
 
     def offset_of(self, t: torch.Tensor) -> int:
         off = t.data_ptr() - self.buf.data_ptr()

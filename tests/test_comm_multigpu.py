@@ -303,7 +303,9 @@ def case_llama_tp_fused(rank, world, heap, grp, chk):
         kw = dict(n_layer=2, d_model=4 * hd, n_head=4, d_ff=1024, vocab=1000, max_seq=seq)
         tp = Llama(LlamaConfig(tp_group=grp, **kw), device="cuda")
         ref = Llama(LlamaConfig(**kw), device="cuda")
-        tok = torch.randint(0, 1000, (2, seq + 1), generator=torch.Generator().manual_seed(3)).cuda()
+        nb = max(2, world * 128 // seq)      # the fused kernels want 128-row blocks per rank
+        tok = torch.randint(0, 1000, (nb, seq + 1),
+                            generator=torch.Generator().manual_seed(3)).cuda()
         x, y = tok[:, :-1].contiguous(), tok[:, 1:].contiguous()
         for step in range(2):          # twice: buffers and flags are reused
             for m in (tp, ref):
