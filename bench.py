@@ -594,10 +594,12 @@ def timed_regions(wl, args, world, dev, clocks=True):
     sync_all()
     e2e_ms = f0.elapsed_time(f1)
     ck = sampler.stop() if sampler else None
-    t = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device=dev)
+    # pipeline stages other than the last one have no loss (they report 0): the maximum over
+    # ranks is the loss of a rank that computed one
+    t = torch.tensor([dev_ms, e2e_ms, first_loss, last_loss], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return float(t[0]), float(t[1]), ck, first_loss, last_loss
+    return float(t[0]), float(t[1]), ck, float(t[2]), float(t[3])
 
 
 def comm_roofline(wl, world, dev, peaks):

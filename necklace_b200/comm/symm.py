@@ -198,7 +198,7 @@ class PeerGroup:
 
 
     def ag_gemm(self, x_full: torch.Tensor, w: torch.Tensor, *, out=None, bias=None, b_mn=False,
-                ag_ctas: int = 8, bn: int = 0) -> torch.Tensor:
+                ag_ctas: int = 16, bn: int = 0) -> torch.Tensor:
         """``out = all_gather_rows(x) @ w^T`` in one kernel.  ``x_full`` is a heap tensor
         ``[world * R, K]`` whose rows ``[rank*R, (rank+1)*R)`` hold this rank's shard; the
         other rows are filled by the kernel's copy CTAs (peer loads) while its GEMM CTAs
@@ -225,7 +225,7 @@ class PeerGroup:
 
 
     def gemm_rs(self, x: torch.Tensor, w: torch.Tensor, *, out=None, bias=None, res=None,
-                b_mn=False, rs_ctas: int = 16, bn: int = 0) -> torch.Tensor:
+                b_mn=False, rs_ctas: int = 24, bn: int = 0) -> torch.Tensor:
         """``out[R, N]`` = this rank's row block of ``sum_ranks x_r @ w_r^T`` (+ bias + res):
         GEMM and reduce-scatter in one kernel.  ``x``: ``[M, K_local]`` with ``M = world*R``;
         partial tiles are stored directly into the owner's staging slab over NVLink and the

@@ -130,9 +130,16 @@ __device__ __noinline__ static void rs_reduce_role(const GemmArgs& g) {
       float acc[8];
 #pragma unroll
       for (int k = 0; k < 8; ++k) acc[k] = 0.f;
-      for (int src = 0; src < c.world; ++src) {
-        uint4 v = ld_volatile_v4(stage + (((long long)src * R + r) * g.N + col) * 2);
-        uint32_t w[4] = {v.x, v.y, v.z, v.w};
+      // all members' partial vectors are requested before any is added
+      uint4 pv[COMM_MAX_WORLD];
+#pragma unroll
+      for (int src = 0; src < COMM_MAX_WORLD; ++src)
+        if (src < c.world)
+          pv[src] = ld_volatile_v4(stage + (((long long)src * R + r) * g.N + col) * 2);
+#pragma unroll
+      for (int src = 0; src < COMM_MAX_WORLD; ++src) {
+        if (src >= c.world) continue;
+        uint32_t w[4] = {pv[src].x, pv[src].y, pv[src].z, pv[src].w};
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           float2 f = unpack_bf16x2(w[k]);
@@ -193,23 +200,41 @@ __device__ __noinline__ static void ag_copy_role(const GemmArgs& g) {
       st_release_sys(flags + c.rank * blocks_per_rank + b, e);
     char* mine = static_cast<char*>(c.heap[c.rank]) + g.ag_data_off;
     const long long v_per_row = g.ag_row_bytes >> 4;
-    for (int p = 1; p < c.world; ++p) {
-      const int q = (c.rank + p) % c.world;
+    // (peer, 128-row block) units are dealt round-robin to the copy CTAs, nearest peer first.
+    // A peer load takes microseconds over NVLink, so every thread keeps AG_UNROLL 16-byte
+    // loads in flight before it stores any of them (one load at a time ran at ~20 GB/s).
+    constexpr int AG_UNROLL = 8;
+    const int units = (c.world - 1) * blocks_per_rank;
+    for (int u = blockIdx.x; u < units; u += g.ag_ctas) {
+      const int q = (c.rank + 1 + u / blocks_per_rank) % c.world;
+      const int b = u % blocks_per_rank;
       const char* theirs = static_cast<const char*>(c.heap[q]) + g.ag_data_off;
-      for (int b = blockIdx.x; b < blocks_per_rank; b += g.ag_ctas) {
-        const int r0 = q * R + b * 128;
-        const int nrows = min(128, R - b * 128);
-        const long long total = (long long)nrows * v_per_row;
-        for (long long i = threadIdx.x; i < total; i += blockDim.x) {
-          const long long row = r0 + i / v_per_row, col = (i % v_per_row) << 4;
-          uint4 v = ld_volatile_v4(theirs + row * g.ag_pitch + col);
-          *reinterpret_cast<uint4*>(mine + row * g.ag_pitch + col) = v;
+      const int r0 = q * R + b * 128;
+      const int nrows = min(128, R - b * 128);
+      const long long total = (long long)nrows * v_per_row;
+      for (long long i0 = threadIdx.x; i0 < total; i0 += (long long)blockDim.x * AG_UNROLL) {
+        uint4 v[AG_UNROLL];
+#pragma unroll
+        for (int k = 0; k < AG_UNROLL; ++k) {
+          const long long i = i0 + (long long)k * blockDim.x;
+          if (i < total) {
+            const long long row = r0 + i / v_per_row, col = (i % v_per_row) << 4;
+            v[k] = ld_volatile_v4(theirs + row * g.ag_pitch + col);
+          }
         }
-        __syncthreads();
-        if (threadIdx.x == 0) {
-          __threadfence();
-          st_release_sys(flags + q * blocks_per_rank + b, e);
+#pragma unroll
+        for (int k = 0; k < AG_UNROLL; ++k) {
+          const long long i = i0 + (long long)k * blockDim.x;
+          if (i < total) {
+            const long long row = r0 + i / v_per_row, col = (i % v_per_row) << 4;
+            *reinterpret_cast<uint4*>(mine + row * g.ag_pitch + col) = v[k];
+          }
         }
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        __threadfence();
+        st_release_sys(flags + q * blocks_per_rank + b, e);
       }
     }
     cta_barrier(c, 2 * e);  // peers may overwrite their shards only after everyone pulled
