@@ -65,7 +65,7 @@ _SIGS = {
     "nkb_comm_flag_bytes": [],
     "nkb_ag_gemm_bf16": [vp, i64, i64, i32, i32, i32, vp, vp, i32, i64, vp, i64, i32, vp, i64, i32,
                          i32, i32, vp, vp, i64, i32, vp, i64, vp, vp, i32, vp],
-    "nkb_gemm_rs_bf16": [vp, i64, i64, i64, i32, i32, i32, vp, i32, vp, i64, vp, i64, i32, vp, i64,
+    "nkb_gemm_rs_bf16": [vp, i64, i64, i64, i32, i32, i32, vp, vp, i64, vp, i64, i32, vp, i64,
                          i32, i32, vp, vp, i64, vp, i32, vp],
     "nkb_rope": [vp, i32, i32, i32, i32, f32, i32, i32, vp],
     "nkb_swiglu_fwd": [vp, vp, i64, i32, vp],

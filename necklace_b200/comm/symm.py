@@ -97,7 +97,7 @@ class PeerGroup:
         self.rank = ranks.index(heap.rank) if self.member else -1
         dev = heap.device
         self.ptrs_dev = torch.tensor([heap.ptrs[r] for r in ranks], dtype=torch.int64, device=dev)
-        self.epoch = torch.zeros(2, dtype=torch.int32, device=dev)
+        self.epoch = torch.zeros(4, dtype=torch.int32, device=dev)
         self.max_ctas = 148
 
     def _ctx(self):
@@ -197,22 +197,41 @@ class PeerGroup:
         _lib.count_launch()
 
 
+    @staticmethod
+    def _auto_ag_ctas(world: int, M: int, N: int, K: int) -> int:
+        """Copy CTAs for the fused all-gather: the fewest (even, 4..32) whose push of this
+        rank's shard to all peers ends before the GEMM on the remaining SMs does.  Rates: a
+        copy CTA moved ~19 GB/s of posted stores over NVLink, the GEMM ~1.3 PFLOP/s on 148
+        SMs (both measured on B200)."""
+        nbytes = (world - 1) * (M // world) * K * 2
+        flops = 2.0 * M * N * K
+        for c in range(4, 32, 2):
+            t_copy = nbytes / (c * 19e9)
+            t_gemm = flops / (1.3e15 * (148 - c) / 148)
+            if t_copy <= 0.85 * t_gemm:
+                return c
+        return 32
+
     def ag_gemm(self, x_full: torch.Tensor, w: torch.Tensor, *, out=None, bias=None, b_mn=False,
-                ag_ctas: int = 16, bn: int = 0) -> torch.Tensor:
+                ag_ctas: int = 0, bn: int = 0) -> torch.Tensor:
         """``out = all_gather_rows(x) @ w^T`` in one kernel.  ``x_full`` is a heap tensor
         ``[world * R, K]`` whose rows ``[rank*R, (rank+1)*R)`` hold this rank's shard; the
-        other rows are filled by the kernel's copy CTAs (peer loads) while its GEMM CTAs
-        already work on the local rows."""
+        other rows are filled by the peers' copy CTAs (each rank pushes its shard to every
+        peer with posted stores) while the GEMM CTAs already work on the local rows."""
         from ..ops._common import ptr
         M, K = x_full.shape
         R = M // self.world
         N = w.shape[1] if b_mn else w.shape[0]
         if out is None:
             out = torch.empty(M, N, dtype=torch.bfloat16, device=x_full.device)
+        if ag_ctas <= 0:
+            ag_ctas = self._auto_ag_ctas(self.world, M, N, K)
         nblk = self.world * ((R + 127) // 128)
         flags = getattr(self, "_ag_flags", None)
         if flags is None or flags.numel() < nblk:
-            flags = torch.zeros(max(nblk, 256), dtype=torch.int32, device=x_full.device)
+            # in the heap (peers raise the flags), at the same offset on every member: all
+            # members make the same calls in the same order.  Fresh heap memory is zero.
+            flags = self.heap.alloc(max(nblk, 4096), torch.int32)
             self._ag_flags = flags
         _lib.call("nkb_ag_gemm_bf16", self.ptrs_dev.data_ptr(), self.flag_off,
                   self.heap.offset_of(x_full), self.rank, self.world, R, self.epoch.data_ptr(),
@@ -225,11 +244,12 @@ class PeerGroup:
 
 
     def gemm_rs(self, x: torch.Tensor, w: torch.Tensor, *, out=None, bias=None, res=None,
-                b_mn=False, rs_ctas: int = 24, bn: int = 0) -> torch.Tensor:
+                b_mn=False, bn: int = 0) -> torch.Tensor:
         """``out[R, N]`` = this rank's row block of ``sum_ranks x_r @ w_r^T`` (+ bias + res):
         GEMM and reduce-scatter in one kernel.  ``x``: ``[M, K_local]`` with ``M = world*R``;
-        partial tiles are stored directly into the owner's staging slab over NVLink and the
-        owner's reduce CTAs sum them as their flags arrive."""
+        partial tiles of other ranks' rows are stored directly into the owner's staging slab
+        over NVLink (bf16); the epilogue of an own tile adds the peers' partial tiles to its
+        fp32 accumulator as their flags arrive."""
         from ..ops._common import ptr
         M, K = x.shape
         N = w.shape[1] if b_mn else w.shape[0]
@@ -250,7 +270,7 @@ class PeerGroup:
             out = torch.empty(R, N, dtype=torch.bfloat16, device=x.device)
         _lib.call("nkb_gemm_rs_bf16", self.ptrs_dev.data_ptr(), self.flag_off,
                   self.heap.offset_of(stage), self.heap.offset_of(tflags), self.rank, self.world,
-                  R, self.epoch.data_ptr(), int(rs_ctas), x.data_ptr(), x.stride(0), w.data_ptr(),
+                  R, self.epoch.data_ptr(), x.data_ptr(), x.stride(0), w.data_ptr(),
                   w.stride(0), int(b_mn), out.data_ptr(), out.stride(0), N, K, ptr(bias), ptr(res),
                   res.stride(0) if res is not None else 0,
                   status_word(self.heap.device).data_ptr(), int(bn), _lib.stream_ptr())
@@ -333,7 +353,7 @@ class TorchGroup:
             dist.all_gather_into_tensor(x_full, mine, group=self.group)
         return gemm(x_full, w, b_mn=b_mn, bias=bias, out=out)
 
-    def gemm_rs(self, x, w, *, out=None, bias=None, res=None, b_mn=False, rs_ctas=16, bn=0):
+    def gemm_rs(self, x, w, *, out=None, bias=None, res=None, b_mn=False, bn=0):
         """Unfused stand-in of ``PeerGroup.gemm_rs``: GEMM (fp32 out), reduce-scatter of the
         rows, then bias and residual."""
         from ..ops.gemm import gemm

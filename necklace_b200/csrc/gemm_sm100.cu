@@ -67,25 +67,30 @@ struct GemmArgs {
   // with the local shard.  ready_flags doubles as the flag array; the target epoch is
   // *ag_epoch + 1 (advanced by a follow-up kernel).
   int ag_ctas;
+  long long ag_rflag_off;  // byte offset of ready_flags in every member's heap
   CommCtx ag;
   long long ag_data_off;   // byte offset of A inside every heap
   int ag_rows_per_rank;
   long long ag_row_bytes;  // bytes to copy per row (K * 2)
   long long ag_pitch;      // row pitch in bytes
-  // Reduce-scatter fused behind the GEMM (optional, rs_ctas > 0): rows of the result are
-  // owned by ranks in contiguous blocks of rs_rows_per_rank.  Each partial 128-row tile
-  // is stored straight into the owner's staging slab [src rank][rows_per_rank][N] (peer
-  // stores) followed by a per-tile flag; the first rs_ctas CTAs of the owner add the
-  // `world` slabs of a tile as soon as its flags are in, apply bias / residual and write
-  // the final [rows_per_rank, N] block.  Remote owners' tiles are computed first.
-  int rs_ctas;
+  // Reduce-scatter fused behind the GEMM (optional, rs_on): rows of the result are owned by
+  // ranks in contiguous blocks of rs_rows_per_rank.  A partial 128-row tile of another
+  // rank's rows is stored straight into the owner's staging slab [src rank][rows_per_rank][N]
+  // (peer stores, bf16) followed by a per-tile flag.  Every n-block is walked with the
+  // other owners' rows first and this rank's own rows last: by then the peers' partial tiles
+  // of those rows have usually arrived, and the epilogue of an own tile waits for their
+  // flags, adds them to its fp32 accumulator, applies bias / residual and writes the final
+  // [rows_per_rank, N] block.  No CTA is set aside for the reduction.  Staging may be
+  // rewritten by a peer only in the next call, after this rank has entered it (one
+  // cross-rank barrier at the start, done by an idle warp; pushes wait for its go word,
+  // epoch[2]).  C and res are passed as bases shifted by -rank * rows_per_rank rows so that
+  // global row numbers index them.
+  int rs_on;
   CommCtx rs;
   long long rs_stage_off;  // byte offset of the staging slabs in every heap
   long long rs_tflag_off;  // byte offset of the tile flags [src][row block][n block]
   int rs_rows_per_rank;
   int rs_bn;               // tile width used by the GEMM CTAs
-  __nv_bfloat16* rs_out;   // [rows_per_rank, N] on this rank
-  long long rs_ldout;
   // Split-K (optional, split_k > 1): the K range is cut into split_k slices that are
   // scheduled as independent work units, so weight-gradient shapes (few output tiles,
   // very long K) still fill the machine.  Slice s stores its raw fp32 partial tile into
@@ -99,75 +104,68 @@ struct GemmArgs {
   CUtensorMap tm_c, tm_aux;
 };
 
-// Reduce role of the fused reduce-scatter (see GemmArgs).
-__device__ __noinline__ static void rs_reduce_role(const GemmArgs& g) {
-  const CommCtx& c = g.rs;
-  const int e = *reinterpret_cast<volatile int*>(c.epoch) + 1;
-  const int R = g.rs_rows_per_rank, BNt = g.rs_bn;
-  const int rb = R / 128, nbk = (g.N + BNt - 1) / BNt;
-  const char* stage = static_cast<const char*>(c.heap[c.rank]) + g.rs_stage_off;
-  const int* tflags = reinterpret_cast<const int*>(static_cast<const char*>(c.heap[c.rank]) +
-                                                   g.rs_tflag_off);
-  __shared__ int sh_ok;
-  bool ok = true;
-  for (int u = blockIdx.x; u < rb * nbk && ok; u += g.rs_ctas) {
-    const int lb = u / nbk, nb = u % nbk;
-    if (threadIdx.x == 0) sh_ok = 1;
-    __syncthreads();
-    if (threadIdx.x < c.world) {
-      if (!wait_flag_ge(tflags + ((long long)threadIdx.x * rb + lb) * nbk + nb, e)) {
-        sh_ok = 0;
-        if (c.status) atomicCAS(c.status, 0, NKB_ERR_FLAG_WAIT);
-      }
-    }
-    __syncthreads();
-    ok = sh_ok != 0;
-    if (!ok) break;
-    const int ncols = min(BNt, g.N - nb * BNt);
-    const int v_per_row = ncols >> 3;  // N % 8 == 0 is required
-    for (int i = threadIdx.x; i < 128 * v_per_row; i += blockDim.x) {
-      const int r = lb * 128 + i / v_per_row, col = nb * BNt + (i % v_per_row) * 8;
-      float acc[8];
-#pragma unroll
-      for (int k = 0; k < 8; ++k) acc[k] = 0.f;
-      // all members' partial vectors are requested before any is added
-      uint4 pv[COMM_MAX_WORLD];
-#pragma unroll
-      for (int src = 0; src < COMM_MAX_WORLD; ++src)
-        if (src < c.world)
-          pv[src] = ld_volatile_v4(stage + (((long long)src * R + r) * g.N + col) * 2);
-#pragma unroll
-      for (int src = 0; src < COMM_MAX_WORLD; ++src) {
-        if (src >= c.world) continue;
-        uint32_t w[4] = {pv[src].x, pv[src].y, pv[src].z, pv[src].w};
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          float2 f = unpack_bf16x2(w[k]);
-          acc[2 * k] += f.x;
-          acc[2 * k + 1] += f.y;
-        }
-      }
-      if (g.bias) {
-#pragma unroll
-        for (int k = 0; k < 8; ++k) acc[k] += __bfloat162float(g.bias[col + k]);
-      }
-      if (g.res) {
-        uint4 v = *reinterpret_cast<const uint4*>(g.res + (long long)r * g.ldres + col);
-        uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          float2 f = unpack_bf16x2(w[k]);
-          acc[2 * k] += f.x;
-          acc[2 * k + 1] += f.y;
-        }
-      }
-      *reinterpret_cast<uint4*>(g.rs_out + (long long)r * g.rs_ldout + col) =
-          make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
-                     pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
-    }
+// Tile t of the persistent walk -> (m-block, n-block).  The plain walk goes down the m-blocks
+// of one n-block before the next n-block.  Fused with a collective (m_major) it finishes all
+// n-blocks of an m-block first: with the all-gather in front it starts with this rank's own
+// rows (shift), so that the CTAs have local work while the peers' rows arrive; with the
+// reduce-scatter behind it starts with the next rank's rows and ends with its own, whose
+// partial tiles from the peers have arrived by then.
+__device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int shift, bool m_major,
+                                            int& mb, int& nb) {
+  if (m_major) {
+    mb = (t / num_n + shift) % num_m;
+    nb = t % num_n;
+  } else {
+    mb = (t % num_m + shift) % num_m;
+    nb = t / num_m;
   }
-  // a peer may start refilling this rank's staging only after everyone finished reducing
-  if (ok) cta_barrier(c, 2 * e);
+}
+
+__device__ __forceinline__ void set_error(int* status, volatile int* abort_flag, int code) {
+  *abort_flag = 1;
+  if (status) atomicCAS(status, 0, code);
+}
+
+// Cross-rank barrier done by one warp on flag slot `slot`.  Returns false on timeout.
+__device__ __forceinline__ bool warp_barrier(const CommCtx& c, int slot, int value, int lane) {
+  bool ok = true;
+  __threadfence_system();
+  if (lane < c.world) {
+    st_release_sys(flag_ptr(c, lane, slot, c.rank), value);
+    ok = wait_flag_ge(flag_ptr(c, c.rank, slot, lane), value);
+  }
+  return __all_sync(0xffffffffu, ok);
+}
+
+// Fused reduce-scatter, start of the kernel (one warp of the first GEMM CTA): once every member
+// has entered this call, its staging slab may be written; the go word tells this rank's
+// epilogue warps.
+__device__ __forceinline__ void rs_open_gate(const GemmArgs& g, int epoch, int lane,
+                                             volatile int* abort_flag) {
+  const bool ok = warp_barrier(g.rs, 0, 2 * epoch - 1, lane);
+  if (lane == 0) {
+    if (ok) st_release_sys(g.rs.epoch + 2, epoch);
+    else set_error(g.status, abort_flag, NKB_ERR_FLAG_WAIT);
+  }
+}
+// An epilogue warp before its first peer store of the call.
+__device__ __forceinline__ bool rs_wait_gate(const GemmArgs& g, int epoch, int lane) {
+  bool ok = true;
+  if (lane == 0) ok = wait_flag_ge(g.rs.epoch + 2, epoch);
+  return __all_sync(0xffffffffu, ok);
+}
+// An epilogue warp before the epilogue of one of this rank's own tiles: the partial tiles of
+// all other members for (row block lb, n-block nb) are in the staging slab.
+__device__ __forceinline__ bool rs_wait_partials(const GemmArgs& g, int lb, int nb, int nbk,
+                                                 int epoch, int lane) {
+  bool ok = true;
+  if (lane < g.rs.world && lane != g.rs.rank) {
+    const int* tflags = reinterpret_cast<const int*>(
+        static_cast<const char*>(g.rs.heap[g.rs.rank]) + g.rs_tflag_off);
+    ok = wait_flag_ge(tflags + ((long long)lane * (g.rs_rows_per_rank / 128) + lb) * nbk + nb,
+                      epoch);
+  }
+  return __all_sync(0xffffffffu, ok);
 }
 
 // Staging row pointer and flag of the 128-row block that starts at global row `row_blk0`
@@ -186,58 +184,59 @@ __device__ __forceinline__ __nv_bfloat16* rs_tile_dst(const GemmArgs& g, int row
 }
 
 // Copy role of the fused all-gather (see GemmArgs).  One flag per 128-row block.
+// The copy is a push: a CTA reads a 128-row block of this rank's own shard and stores it
+// into one peer's gather buffer (posted writes pipeline over NVLink; peer loads, which are
+// ordered system-scope reads, ran one round trip at a time), fences, and raises the block's
+// flag in that peer's flag array.  A peer's buffer may be written once that peer has entered
+// the kernel (first barrier): everything it launched before, readers of the buffer's previous
+// content included, has finished by then.  No barrier is needed at the end: nobody reads
+// this rank's memory, and this rank's own stores are fenced before the flags they precede.
 __device__ __noinline__ static void ag_copy_role(const GemmArgs& g) {
   const CommCtx& c = g.ag;
   const int e = *reinterpret_cast<volatile int*>(c.epoch) + 1;
   int* flags = const_cast<int*>(g.ready_flags);
   const int R = g.ag_rows_per_rank;
   const int blocks_per_rank = (R + 127) / 128;
-  bool ok = cta_barrier(c, 2 * e - 1);  // every rank's shard is complete
-  if (ok) {
-    // local shard: ready at once
-    for (int b = blockIdx.x * blockDim.x + threadIdx.x; b < blocks_per_rank;
-         b += g.ag_ctas * blockDim.x)
-      st_release_sys(flags + c.rank * blocks_per_rank + b, e);
-    char* mine = static_cast<char*>(c.heap[c.rank]) + g.ag_data_off;
-    const long long v_per_row = g.ag_row_bytes >> 4;
-    // (peer, 128-row block) units are dealt round-robin to the copy CTAs, nearest peer first.
-    // A peer load takes microseconds over NVLink, so every thread keeps AG_UNROLL 16-byte
-    // loads in flight before it stores any of them (one load at a time ran at ~20 GB/s).
-    constexpr int AG_UNROLL = 8;
-    const int units = (c.world - 1) * blocks_per_rank;
-    for (int u = blockIdx.x; u < units; u += g.ag_ctas) {
-      const int q = (c.rank + 1 + u / blocks_per_rank) % c.world;
-      const int b = u % blocks_per_rank;
-      const char* theirs = static_cast<const char*>(c.heap[q]) + g.ag_data_off;
-      const int r0 = q * R + b * 128;
-      const int nrows = min(128, R - b * 128);
-      const long long total = (long long)nrows * v_per_row;
-      for (long long i0 = threadIdx.x; i0 < total; i0 += (long long)blockDim.x * AG_UNROLL) {
-        uint4 v[AG_UNROLL];
+  bool ok = cta_barrier(c, 2 * e - 1);  // every rank is in the kernel
+  if (!ok) return;
+  // local shard: ready at once
+  for (int b = blockIdx.x * blockDim.x + threadIdx.x; b < blocks_per_rank;
+       b += g.ag_ctas * blockDim.x)
+    st_release_sys(flags + c.rank * blocks_per_rank + b, e);
+  const char* mine = static_cast<const char*>(c.heap[c.rank]) + g.ag_data_off;
+  const int v_per_row = (int)(g.ag_row_bytes >> 4);  // 128 rows of it fit an int by far
+  constexpr int AG_UNROLL = 8;
+  // (peer, block) units dealt round-robin to the copy CTAs.  A peer's GEMM walks the row
+  // blocks starting with its own shard and going up the ranks, so it needs this rank's rows
+  // the sooner the closer it sits below this rank: peers are served in that order.
+  const int units = (c.world - 1) * blocks_per_rank;
+  for (int u = blockIdx.x; u < units; u += g.ag_ctas) {
+    const int q = (c.rank + c.world - 1 - u / blocks_per_rank) % c.world;
+    const int b = u % blocks_per_rank;
+    const long long blk_off = (long long)(c.rank * R + b * 128) * g.ag_pitch;
+    const char* src = mine + blk_off;
+    char* dst = static_cast<char*>(c.heap[q]) + g.ag_data_off + blk_off;
+    const int nrows = min(128, R - b * 128);
+    const int total = nrows * v_per_row;
+    for (int i0 = threadIdx.x; i0 < total; i0 += (int)blockDim.x * AG_UNROLL) {
+      uint4 v[AG_UNROLL];
+      long long off[AG_UNROLL];
 #pragma unroll
-        for (int k = 0; k < AG_UNROLL; ++k) {
-          const long long i = i0 + (long long)k * blockDim.x;
-          if (i < total) {
-            const long long row = r0 + i / v_per_row, col = (i % v_per_row) << 4;
-            v[k] = ld_volatile_v4(theirs + row * g.ag_pitch + col);
-          }
-        }
+      for (int k = 0; k < AG_UNROLL; ++k) {
+        const int i = i0 + k * (int)blockDim.x;
+        off[k] = (long long)(i / v_per_row) * g.ag_pitch + ((i % v_per_row) << 4);
+        if (i < total) v[k] = *reinterpret_cast<const uint4*>(src + off[k]);
+      }
 #pragma unroll
-        for (int k = 0; k < AG_UNROLL; ++k) {
-          const long long i = i0 + (long long)k * blockDim.x;
-          if (i < total) {
-            const long long row = r0 + i / v_per_row, col = (i % v_per_row) << 4;
-            *reinterpret_cast<uint4*>(mine + row * g.ag_pitch + col) = v[k];
-          }
-        }
-      }
-      __syncthreads();
-      if (threadIdx.x == 0) {
-        __threadfence();
-        st_release_sys(flags + q * blocks_per_rank + b, e);
-      }
+      for (int k = 0; k < AG_UNROLL; ++k)
+        if (i0 + k * (int)blockDim.x < total) *reinterpret_cast<uint4*>(dst + off[k]) = v[k];
     }
-    cta_barrier(c, 2 * e);  // peers may overwrite their shards only after everyone pulled
+    __threadfence_system();  // this thread's stores have reached the peer
+    __syncthreads();
+    if (threadIdx.x == 0)
+      st_release_sys(reinterpret_cast<int*>(static_cast<char*>(c.heap[q]) + g.ag_rflag_off) +
+                         c.rank * blocks_per_rank + b,
+                     e);
   }
 }
 
@@ -291,11 +290,6 @@ __device__ __forceinline__ float gelu_tanh_grad(float x) {
   asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
   float du = k0 * (1.f + 3.f * k1 * x2);
   return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * du;
-}
-
-__device__ __forceinline__ void set_error(int* status, volatile int* abort_flag, int code) {
-  *abort_flag = 1;
-  if (status) atomicCAS(status, 0, code);
 }
 
 // ---- epilogue staging tile: 32 rows x 128 bytes per warp, 16-byte chunks XOR-swizzled
@@ -619,7 +613,8 @@ __device__ __forceinline__ void epilogue_chunk_general(const GemmArgs& g, uint8_
                                                uint32_t t_addr, int row0, int rows_valid, int n0,
                                                float alpha, bool bias_vec, int cc,
                                                __nv_bfloat16* rs_dst, long long rs_ld,
-                                               float* raw_dst) {
+                                               float* raw_dst,
+                                               const __nv_bfloat16* rs_own = nullptr) {
     uint32_t r[64];
     tmem_ld_32x32(t_addr + cc * 64, r);
     tmem_ld_32x32(t_addr + cc * 64 + 32, r + 32);
@@ -654,6 +649,35 @@ __device__ __forceinline__ void epilogue_chunk_general(const GemmArgs& g, uint8_
         stage_put_bf16(stg, lane, v);
         stage_store_bf16(stg, lane, rs_dst + cc * 64, rs_ld, rows_valid, cols_valid);
         return;
+      }
+      if (rs_own) {
+        // own rows: add the other members' partial sums (this lane's row of each slab, read
+        // from L2, where the peers' stores arrived); bias, residual and the store follow
+        if (lane < rows_valid) {
+          const long long slab = (long long)g.rs_rows_per_rank * g.N;
+          for (int src = 0; src < g.rs.world; ++src) {
+            if (src == g.rs.rank) continue;
+            const __nv_bfloat16* prow = rs_own + src * slab + (long long)lane * g.N + cc * 64;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              uint4 pv[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q)
+                if ((h * 4 + q) * 8 < cols_valid) pv[q] = ld_cg_v4(prow + (h * 4 + q) * 8);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                if ((h * 4 + q) * 8 >= cols_valid) continue;
+                const uint32_t w[4] = {pv[q].x, pv[q].y, pv[q].z, pv[q].w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float2 f = unpack_bf16x2(w[j]);
+                  v[(h * 4 + q) * 8 + 2 * j] += f.x;
+                  v[(h * 4 + q) * 8 + 2 * j + 1] += f.y;
+                }
+              }
+            }
+          }
+        }
       }
     }
     if (g.bias) {
@@ -771,12 +795,61 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, uint8_t* stg, i
                                               uint32_t t_addr, int row0, int rows_valid, int n0,
                                               float alpha, bool bias_vec, int cc0,
                                               __nv_bfloat16* rs_dst = nullptr,
-                                              long long rs_ld = 0, float* raw_dst = nullptr) {
+                                              long long rs_ld = 0, float* raw_dst = nullptr,
+                                              const __nv_bfloat16* rs_own = nullptr) {
   epilogue_chunk_general<MODE>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec, cc0,
-                               rs_dst, rs_ld, raw_dst);
+                               rs_dst, rs_ld, raw_dst, rs_own);
   if constexpr (NCW > 1)
     epilogue_chunk_general<MODE>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec,
-                                 cc0 + 1, rs_dst, rs_ld, raw_dst);
+                                 cc0 + 1, rs_dst, rs_ld, raw_dst, rs_own);
+}
+
+// Epilogue of one tile of the fused reduce-scatter by one warp (see GemmArgs::rs_on).
+// blk_row0: first global row of this CTA's 128-row block.  Returns false on a wait that ran
+// out.  For a tile of another rank's rows *tflag is the flag to raise with rs_signal_tile
+// once the accumulator has been handed back (the stores are only issued here); null for an
+// own tile.
+template <int BN, int MODE, int NCW>
+__device__ __noinline__ bool rs_epilogue_tile(const GemmArgs& g, uint8_t* stg, int lane,
+                                                 uint32_t t_addr, int blk_row0, int lane_grp,
+                                                 int n0, int nb, float alpha, bool bias_vec,
+                                                 int cc0, int epoch, bool& gate_open,
+                                                 int** tflag_out) {
+  const int R = g.rs_rows_per_rank;
+  const int owner = blk_row0 / R;
+  const int row0 = blk_row0 + lane_grp * 32;
+  if (owner != g.rs.rank) {
+    if (!gate_open) {
+      if (!rs_wait_gate(g, epoch, lane)) return false;
+      gate_open = true;
+    }
+    __nv_bfloat16* dst = rs_tile_dst(g, blk_row0, lane_grp, n0, tflag_out, nb, g.num_n_blocks);
+    epilogue_tile<BN, MODE, NCW>(g, stg, lane, t_addr, row0, 32, n0, alpha, bias_vec, cc0, dst,
+                                 g.N);
+    return true;
+  }
+  *tflag_out = nullptr;
+  const int lb = (blk_row0 - owner * R) / 128;
+  if (!rs_wait_partials(g, lb, nb, g.num_n_blocks, epoch, lane)) return false;
+  const __nv_bfloat16* own =
+      reinterpret_cast<const __nv_bfloat16*>(static_cast<const char*>(g.rs.heap[g.rs.rank]) +
+                                             g.rs_stage_off) +
+      (long long)(lb * 128 + lane_grp * 32) * g.N + n0;
+  epilogue_tile<BN, MODE, NCW>(g, stg, lane, t_addr, row0, 32, n0, alpha, bias_vec, cc0, nullptr,
+                               0, nullptr, own);
+  return true;
+}
+
+// All eight epilogue warps after the stores of a pushed tile: once every warp has issued its
+// stores (named barrier), one thread waits for them to land at the owner (the fence covers
+// the other threads' stores through the barrier) and raises the tile's flag there.  The
+// other warps go on to the next tile meanwhile.
+__device__ __forceinline__ void rs_signal_tile(int* tflag, int epoch, int ew, int lane) {
+  asm volatile("bar.sync 1, 256;" ::: "memory");
+  if (ew == 0 && lane == 0) {
+    __threadfence_system();
+    st_release_sys(tflag, epoch);
+  }
 }
 
 template <int BN, bool A_MN, bool B_MN, int MODE>
@@ -801,27 +874,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   constexpr bool COMM = MODE == 1;
-  const int ag_ctas = COMM ? g.ag_ctas : 0, rs_ctas = COMM ? g.rs_ctas : 0;
+  const int ag_ctas = COMM ? g.ag_ctas : 0;
+  const bool rs_on = COMM && g.rs_on;
   const int split_k = MODE == 2 ? g.split_k : 1;
   if constexpr (COMM) {
     if ((int)blockIdx.x < ag_ctas) {
       ag_copy_role(g);
       return;
     }
-    if ((int)blockIdx.x < rs_ctas) {
-      rs_reduce_role(g);
-      return;
-    }
   }
-  const int pre = ag_ctas + rs_ctas;  // at most one of the two is non-zero
+  const int pre = ag_ctas;
   const int cta_id = blockIdx.x - pre, n_ctas = gridDim.x - pre;
-  const int rs_epoch = rs_ctas ? *reinterpret_cast<volatile int*>(g.rs.epoch) + 1 : 0;
+  const int rs_epoch = rs_on ? *reinterpret_cast<volatile int*>(g.rs.epoch) + 1 : 0;
   const int ready_target = ag_ctas ? *reinterpret_cast<volatile int*>(g.ag.epoch) + 1
                                    : g.ready_target;
   // with a fused all-gather the local shard's row blocks come first
   // ... and with a fused reduce-scatter the rows owned by the other ranks
   const int mb_shift = ag_ctas ? g.ag.rank * ((g.ag_rows_per_rank + BM - 1) / BM)
-                     : rs_ctas ? ((g.rs.rank + 1) % g.rs.world) * (g.rs_rows_per_rank / BM) : 0;
+                     : rs_on ? ((g.rs.rank + 1) % g.rs.world) * (g.rs_rows_per_rank / BM) : 0;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_tiles = g.num_m_blocks * g.num_n_blocks;
@@ -856,7 +926,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (warp < 4) {
     reg_alloc_dec<GEMM_CTRL_REGS>();
   }
-  if (warp == 0) {
+  if (warp == 2) {
+    if (rs_on && cta_id == 0) rs_open_gate(g, rs_epoch, lane, abort_flag);
+  } else if (warp == 0) {
     // ------------------------------------------------------------ producer
     if (lane == 0) {
       int stage = 0;
@@ -865,7 +937,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int u = cta_id; u < num_units && ok; u += n_ctas) {
         const int t = u % num_tiles, ks = u / num_tiles;
         const int kb_lo = ks * KB / split_k, kb_hi = (ks + 1) * KB / split_k;
-        const int mb = (t % g.num_m_blocks + mb_shift) % g.num_m_blocks, nb = t / g.num_m_blocks;
+        int mb, nb;
+        tile_coords(t, g.num_m_blocks, g.num_n_blocks, mb_shift, ag_ctas > 0 || rs_on, mb, nb);
         const int m0 = mb * BM, n0 = nb * BN;
         if (g.ready_flags) {
           int f0 = m0 / g.rows_per_flag;
@@ -976,6 +1049,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint8_t* stg = smem + STAGES * STAGE_BYTES + ew * EPI_STAGE_BYTES;
     int acc = 0;
     uint32_t acc_phase = 0;
+    bool rs_gate_open = false;
     const float alpha = g.alpha_dev ? g.alpha * __ldg(g.alpha_dev) : g.alpha;
     const bool bias_vec = g.bias && ((reinterpret_cast<uintptr_t>(g.bias) & 15) == 0);
     const bool fast = MODE == 0 && epi_fast_ok(g);
@@ -983,7 +1057,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const __nv_bfloat16* in_src = epi_async_src(g, &in_ld);
     for (int u = cta_id; u < num_units; u += n_ctas) {
       const int t = u % num_tiles, ks = u / num_tiles;
-      const int mb = (t % g.num_m_blocks + mb_shift) % g.num_m_blocks, nb = t / g.num_m_blocks;
+      int mb, nb;
+      tile_coords(t, g.num_m_blocks, g.num_n_blocks, mb_shift, ag_ctas > 0 || rs_on, mb, nb);
       const int row0 = mb * BM + lane_grp * 32;  // first row of this warp's slab
       const int n0 = nb * BN;
       int rows_valid = g.M - row0;
@@ -998,14 +1073,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       tc_fence_after();
       const uint32_t t_addr = tmem_base + (uint32_t(lane_grp * 32) << 16) + acc * BN;
-      if (rs_ctas) {
-        int* tflag;
-        __nv_bfloat16* dst = rs_tile_dst(g, mb * BM, lane_grp, n0, &tflag, nb, g.num_n_blocks);
-        epilogue_tile<BN, MODE, NCW>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec,
-                                     cc0, dst, g.N);
-        __threadfence_system();
-        asm volatile("bar.sync 1, 256;" ::: "memory");  // the eight epilogue warps
-        if (ew == 0 && lane == 0) st_release_sys(tflag, rs_epoch);
+      int* rs_tflag = nullptr;
+      if (rs_on) {
+        if (!rs_epilogue_tile<BN, MODE, NCW>(g, stg, lane, t_addr, mb * BM, lane_grp, n0, nb, alpha,
+                                             bias_vec, cc0, rs_epoch, rs_gate_open, &rs_tflag)) {
+          set_error(g.status, abort_flag, NKB_ERR_FLAG_WAIT);
+          break;
+        }
       } else if (fast) {
         epilogue_fast_tile(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec, cc0, NCW,
                            first_async);
@@ -1017,6 +1091,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      if (rs_tflag) rs_signal_tile(rs_tflag, rs_epoch, ew, lane);
       if (++acc == 2) {
         acc = 0;
         acc_phase ^= 1;
@@ -1069,30 +1144,27 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   constexpr bool COMM = MODE == 1;
-  const int ag_ctas = COMM ? g.ag_ctas : 0, rs_ctas = COMM ? g.rs_ctas : 0;
+  const int ag_ctas = COMM ? g.ag_ctas : 0;
+  const bool rs_on = COMM && g.rs_on;
   const int split_k = MODE == 2 ? g.split_k : 1;
   if constexpr (COMM) {
     if ((int)blockIdx.x < ag_ctas) {  // ag_ctas is even: whole clusters take the copy role
       ag_copy_role(g);
       return;
     }
-    if ((int)blockIdx.x < rs_ctas) {
-      rs_reduce_role(g);
-      return;
-    }
   }
-  const int rs_epoch = rs_ctas ? *reinterpret_cast<volatile int*>(g.rs.epoch) + 1 : 0;
+  const int rs_epoch = rs_on ? *reinterpret_cast<volatile int*>(g.rs.epoch) + 1 : 0;
   const int ready_target = ag_ctas ? *reinterpret_cast<volatile int*>(g.ag.epoch) + 1
                                    : g.ready_target;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
-  const int pre = ag_ctas + rs_ctas;
+  const int pre = ag_ctas;
   const int pair = ((int)blockIdx.x - pre) >> 1, npairs = ((int)gridDim.x - pre) >> 1;
   const int num_m2 = (g.M + 255) / 256;
   const int mb_shift = ag_ctas ? g.ag.rank * ((g.ag_rows_per_rank + 255) / 256)
-                     : rs_ctas ? ((g.rs.rank + 1) % g.rs.world) * (g.rs_rows_per_rank / 256) : 0;
+                     : rs_on ? ((g.rs.rank + 1) % g.rs.world) * (g.rs_rows_per_rank / 256) : 0;
   const int num_tiles = num_m2 * g.num_n_blocks;
   const int KB = (g.K + BK - 1) / BK;
   const int num_units = num_tiles * split_k;
@@ -1124,7 +1196,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
   if (warp < 4) {
     reg_alloc_dec<GEMM_CTRL_REGS>();
   }
-  if (warp == 0) {
+  if (warp == 2) {
+    if (rs_on && pair == 0 && leader) rs_open_gate(g, rs_epoch, lane, abort_flag);
+  } else if (warp == 0) {
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
@@ -1132,7 +1206,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       for (int u = pair; u < num_units && ok; u += npairs) {
         const int t = u % num_tiles, ks = u / num_tiles;
         const int kb_lo = ks * KB / split_k, kb_hi = (ks + 1) * KB / split_k;
-        const int mb2 = (t % num_m2 + mb_shift) % num_m2, nb = t / num_m2;
+        int mb2, nb;
+        tile_coords(t, num_m2, g.num_n_blocks, mb_shift, ag_ctas > 0 || rs_on, mb2, nb);
         const int m0 = mb2 * 256 + (int)rank * 128;
         const int nB = nb * BN + (int)rank * 128;
         if (g.ready_flags) {
@@ -1237,6 +1312,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
     uint8_t* stg = smem + PAIR_STAGES * PAIR_STAGE_BYTES + ew * EPI_STAGE_BYTES;
     int acc = 0;
     uint32_t acc_phase = 0;
+    bool rs_gate_open = false;
     const float alpha = g.alpha_dev ? g.alpha * __ldg(g.alpha_dev) : g.alpha;
     const bool bias_vec = g.bias && ((reinterpret_cast<uintptr_t>(g.bias) & 15) == 0);
     const bool fast = MODE == 0 && epi_fast_ok(g);
@@ -1244,7 +1320,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
     const __nv_bfloat16* in_src = epi_async_src(g, &in_ld);
     for (int u = pair; u < num_units; u += npairs) {
       const int t = u % num_tiles, ks = u / num_tiles;
-      const int mb2 = (t % num_m2 + mb_shift) % num_m2, nb = t / num_m2;
+      int mb2, nb;
+      tile_coords(t, num_m2, g.num_n_blocks, mb_shift, ag_ctas > 0 || rs_on, mb2, nb);
       const int row0 = mb2 * 256 + (int)rank * 128 + lane_grp * 32;
       const int n0 = nb * BN;
       int rows_valid = g.M - row0;
@@ -1259,15 +1336,14 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       }
       tc_fence_after();
       const uint32_t t_addr = tmem_base + (uint32_t(lane_grp * 32) << 16) + acc * BN;
-      if (rs_ctas) {
-        int* tflag;
-        __nv_bfloat16* dst = rs_tile_dst(g, mb2 * 256 + (int)rank * 128, lane_grp, n0, &tflag, nb,
-                                         g.num_n_blocks);
-        epilogue_tile<BN, MODE, NCW>(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec,
-                                     cc0, dst, g.N);
-        __threadfence_system();
-        asm volatile("bar.sync 1, 256;" ::: "memory");
-        if (ew == 0 && lane == 0) st_release_sys(tflag, rs_epoch);
+      int* rs_tflag = nullptr;
+      if (rs_on) {
+        if (!rs_epilogue_tile<BN, MODE, NCW>(g, stg, lane, t_addr, mb2 * 256 + (int)rank * 128,
+                                             lane_grp, n0, nb, alpha, bias_vec, cc0, rs_epoch,
+                                             rs_gate_open, &rs_tflag)) {
+          set_error(g.status, abort_flag, NKB_ERR_FLAG_WAIT);
+          break;
+        }
       } else if (fast) {
         epilogue_fast_tile(g, stg, lane, t_addr, row0, rows_valid, n0, alpha, bias_vec, cc0, NCW,
                            first_async);
@@ -1282,6 +1358,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
         if (leader) mbar_arrive(&acc_empty[acc]);
         else mbar_arrive_cluster(mapa_shared(smem_u32(&acc_empty[acc]), 0));
       }
+      if (rs_tflag) rs_signal_tile(rs_tflag, rs_epoch, ew, lane);
       if (++acc == 2) {
         acc = 0;
         acc_phase ^= 1;
@@ -1377,11 +1454,11 @@ static int launch_gemm_mode(const CUtensorMap& tmA, const CUtensorMap& tmB, Gemm
   g.num_m_blocks = (g.M + BM - 1) / BM;
   g.num_n_blocks = (g.N + BN - 1) / BN;
   int tiles = g.num_m_blocks * g.num_n_blocks * g.split_k;
-  int ctas = num_sms() - g.ag_ctas - g.rs_ctas;
+  int ctas = num_sms() - g.ag_ctas;
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
   if (tiles < ctas) ctas = tiles;
   g.rs_bn = BN;
-  kern<<<ctas + g.ag_ctas + g.rs_ctas, GEMM_THREADS, smem_bytes, stream>>>(tmA, tmB, g);
+  kern<<<ctas + g.ag_ctas, GEMM_THREADS, smem_bytes, stream>>>(tmA, tmB, g);
   return (int)cudaGetLastError();
 }
 
@@ -1390,7 +1467,7 @@ static int launch_gemm_mode(const CUtensorMap& tmA, const CUtensorMap& tmB, Gemm
 template <int BN, bool A_MN, bool B_MN>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs& g, int max_ctas,
                        cudaStream_t stream) {
-  if (g.ag_ctas || g.rs_ctas) return launch_gemm_mode<BN, A_MN, B_MN, 1>(tmA, tmB, g, max_ctas, stream);
+  if (g.ag_ctas || g.rs_on) return launch_gemm_mode<BN, A_MN, B_MN, 1>(tmA, tmB, g, max_ctas, stream);
   if (g.split_k > 1) return launch_gemm_mode<BN, A_MN, B_MN, 2>(tmA, tmB, g, max_ctas, stream);
   return launch_gemm_mode<BN, A_MN, B_MN, 0>(tmA, tmB, g, max_ctas, stream);
 }
@@ -1410,20 +1487,20 @@ static int launch_gemm_pair_mode(const CUtensorMap& tmA, const CUtensorMap& tmB,
   g.num_m_blocks = (g.M + 255) / 256;
   g.num_n_blocks = (g.N + 255) / 256;
   int tiles = g.num_m_blocks * g.num_n_blocks * g.split_k;
-  int ctas = num_sms() - g.ag_ctas - g.rs_ctas;
+  int ctas = num_sms() - g.ag_ctas;
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
   ctas &= ~1;
   if (2 * tiles < ctas) ctas = 2 * tiles;
   if (ctas < 2) ctas = 2;
   g.rs_bn = 256;
-  kern<<<ctas + g.ag_ctas + g.rs_ctas, GEMM_THREADS, smem_bytes, stream>>>(tmA, tmB, g);
+  kern<<<ctas + g.ag_ctas, GEMM_THREADS, smem_bytes, stream>>>(tmA, tmB, g);
   return (int)cudaGetLastError();
 }
 
 template <bool A_MN, bool B_MN>
 static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs& g,
                             int max_ctas, cudaStream_t stream) {
-  if (g.ag_ctas || g.rs_ctas) return launch_gemm_pair_mode<A_MN, B_MN, 1>(tmA, tmB, g, max_ctas, stream);
+  if (g.ag_ctas || g.rs_on) return launch_gemm_pair_mode<A_MN, B_MN, 1>(tmA, tmB, g, max_ctas, stream);
   if (g.split_k > 1) return launch_gemm_pair_mode<A_MN, B_MN, 2>(tmA, tmB, g, max_ctas, stream);
   return launch_gemm_pair_mode<A_MN, B_MN, 0>(tmA, tmB, g, max_ctas, stream);
 }
@@ -1500,7 +1577,7 @@ static int gemm_run(GemmArgs g, const void* A, long long lda, int a_mn, const vo
   // split-K when the output has too few tiles to occupy the machine and K is long
   g.split_k = 1;
   g.splitk_ws = nullptr;
-  if (g_splitk_enabled && g_splitk_ws && !g.ag_ctas && !g.rs_ctas && g.epi == NKB_EPI_NONE &&
+  if (g_splitk_enabled && g_splitk_ws && !g.ag_ctas && !g.rs_on && g.epi == NKB_EPI_NONE &&
       !g.bias && !g.res && (N % 4) == 0 && (g.ldc % 4) == 0 && K >= 2048) {
     long long slots = pair ? num_sms() / 2 : num_sms();
     long long tl = pair ? ((M + 255) / 256) * (long long)((N + 255) / 256)
@@ -1516,7 +1593,7 @@ static int gemm_run(GemmArgs g, const void* A, long long lda, int a_mn, const vo
   CUtensorMap tmA, tmB;
   int rc;
   g.tma_c = g.tma_aux = 0;
-  if (!g.c_fp32 && !g.ag_ctas && !g.rs_ctas && g.split_k == 1 && (g.ldc & 7) == 0 &&
+  if (!g.c_fp32 && !g.ag_ctas && !g.rs_on && g.split_k == 1 && (g.ldc & 7) == 0 &&
       (reinterpret_cast<uintptr_t>(g.C) & 15) == 0 &&
       make_tmap_bf16_2d(&g.tm_c, g.C, N, M, g.ldc, 64, 32) == 0)
     g.tma_c = 1;
@@ -1574,15 +1651,16 @@ extern "C" int nkb_gemm_bf16(const void* A, long long lda, int a_mn, const void*
   g.rows_per_flag = rows_per_flag > 0 ? rows_per_flag : 1;
   g.ready_target = ready_target;
   g.ag_ctas = 0;
-  g.rs_ctas = 0;
+  g.rs_on = 0;
   return gemm_run(g, A, lda, a_mn, B, ldb, b_mn, max_ctas, bn_hint, stream);
 }
 
 
 // A = all-gather over the group of per-rank row shards [rows_per_rank, K] that sit at
 // byte offset data_off (row pitch lda) of every member's heap; C = epi(A_full * B^T).
-// The gather runs inside the GEMM kernel (see GemmArgs::ag_ctas).  ready_flags: local
-// int array with one entry per 128-row block of A_full (zeroed once).
+// The gather runs inside the GEMM kernel (see GemmArgs::ag_ctas).  ready_flags: int array
+// with one entry per 128-row block of A_full at the same offset of every member's heap
+// (zero when the heap is created); A_local: this rank's address of the gather buffer.
 extern "C" int nkb_ag_gemm_bf16(void** heap, long long flag_off, long long data_off, int rank,
                                 int world, int rows_per_rank, int* epoch, int* ready_flags,
                                 int ag_ctas, long long lda, const void* B, long long ldb,
@@ -1610,10 +1688,15 @@ extern "C" int nkb_ag_gemm_bf16(void** heap, long long flag_off, long long data_
   if (ag_ctas <= 0) ag_ctas = 8;
   ag_ctas = (ag_ctas + 1) & ~1;
   g.ag_ctas = world > 1 ? ag_ctas : 0;
-  g.rs_ctas = 0;
+  g.rs_on = 0;
   g.ag.heap = heap; g.ag.flag_off = flag_off; g.ag.rank = rank; g.ag.world = world;
   g.ag.epoch = epoch; g.ag.status = status;
   g.ag_data_off = data_off;
+  // the flag array lies in the heap too (peers raise the flags): its offset follows from the
+  // local addresses of the flags and of the gather buffer
+  g.ag_rflag_off = reinterpret_cast<const char*>(ready_flags) -
+                   (static_cast<const char*>(A_local) - data_off);
+  if (world > 1 && (g.ag_rflag_off < 0 || (g.ag_rflag_off & 3))) return -3;
   g.ag_rows_per_rank = rows_per_rank;
   g.ag_row_bytes = (long long)K * 2;
   g.ag_pitch = lda * 2;
@@ -1628,11 +1711,12 @@ extern "C" int nkb_ag_gemm_bf16(void** heap, long long flag_off, long long data_
 
 // out[rows_per_rank, N] on every rank = rows [rank*rows_per_rank, ...) of
 // sum over ranks of A_r[M, K_r] * B_r[N, K_r]^T (+ bias + res): GEMM and reduce-scatter in
-// one kernel (see GemmArgs::rs_ctas).  stage_off: bf16 [world][rows_per_rank][N] in every
-// heap; tflag_off: int [world][rows_per_rank/128][ceil(N/128)] in every heap (zeroed once).
+// one kernel (see GemmArgs::rs_on).  stage_off: bf16 [world][rows_per_rank][N] in every
+// heap; tflag_off: int [world][rows_per_rank/128][ceil(N/128)] in every heap (zeroed once);
+// epoch: device int[4] ([0] completed calls, [2] the go word of this kernel).
 extern "C" int nkb_gemm_rs_bf16(void** heap, long long flag_off, long long stage_off,
                                 long long tflag_off, int rank, int world, int rows_per_rank,
-                                int* epoch, int rs_ctas, const void* A, long long lda,
+                                int* epoch, const void* A, long long lda,
                                 const void* B, long long ldb, int b_mn, void* out,
                                 long long ldout, int N, int K, const void* bias, const void* res,
                                 long long ldres, int* status, int bn_hint, void* stream) {
@@ -1641,24 +1725,24 @@ extern "C" int nkb_gemm_rs_bf16(void** heap, long long flag_off, long long stage
   if ((lda & 7) || (ldb & 7) || (stage_off & 15) || (tflag_off & 3)) return -3;
   GemmArgs g;
   g.M = rows_per_rank * world; g.N = N; g.K = K;
-  g.C = nullptr; g.ldc = 0; g.c_fp32 = 0; g.accumulate = 0; g.alpha = 1.f; g.alpha_dev = nullptr;
+  // bases shifted so that global row numbers (this rank owns rows [rank * R, (rank + 1) * R))
+  // index the [R, N] output and residual; only own rows are ever touched through them
+  const long long row_shift = (long long)rank * rows_per_rank;
+  g.C = static_cast<__nv_bfloat16*>(out) - row_shift * ldout;
+  g.ldc = ldout; g.c_fp32 = 0; g.accumulate = 0; g.alpha = 1.f; g.alpha_dev = nullptr;
   g.bias = static_cast<const __nv_bfloat16*>(bias);
-  g.res = static_cast<const __nv_bfloat16*>(res);
+  g.res = res ? static_cast<const __nv_bfloat16*>(res) - row_shift * ldres : nullptr;
   g.ldres = ldres;
   g.epi = NKB_EPI_NONE;
   g.aux_out = nullptr; g.aux_in = nullptr; g.ldaux = 0;
   g.status = status;
   g.ready_flags = nullptr; g.rows_per_flag = 1; g.ready_target = 0;
   g.ag_ctas = 0;
-  if (rs_ctas <= 0) rs_ctas = 16;
-  rs_ctas = (rs_ctas + 1) & ~1;
-  g.rs_ctas = rs_ctas;
+  g.rs_on = 1;
   g.rs.heap = heap; g.rs.flag_off = flag_off; g.rs.rank = rank; g.rs.world = world;
   g.rs.epoch = epoch; g.rs.status = status;
   g.rs_stage_off = stage_off; g.rs_tflag_off = tflag_off;
   g.rs_rows_per_rank = rows_per_rank;
-  g.rs_out = static_cast<__nv_bfloat16*>(out);
-  g.rs_ldout = ldout;
   // the tile-flag layout depends on the tile width: fix it (pair tiles when shards are
   // multiples of 256 rows, else single-CTA 128 x 256)
   if (bn_hint == 0) bn_hint = (rows_per_rank % 256 == 0 && g_pair_enabled) ? 512 : 256;

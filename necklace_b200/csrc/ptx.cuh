@@ -475,6 +475,16 @@ __device__ __forceinline__ uint4 ld_nc_v4(const void* p) {
                : "l"(p));
   return v;
 }
+// 16-byte load that is served by L2 and never by L1: for local memory that another GPU wrote
+// during this kernel (its stores arrive in L2).  Unlike a volatile load it is unordered, so a
+// thread can have many in flight.
+__device__ __forceinline__ uint4 ld_cg_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
 // Volatile (non-cached in L1) 16-byte load: used for peer memory that another
 // GPU wrote during this kernel.
 __device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
