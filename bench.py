@@ -419,6 +419,14 @@ class LlamaHybrid(Workload):
             replicas = zrg.world_size
             par = f"dp=1 zr={replicas} mp={mp}"
         self.mp_peer = mp_peer
+        self.fused = fused
+        self.shape = {"rows": mb_seqs * S, "d_model": cfgm.d_model, "d_ff": cfgm.d_ff, "mp": mp}
+        # model FLOPs of one step (forward + backward): 6 per weight of the GEMMs and of the
+        # vocabulary projection per token, plus causal attention (6 * S * d_model per token
+        # and layer)
+        self.flops_per_step = float(B * replicas * S) * (
+            6.0 * (cfgm.n_layer * per_layer + cfgm.vocab * cfgm.d_model) +
+            6.0 * cfgm.n_layer * S * cfgm.d_model)
         # the replica's batch is drawn on tensor-parallel rank 0 and broadcast over the group
         seed_rank = rank - self.mp_rank
         self.hx, self.hy, self.dx, self.dy = _token_pool(cfgm.vocab, B, S, seed_rank, dev, pool=4)
@@ -643,6 +651,55 @@ def comm_roofline(wl, world, dev, peaks):
                           "frac_of_measured_roofline": round(floor_ms / ms, 3)}}
 
 
+def tp_roofline(wl, world, dev, peaks):
+    """CUDA-event time of the fused all-gather -> GEMM and GEMM -> reduce-scatter kernels on
+    the layer shapes of the tensor-parallel group (attention and MLP pair, one micro-batch of
+    rows), run as they alternate in a block, against their floors: the slower of FLOPs over
+    the measured sustained bf16 GEMM rate and the bytes that cross NVLink per direction over
+    the measured 770 GB/s peer bandwidth.  Max over all ranks (every group runs at once)."""
+    import torch
+    import torch.distributed as dist
+    grp, sh = wl.mp_peer, wl.shape
+    if not wl.fused or grp is None or grp.world == 1:
+        return None
+    W, M, C, F = grp.world, sh["rows"], sh["d_model"], sh["d_ff"]
+    r8 = lambda v: v // 8 * 8
+    gemm_peak = peaks.get("bf16_tflops_sustained", 1401.1) * 1e12
+    out, iters = {}, 5
+    for name, n1, k2 in (("attention", r8(3 * C // W), r8(C // W)), ("mlp", r8(2 * F // W), r8(F // W))):
+        xf = grp.heap.alloc(M * C, torch.bfloat16).view(M, C)
+        xf.normal_()
+        w1 = (torch.randn(n1, C, device=dev) * 0.02).bfloat16()
+        x2 = (torch.randn(M, k2, device=dev) * 0.5).bfloat16()
+        w2 = (torch.randn(C, k2, device=dev) * 0.02).bfloat16()
+        for _ in range(2):
+            grp.ag_gemm(xf, w1)
+            grp.gemm_rs(x2, w2)
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(iters)]
+        for e in evs:
+            e[0].record()
+            grp.ag_gemm(xf, w1)
+            e[1].record()
+            grp.gemm_rs(x2, w2)
+            e[2].record()
+        torch.cuda.synchronize()
+        t = torch.tensor([sum(e[0].elapsed_time(e[1]) for e in evs) / iters,
+                          sum(e[1].elapsed_time(e[2]) for e in evs) / iters],
+                         dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        link = (W - 1) / W * M * C * 2
+        for kern, ms, fl in (("ag_gemm", float(t[0]), 2.0 * M * n1 * C),
+                             ("gemm_rs", float(t[1]), 2.0 * M * C * k2)):
+            floor = max(fl / gemm_peak, link / 770e9) * 1e3
+            out[f"{kern}_{name}"] = {"ms": round(ms, 4), "flops": fl, "nvlink_bytes_per_dir": int(link),
+                                     "floor_ms": round(floor, 4),
+                                     "frac_of_measured_roofline": round(floor / ms, 3)}
+    return out
+
+
 def necklace_launcher_arm(args):
     """Config 3 through the framework's own process model: every rank of the launch starts
     one worker of ``examples/gpt2/train_gpt2_necklace.py`` (scheduler / worker services over
@@ -844,6 +901,18 @@ def main():
                                                       (b_e2e / 1e3), 2)}
             except Exception as e:  # noqa: BLE001
                 out["baseline"] = {"error": repr(e)[:200]}
+    if args.impl == "ours" and args.config in (4, 5):
+        step_s = dev_ms / args.steps / 1e3
+        out["roofline_compute"] = {
+            "model_tflop_per_step": round(wl.flops_per_step / 1e12, 1),
+            "tflops_per_gpu": round(wl.flops_per_step / step_s / world / 1e12, 1),
+            "frac_of_measured_sustained_bf16": round(
+                wl.flops_per_step / step_s / world / 1e12 /
+                peaks.get("bf16_tflops_sustained", 1401.1), 3)}
+        try:
+            out["roofline"] = tp_roofline(wl, world, dev, peaks)
+        except Exception as e:  # noqa: BLE001
+            out["roofline"] = {"error": repr(e)[:200]}
     if rank == 0:
         print(json.dumps(out), flush=True)
     if world > 1:
