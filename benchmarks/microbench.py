@@ -1,6 +1,6 @@
 """Micro-benchmarks of the native kernels against the measured device peaks.
 
-``python -m benchmarks.microbench [gemm|norm|ce|adam|attn|all]`` (from the repository
+``python -m benchmarks.microbench [gemm|norm|ce|adam|attn|small|all]`` (from the repository
 root) times each
 kernel with CUDA events (3 warm-up launches, L2 flushed between timed launches by
 writing a 256 MB buffer) and prints achieved TFLOP/s or GB/s, plus the same
@@ -150,6 +150,56 @@ def bench_attn(flush):
                           "torch_sdpa_fwd_ms": round(ms_t, 4)}), flush=True)
 
 
+def bench_small(flush):
+    """``small``: three launches each of the memory-bound kernels and of the 3x3 convolution
+    (im2col gather + tcgen05 GEMM, forward and both gradients) on cases a few hundred MB in
+    size: larger than L2, small enough for a counter capture of single launches."""
+    from necklace_b200.ops import adam_step, cross_entropy_fwd_bwd
+    from necklace_b200.ops.conv import Conv2d
+    from necklace_b200.ops.norm import norm_bwd, norm_fwd
+    rows, C = 65536, 1024
+    x = torch.randn(rows, C, device="cuda").bfloat16()
+    w = torch.ones(C, device="cuda").bfloat16()
+    b = torch.zeros(C, device="cuda").bfloat16()
+    y, st = norm_fwd(x, w, b, 1e-5, False)
+    ms = _time(lambda: norm_fwd(x, w, b, 1e-5, False), iters=3, warmup=1, flush=flush)
+    ms_b = _time(lambda: norm_bwd(x, x, w, st, False), iters=3, warmup=1, flush=flush)
+    byts = rows * C * 2
+    print(json.dumps({"op": "layernorm_fwd", "rows": rows, "C": C, "ms": round(ms, 4),
+                      "GBps": round(2 * byts / ms / 1e6)}))
+    print(json.dumps({"op": "layernorm_bwd", "ms": round(ms_b, 4),
+                      "GBps_min_traffic": round(3 * byts / ms_b / 1e6)}), flush=True)
+    T, V, ld = 2048, 50257, 50304
+    lg = torch.randn(T, ld, device="cuda").bfloat16()
+    tg = torch.randint(0, V, (T,), device="cuda")
+    ms = _time(lambda: cross_entropy_fwd_bwd(lg, tg, V, 1.0 / T), iters=3, warmup=1, flush=flush)
+    print(json.dumps({"op": "ce_fwd_bwd", "T": T, "V": V, "ms": round(ms, 4),
+                      "GBps": round(2 * T * ld * 2 / ms / 1e6)}), flush=True)
+    n = 32 * 1024 * 1024
+    master = torch.randn(n, device="cuda")
+    m, v = torch.zeros_like(master), torch.zeros_like(master)
+    g = torch.randn(n, device="cuda").bfloat16()
+    pb = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    ms = _time(lambda: adam_step(master, m, v, g, pb, lr=1e-4, step=2), iters=3, warmup=1,
+               flush=flush)
+    print(json.dumps({"op": "adam_flat", "n": n, "ms": round(ms, 4),
+                      "GBps": round(n * (12 * 2 + 2 + 2) / ms / 1e6)}), flush=True)
+    del master, m, v, g, pb, lg
+    N, H, Cc = 256, 56, 64
+    conv = Conv2d(Cc, Cc, k=3, stride=1, pad=1, device="cuda")
+    xi = torch.randn(N, H, H, Cc, device="cuda").bfloat16().requires_grad_(True)
+    dy = torch.randn(N, H, H, Cc, device="cuda").bfloat16()
+
+    def fb():
+        xi.grad = None
+        conv.weight.grad = None
+        conv(xi).backward(dy)
+    ms = _time(fb, iters=3, warmup=1, flush=flush)
+    fl = 3 * 2.0 * N * H * H * Cc * Cc * 9
+    print(json.dumps({"op": "conv3x3 fwd+bwd", "N": N, "HW": H, "C": Cc, "ms": round(ms, 4),
+                      "tflops": round(fl / ms / 1e9, 1)}), flush=True)
+
+
 def one_gemm(argv):
     """``gemm_one M N K [a_mn b_mn [epilogue]]``: a handful of launches of one shape (ncu
     captures); epilogue: none | bias | gelu (bias + GELU, saves the pre-activation) |
@@ -206,6 +256,8 @@ def main(argv):
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
     table = {"gemm": bench_gemm, "colsum": bench_colsum, "norm": bench_norm, "ce": bench_ce, "adam": bench_adam,
              "attn": bench_attn}
+    if which == "small":
+        bench_small(flush)
     for name, fn in table.items():
         if which in ("all", name):
             fn(flush)
