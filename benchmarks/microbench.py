@@ -151,7 +151,7 @@ def bench_attn(flush):
 
 
 def bench_small(flush):
-    """``small``: three launches each of the memory-bound kernels and of the 3x3 convolution
+    """``small``: three launches each (one warm-up, two timed) of the memory-bound kernels and of the 3x3 convolution
     (im2col gather + tcgen05 GEMM, forward and both gradients) on cases a few hundred MB in
     size: larger than L2, small enough for a counter capture of single launches."""
     from necklace_b200.ops import adam_step, cross_entropy_fwd_bwd
@@ -162,8 +162,8 @@ def bench_small(flush):
     w = torch.ones(C, device="cuda").bfloat16()
     b = torch.zeros(C, device="cuda").bfloat16()
     y, st = norm_fwd(x, w, b, 1e-5, False)
-    ms = _time(lambda: norm_fwd(x, w, b, 1e-5, False), iters=3, warmup=1, flush=flush)
-    ms_b = _time(lambda: norm_bwd(x, x, w, st, False), iters=3, warmup=1, flush=flush)
+    ms = _time(lambda: norm_fwd(x, w, b, 1e-5, False), iters=2, warmup=1, flush=flush)
+    ms_b = _time(lambda: norm_bwd(x, x, w, st, False), iters=2, warmup=1, flush=flush)
     byts = rows * C * 2
     print(json.dumps({"op": "layernorm_fwd", "rows": rows, "C": C, "ms": round(ms, 4),
                       "GBps": round(2 * byts / ms / 1e6)}))
@@ -172,7 +172,7 @@ def bench_small(flush):
     T, V, ld = 2048, 50257, 50304
     lg = torch.randn(T, ld, device="cuda").bfloat16()
     tg = torch.randint(0, V, (T,), device="cuda")
-    ms = _time(lambda: cross_entropy_fwd_bwd(lg, tg, V, 1.0 / T), iters=3, warmup=1, flush=flush)
+    ms = _time(lambda: cross_entropy_fwd_bwd(lg, tg, V, 1.0 / T), iters=2, warmup=1, flush=flush)
     print(json.dumps({"op": "ce_fwd_bwd", "T": T, "V": V, "ms": round(ms, 4),
                       "GBps": round(2 * T * ld * 2 / ms / 1e6)}), flush=True)
     n = 32 * 1024 * 1024
@@ -180,7 +180,7 @@ def bench_small(flush):
     m, v = torch.zeros_like(master), torch.zeros_like(master)
     g = torch.randn(n, device="cuda").bfloat16()
     pb = torch.empty(n, device="cuda", dtype=torch.bfloat16)
-    ms = _time(lambda: adam_step(master, m, v, g, pb, lr=1e-4, step=2), iters=3, warmup=1,
+    ms = _time(lambda: adam_step(master, m, v, g, pb, lr=1e-4, step=2), iters=2, warmup=1,
                flush=flush)
     print(json.dumps({"op": "adam_flat", "n": n, "ms": round(ms, 4),
                       "GBps": round(n * (12 * 2 + 2 + 2) / ms / 1e6)}), flush=True)
@@ -194,7 +194,7 @@ def bench_small(flush):
         xi.grad = None
         conv.weight.grad = None
         conv(xi).backward(dy)
-    ms = _time(fb, iters=3, warmup=1, flush=flush)
+    ms = _time(fb, iters=2, warmup=1, flush=flush)
     fl = 3 * 2.0 * N * H * H * Cc * Cc * 9
     print(json.dumps({"op": "conv3x3 fwd+bwd", "N": N, "HW": H, "C": Cc, "ms": round(ms, 4),
                       "tflops": round(fl / ms / 1e9, 1)}), flush=True)

@@ -300,7 +300,8 @@ def case_llama_tp_fused(rank, world, heap, grp, chk):
     from necklace_b200 import checkpoint as ck
     from necklace_b200.models.llama import Llama, LlamaConfig
     for hd, seq in ((64, 128), (128, 256)):
-        kw = dict(n_layer=2, d_model=4 * hd, n_head=4, d_ff=1024, vocab=1000, max_seq=seq)
+        nh = max(4, world)                   # every rank needs at least one head
+        kw = dict(n_layer=2, d_model=nh * hd, n_head=nh, d_ff=1024, vocab=1000, max_seq=seq)
         tp = Llama(LlamaConfig(tp_group=grp, **kw), device="cuda")
         ref = Llama(LlamaConfig(**kw), device="cuda")
         nb = max(2, world * 128 // seq)      # the fused kernels want 128-row blocks per rank
