@@ -25,3 +25,13 @@ def debug(i, *args, **kwargs) -> None:
     if i in IL:
         print(f"[{time.strftime('%H:%M:%S')}][{i}]", *args, **kwargs)
         sys.stdout.flush()
+
+
+def debug_any(ids, *args, **kwargs) -> None:
+    """One line if any of the channels ``ids`` is enabled (a message that several
+    differently numbered channels of the reference's service flavours would carry)."""
+    for i in ids:
+        if i in IL:
+            print(f"[{time.strftime('%H:%M:%S')}][{i}]", *args, **kwargs)
+            sys.stdout.flush()
+            return

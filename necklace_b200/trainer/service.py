@@ -32,10 +32,26 @@ import traceback
 
 from ..rpc import ilog, svctmp, zrpc
 
-# log channels (reference: tndspp.py / tndszd.py ILOG_I_* constants)
+# Log channels.  The reference numbers four channels per service flavour (worker / scheduler,
+# RPC server "SVR" / state machine "SVC"; tndsmp.py:14-17, tndspp.py:14-21, tndszr.py:14-26) and
+# user scripts switch them on with ``ilog.il_add(tndszd.ILOG_I_ZR_SVR_WKR)``.  One service
+# serves all flavours here, so a message goes out if any flavour's channel of its kind is on;
+# the flavour modules (tndsmp, tndspp, tndszr, tndszd) export the reference's names and numbers.
 ILOG_I_SVC_WORKER, ILOG_I_SVC_SCHEDULER = 500001, 500002
 ILOG_I_MP_WORKER, ILOG_I_MP_SCHEDULER = 600001, 600002
 ILOG_I_ZR_WORKER, ILOG_I_ZR_SCHEDULER = 800001, 800002
+ILOG_CHANNELS = {
+    "svr_wkr": (600001, 600011, 800001),            # worker: RPC endpoints
+    "svc_wkr": (500001, 600002, 600012, 800002),    # worker: state machine
+    "svr_sch": (600003, 600021, 800003),            # scheduler: RPC endpoints
+    "svc_sch": (500002, 600004, 600022, 800004),    # scheduler: state machine / phases
+    "prt_wkr": (600015, 600016),                    # verbose (pipeline flavour)
+    "prt_sch": (600025, 600026),
+}
+
+
+def _dbg(kind, *args):
+    ilog.debug_any(ILOG_CHANNELS[kind], *args)
 
 # command endpoint on the worker -> callback endpoint on the scheduler
 PHASES = {
@@ -118,6 +134,7 @@ class SVRWorker(svctmp.TmplServer):
 
     def _phase_endpoint(self, fn, msg):
         m = self.msg_unpck(msg)
+        _dbg("svr_wkr", f"worker {self.rank}: <- {fn}")
         self.q_put_state(Q_STATE_CMD, fn, m.get("msg") or {})
         return self.msg_pck(self.mk_rpc_ret(fn, "ok"))
 
@@ -186,7 +203,7 @@ class SVCWorker(svctmp.TmplService):
             elif state == Q_STATE_CMD:
                 self.do_cmd(*a)
             elif state == Q_STATE_STOP:
-                ilog.debug(ILOG_I_SVC_WORKER, f"worker {self.rank}: stop")
+                _dbg("svc_wkr", f"worker {self.rank}: stop")
                 self.svr.trnr.clear()
                 self.exit_status = "stopped"
                 self.stop()
@@ -223,6 +240,8 @@ class SVCWorker(svctmp.TmplService):
 
     def do_cmd(self, fn, msg):
         svr = self.svr
+        _dbg("svc_wkr", f"worker {self.rank}: do {fn}")
+        _dbg("prt_wkr", f"worker {self.rank}: {fn} msg keys {sorted(msg) if isinstance(msg, dict) else msg}")
         if fn == "fn_init_nccl_comm":
             svr.trnr.init_nccl_comm(msg)
             ret = {"ret": "nccl_comm_inited"}
@@ -265,6 +284,7 @@ class SVRScheduler(svctmp.TmplServer):
 
     def _ack(self, fn, msg):
         m = self.msg_unpck(msg)
+        _dbg("svr_sch", f"scheduler: <- {fn} from worker {m.get('rank')}")
         self.q_put_state(Q_STATE_RET, fn, m["rank"], m["msg"])
         return self.msg_pck(self.mk_rpc_ret(fn, "ok"))
 
@@ -328,6 +348,8 @@ class SVCScheduler(svctmp.TmplService):
 
     def start_phase(self, ph: Phase):
         self.phase, self.phase_started = ph, time.time()
+        _dbg("svc_sch", f"scheduler: phase {ph.fn} -> workers {list(ph.ranks)}")
+        _dbg("prt_sch", f"scheduler: phase {ph.fn} msg keys {sorted(ph.msg)}")
         for r in ph.ranks:
             rep = self.send(r, ph.fn, **{**ph.msg, **ph.per_rank.get(r, {})})
             if rep.get("ret") != "ok":
@@ -379,7 +401,7 @@ class SVCScheduler(svctmp.TmplService):
 
     def on_worker_reg(self, rank, url):
         self.worker_urls[rank] = url
-        ilog.debug(ILOG_I_SVC_SCHEDULER, f"scheduler: worker {rank} registered at {url}")
+        _dbg("svc_sch", f"scheduler: worker {rank} registered at {url}")
         if len(self.worker_urls) == self.workers_n and self.program is None:
             for r, u in self.worker_urls.items():
                 self.worker_clis[r] = self.svr.mk_rpc_cli(

@@ -4,3 +4,9 @@ from .service import *  # noqa: F401,F403
 from .service import (MPSVCScheduler, MPSVCWorker, MPSVRScheduler, MPSVRWorker,  # noqa: F401
                       ILOG_I_MP_SCHEDULER, ILOG_I_MP_WORKER, ILOG_I_ZR_SCHEDULER,
                       ILOG_I_ZR_WORKER)
+
+# the reference's log channel numbers of this flavour (necklace/trainer/tndsmp.py:14-26)
+ILOG_I_MP_SVR_WKR = 600001
+ILOG_I_MP_SVC_WKR = 600002
+ILOG_I_MP_SVR_SCH = 600003
+ILOG_I_MP_SVC_SCH = 600004

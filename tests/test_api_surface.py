@@ -1,0 +1,104 @@
+"""The names a user script of the reference imports exist here under ``necklace_b200`` with the
+same spelling (reference: necklace/__init__.py, necklace/trainer/*.py, necklace/cuda/ncclgrp.py,
+necklace/frmwrk/pytorch/mpnn/__init__.py:8-27, examples/*), and the log-channel numbers that
+scripts pass to ``ilog.il_add`` are the reference's."""
+import importlib
+
+import pytest
+
+SURFACE = {
+    "": ["init"],
+    "utils.argutils": ["attach_nk_args_parser", "args_remake"],
+    "utils.hookbase": ["NklcHookBase"],
+    "utils.wrpbase": ["NklcWrapperBase"],
+    "utils.tmrit": ["TimerItLogger"],
+    "rpc.ilog": ["il_add", "il_del", "debug"],
+    "rpc.svctmp": ["TmplServer", "TmplService", "TmplClient"],
+    "cuda.ncclgrp": ["init_nccl_groups_map", "get_nccl_groups_map_cfg_dict",
+                     "get_nccl_groups_map_grp_dict", "get_nccl_group_main_grp_list",
+                     "get_nccl_group_dp", "get_nccl_group_mp", "get_nccl_group_pp",
+                     "get_nccl_group_zr", "get_nccl_group_dp_or_main", "get_nccl_group_mp_or_main",
+                     "get_nccl_group_pp_or_main", "get_nccl_group_zr_or_main", "get_rank",
+                     "get_world_size"],
+    "cuda.ncclfns": [], "cuda.ncclwrp": ["PYNCCL_DTYPE_MAP"], "cuda.quantize": [],
+    "trainer.tndsnc": ["SVCScheduler", "SVCWorker"],
+    "trainer.tndsms": ["SVCScheduler", "SVCWorker"],
+    "trainer.tndsmp": ["MPSVCScheduler", "MPSVCWorker"],
+    "trainer.tndspp": ["MPSVCScheduler", "MPSVCWorker"],
+    "trainer.tndszr": ["MPSVCScheduler", "MPSVCWorker"],
+    "trainer.tndszd": ["MPSVCScheduler", "MPSVCWorker"],
+    "trainer.tnoppt": ["TrainerOPPytorch"],
+    "trainer.mpoppt": ["TrainerMPOPPytorch"], "trainer.ppoppt": ["TrainerMPOPPytorch"],
+    "trainer.zroppt": ["TrainerMPOPPytorch"], "trainer.zroppf": ["TrainerMPOPPytorch"],
+    "trainer.zroppd": ["TrainerMPOPPytorch"], "trainer.tnmode": [],
+    "frmwrk.pytorch.mpnn": [
+        "destroy_model_parallel", "get_data_parallel_group", "get_data_parallel_rank",
+        "get_data_parallel_world_size", "get_model_parallel_group", "get_model_parallel_rank",
+        "get_model_parallel_src_rank", "get_model_parallel_world_size",
+        "initialize_model_parallel", "model_parallel_is_initialized", "ColumnParallelLinear",
+        "ParallelEmbedding", "RowParallelLinear", "VocabParallelEmbedding",
+        "copy_to_model_parallel_region", "gather_from_model_parallel_region",
+        "reduce_from_model_parallel_region", "scatter_to_model_parallel_region"],
+    "frmwrk.pytorch.mpnn.checkpointing": ["checkpoint", "get_cuda_rng_tracker",
+                                          "model_parallel_cuda_manual_seed"],
+    "frmwrk.pytorch.mpnn.samplers": [], "frmwrk.pytorch.mpnn.utils": [],
+    "frmwrk.pytorch.ptutils": ["prnt_md"],
+    "frmwrk.pytorch.dataldr": ["get_dist_dataloader"],
+    "frmwrk.pytorch.callback": ["save_checkpoint"],
+    "data.dtdummy": ["DtstDummy", "DtldDummy"],
+    "data.dtqpto": ["DataLoaderSharedMemory"], "data.dtqptp": ["DataLoaderSharedMemory"],
+    "data.dtmptp": ["DataLoaderSharedMemory"], "data.dtmptv": ["DataLoaderSharedMemory"],
+    "data.sampler": [], "data.batchify": [], "data.shmem": [], "data.dtmem": [], "data.dtshm": [],
+    "data.dtshmp": [], "data.shmpt": [], "data.dtdist": [], "data.dtset": [], "data.dtwrp": [],
+    "data.dtldngn": [],
+}
+
+CHANNELS = {
+    "tndsmp": {"ILOG_I_MP_SVR_WKR": 600001, "ILOG_I_MP_SVC_WKR": 600002,
+               "ILOG_I_MP_SVR_SCH": 600003, "ILOG_I_MP_SVC_SCH": 600004},
+    "tndspp": {"ILOG_I_MP_SVR_WKR": 600011, "ILOG_I_MP_SVR_WKR_PRT": 600015,
+               "ILOG_I_MP_SVC_WKR": 600012, "ILOG_I_MP_SVC_WKR_PRT": 600016,
+               "ILOG_I_MP_SVR_SCH": 600021, "ILOG_I_MP_SVR_SCH_PRT": 600025,
+               "ILOG_I_MP_SVC_SCH": 600022, "ILOG_I_MP_SVC_SCH_PRT": 600026},
+    "tndszr": {"ILOG_I_MP_SVR_WKR": 600001, "ILOG_I_ZR_SVR_WKR": 800001,
+               "ILOG_I_ZR_SVC_WKR": 800002, "ILOG_I_ZR_SVR_SCH": 800003,
+               "ILOG_I_ZR_SVC_SCH": 800004},
+    "tndszd": {"ILOG_I_MP_SVC_SCH": 600004, "ILOG_I_ZR_SVR_WKR": 800001,
+               "ILOG_I_ZR_SVC_WKR": 800002, "ILOG_I_ZR_SVR_SCH": 800003,
+               "ILOG_I_ZR_SVC_SCH": 800004},
+}
+
+
+@pytest.mark.parametrize("mod", sorted(SURFACE))
+def test_module_and_names_exist(mod):
+    m = importlib.import_module("necklace_b200" + ("." + mod if mod else ""))
+    missing = [n for n in SURFACE[mod] if not hasattr(m, n)]
+    assert not missing, (mod, missing)
+
+
+def test_trainer_hook_registration_and_attributes():
+    from necklace_b200.trainer.tnoppt import TrainerOPPytorch
+    from necklace_b200.trainer.zroppt import TrainerMPOPPytorch
+    for when in ("before", "after"):
+        for what in ("train", "epoch", "data_batch", "batch", "do_a_batch_grads",
+                     "do_a_train_step"):
+            assert hasattr(TrainerOPPytorch, f"register_hook_{when}_{what}")
+    assert hasattr(TrainerMPOPPytorch, "get_whole_net_cpu")
+
+
+def test_log_channels_have_the_reference_numbers_and_switch_service_lines_on(capsys):
+    from necklace_b200.rpc import ilog
+    from necklace_b200.trainer import service
+    for mod, names in CHANNELS.items():
+        m = importlib.import_module("necklace_b200.trainer." + mod)
+        for name, val in names.items():
+            assert getattr(m, name) == val, (mod, name)
+    service._dbg("svr_wkr", "hidden")
+    assert capsys.readouterr().out == ""
+    from necklace_b200.trainer import tndszd
+    ilog.il_add(tndszd.ILOG_I_ZR_SVR_WKR)
+    try:
+        service._dbg("svr_wkr", "shown")
+        assert "shown" in capsys.readouterr().out
+    finally:
+        ilog.il_del(tndszd.ILOG_I_ZR_SVR_WKR)
