@@ -4,8 +4,9 @@ Call shapes follow the reference (necklace/cuda/ncclfns.py:32-260): a rank that
 is not a member of ``group`` returns at once, the default reduction is a sum, and
 ``group=None`` means the main group.  Differences: every call is ordered on the
 caller's current stream (the reference launches on pynccl's own stream and blocks
-on it), tensors living in the symmetric heap take the native peer-memory kernels,
-everything else goes through ``torch.distributed`` on the group's process group.
+on it), tensors living in the symmetric heap take the native peer-memory kernels
+(all-reduce, all-gather, broadcast, reduce-scatter), everything else goes through
+``torch.distributed`` on the group's process group.
 """
 from __future__ import annotations
 
@@ -68,6 +69,15 @@ def all_gather(out: torch.Tensor, t: torch.Tensor, group=None) -> torch.Tensor:
     if _world(group) == 1:
         out.view(-1).copy_(t.reshape(-1))
         return out
+    peer = _peer(group, out)
+    W = _world(group)
+    if peer is not None and out.is_contiguous() and out.numel() == W * t.numel() \
+            and (out.numel() * out.element_size()) % (16 * W) == 0:
+        mine = out.view(-1)[group.rank * t.numel():(group.rank + 1) * t.numel()]
+        if mine.data_ptr() != t.data_ptr():
+            mine.copy_(t.reshape(-1))
+        peer.all_gather(out)          # every member pushes its slice to the others
+        return out
     dist.all_gather_into_tensor(out.view(-1), t.contiguous().view(-1), group=_pg(group))
     return out
 
@@ -76,6 +86,10 @@ def broadcast(t: torch.Tensor, root: int = 0, group=None) -> torch.Tensor:
     """``root`` is the rank inside the group."""
     group = _resolve(group)
     if not _is_member(group) or _world(group) == 1:
+        return t
+    peer = _peer(group, t)
+    if peer is not None and t.is_contiguous() and (t.numel() * t.element_size()) % 16 == 0:
+        peer.broadcast(t, root)       # the root pushes to every member's copy
         return t
     dist.broadcast(t, src=group.pg_ranks[root], group=_pg(group))
     return t
@@ -95,6 +109,13 @@ def reduce_scatter(out: torch.Tensor, t: torch.Tensor, op: str = "sum", group=No
         return out
     if _world(group) == 1:
         out.view(-1).copy_(t.reshape(-1))
+        return out
+    peer = _peer(group, t)
+    W = _world(group)
+    if peer is not None and op == "sum" and t.dtype in (torch.float32, torch.bfloat16) \
+            and out.dtype == t.dtype and t.is_contiguous() and out.is_contiguous() \
+            and t.numel() % (256 * W) == 0 and out.numel() * W == t.numel():
+        peer.reduce_scatter(t.view(-1), out.view(-1))
         return out
     dist.reduce_scatter_tensor(out.view(-1), t.contiguous().view(-1), op=_OPS[op],
                                group=_pg(group))

@@ -21,6 +21,15 @@ SURFACE = {
                      "get_nccl_group_pp_or_main", "get_nccl_group_zr_or_main", "get_rank",
                      "get_world_size"],
     "cuda.ncclfns": [], "cuda.ncclwrp": ["PYNCCL_DTYPE_MAP"], "cuda.quantize": [],
+    "cuda.nbutils": ["cuda_select_device", "cuda_current_context", "cuda_stream", "cuda_to_device",
+                     "cuda_devarr_c_void_p"],
+    "cuda.ncclutils": ["tensor_data_ptr", "tensor_size", "tensor_dtype", "nccl_all_reduce",
+                       "nccl_all_gather", "nccl_reduce", "nccl_bcast", "nccl_reduce_scatter",
+                       "seg_cb_nccl_ar", "nccl_out_all_gather"],
+    "cuda.ncclpgs": ["NcclProcessGroup", "init_nccl_groups_map", "get_nccl_group_dp",
+                     "get_nccl_group_mp", "get_nccl_group_dp_or_main", "get_nccl_group_mp_or_main",
+                     "get_nccl_groups_map_cfg_dict", "get_nccl_groups_map_grp_dict", "get_rank",
+                     "get_world_size", "ensure_divisibility", "divide", "build_pg_cfg"],
     "trainer.tndsnc": ["SVCScheduler", "SVCWorker"],
     "trainer.tndsms": ["SVCScheduler", "SVCWorker"],
     "trainer.tndsmp": ["MPSVCScheduler", "MPSVCWorker"],
@@ -50,7 +59,16 @@ SURFACE = {
     "data.dtmptp": ["DataLoaderSharedMemory"], "data.dtmptv": ["DataLoaderSharedMemory"],
     "data.sampler": [], "data.batchify": [], "data.shmem": [], "data.dtmem": [], "data.dtshm": [],
     "data.dtshmp": [], "data.shmpt": [], "data.dtdist": [], "data.dtset": [], "data.dtwrp": [],
-    "data.dtldngn": [],
+    "data.dtldngn": [], "data.shmmx": ["SharedMemArray"], "data.dtmmx": ["DataLoaderSharedMemory"],
+    "data.dtmmxp": ["DataLoaderSharedMemory"], "data.dtexchg": ["DataExchanger"],
+    "data.ptdlspn": [], "frmwrk.mxnet": [], "trainer.tnopmx": ["TrainerOPGluon"],
+    "frmwrk.pytorch.ptmpi": ["params_do_mpi_allreduce", "opt_grads_do_mpi_allreduce",
+                             "init_params_recvs", "init_opt_grads_recvs", "nccl_nc_allreduce",
+                             "nccl_pg_allreduce", "nccl_pg_broadcast", "nccl_pg_reduce",
+                             "opt_grads_do_nccl_allreduce", "opt_one_grads_do_nccl_allreduce",
+                             "nccl_allreduce_by_buckets"],
+    "frmwrk.pytorch.dtwrp": ["DataLoaderWrp", "DataLoaderIterWrp"],
+    "frmwrk.pytorch.ptacts": [],
 }
 
 CHANNELS = {
@@ -102,3 +120,44 @@ def test_log_channels_have_the_reference_numbers_and_switch_service_lines_on(cap
         assert "shown" in capsys.readouterr().out
     finally:
         ilog.il_del(tndszd.ILOG_I_ZR_SVR_WKR)
+
+
+def test_two_way_group_map_has_the_reference_layout():
+    """8 ranks, model parallel 2: mp groups are adjacent pairs, dp groups stride over them
+    (reference: necklace/cuda/ncclpgs.py:189-258)."""
+    from necklace_b200.comm import groups as G
+    from necklace_b200.cuda import ncclpgs
+    G.reset_nccl_groups_map()
+    try:
+        ncclpgs.init_nccl_groups_map(8, 5, 2, 4, True)
+        grp = ncclpgs.get_nccl_groups_map_grp_dict()
+        assert grp["mp_group"] == [[0, 1], [2, 3], [4, 5], [6, 7]]
+        assert grp["dp_group"] == [[0, 2, 4, 6], [1, 3, 5, 7]]
+        assert ncclpgs.get_nccl_group_dp().pg_ranks == [1, 3, 5, 7]
+        assert ncclpgs.get_nccl_group_mp().pg_ranks == [4, 5]
+    finally:
+        G.reset_nccl_groups_map()
+
+
+def test_array_level_helpers_on_a_single_rank_group():
+    import ctypes
+
+    import numpy as np
+    import torch
+
+    from necklace_b200.comm.symm import TorchGroup
+    from necklace_b200.cuda import nbutils, ncclutils
+    nc = TorchGroup()
+    a = torch.arange(8, dtype=torch.float32)
+    assert ncclutils.nccl_all_reduce(a, nc, 1) is a
+    outs = torch.zeros(8)
+    ncclutils.nccl_all_gather(a, outs, nc, 1)
+    assert torch.equal(outs, a)
+    assert ncclutils.nccl_all_reduce(None, nc, 1) is None
+    assert ncclutils.tensor_size(np.ones((2, 3))) == 6
+    assert ncclutils.tensor_dtype(np.ones(2, dtype=np.float16)) == torch.float16
+    assert ncclutils.tensor_data_ptr(a) == a.data_ptr()
+    assert ncclutils.tensor_data_ptr(np.ones(2)) != 0
+    d = nbutils.cuda_to_device(np.ones(3, dtype=np.float32))
+    assert isinstance(nbutils.cuda_devarr_c_void_p(d), ctypes.c_void_p)
+    assert nbutils.cuda_current_context().type in ("cpu", "cuda")

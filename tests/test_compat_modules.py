@@ -1,0 +1,97 @@
+"""The small modules kept for scripts written against the reference's tree: the numpy
+shared-memory array (necklace/data/shmmx.py), the host-buffer averaging helpers
+(necklace/frmwrk/pytorch/ptmpi.py:107-174) on two gloo ranks, the data exchanger stub and the
+Gluon operator placeholder."""
+import os
+import pickle
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _attach_and_write(sk, q):
+    from necklace_b200.data.shmmx import SharedMemArray
+    a = SharedMemArray.create_from_shmem_key(sk)
+    a[2] = np.full(3, 7.0, dtype=np.float32)
+    q.put(a[1].tolist())
+    a.unlink()
+
+
+def test_shared_array_is_visible_across_processes():
+    import multiprocessing as mp
+    from necklace_b200.data.shmmx import SharedMemArray
+    a = SharedMemArray(obj_shape=(4, 3), dtype=np.float32)
+    try:
+        a[1] = np.arange(3, dtype=np.float32)
+        ctx = mp.get_context("spawn")
+        q = ctx.Queue()
+        p = ctx.Process(target=_attach_and_write, args=(pickle.loads(pickle.dumps(a.sk)), q))
+        p.start()
+        assert q.get(timeout=60) == [0.0, 1.0, 2.0]
+        p.join(60)
+        assert a[2].tolist() == [7.0, 7.0, 7.0]
+        view = SharedMemArray.ndarray_from_shmem_key(a.sk)
+        assert view.shape == (4, 3) and view[2, 0] == 7.0
+    finally:
+        a.unlink()
+    with pytest.raises(Exception):
+        SharedMemArray.create_from_shmem_key(None)
+
+
+def _avg_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    from necklace_b200.comm import backend
+    from necklace_b200.frmwrk.pytorch import ptmpi
+    backend.init_backend("dp", {"world_size": world, "my_rank": rank, "dp_size": world},
+                         comm_type="gloo", master_port=port)
+    torch.manual_seed(rank)
+    net = torch.nn.Linear(3, 2)
+    opt = torch.optim.SGD(net.parameters(), lr=0.1)
+    net(torch.ones(1, 3) * (rank + 1)).sum().backward()
+    before = (net.weight.detach().clone().numpy(), net.weight.grad.clone().numpy())
+    ptmpi.params_do_mpi_allreduce(None, world, net, ptmpi.init_params_recvs(net))
+    ptmpi.opt_grads_do_mpi_allreduce(None, world, opt)
+    q.put((rank, before, net.weight.detach().numpy().copy(), net.weight.grad.numpy().copy()))
+    backend.shutdown_backend()
+
+
+@pytest.mark.timeout(300)
+def test_host_buffer_averaging_on_two_gloo_ranks():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q, port = ctx.Queue(), _free_port()
+    procs = [ctx.Process(target=_avg_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = sorted((q.get(timeout=240) for _ in procs), key=lambda r: r[0])
+    for p in procs:
+        p.join(60)
+    w_mean = (res[0][1][0] + res[1][1][0]) / 2
+    g_mean = (res[0][1][1] + res[1][1][1]) / 2
+    for _, _, w, g in res:
+        assert np.allclose(w, w_mean, atol=1e-6) and np.allclose(g, g_mean, atol=1e-6)
+
+
+def test_exchanger_dataloader_wrapper_and_gluon_placeholder():
+    from necklace_b200.data.dtexchg import DataExchanger
+    from necklace_b200.data.ptdlspn import spawn_dataloader
+    from necklace_b200.frmwrk.pytorch.dtwrp import DataLoaderIterWrp, DataLoaderWrp
+    from necklace_b200.trainer.tnopmx import TrainerOPGluon
+    assert DataExchanger().exchange(1) is None
+    assert DataExchanger(exchange_fn=lambda a, b=0: a + b).exchange(2, b=3) == 5
+    ds = torch.utils.data.TensorDataset(torch.arange(10.0))
+    assert sum(len(b[0]) for b in DataLoaderIterWrp(DataLoaderWrp(ds, batch_size=4))) == 10
+    assert len(list(spawn_dataloader(ds, batch_size=5))) == 2
+    try:
+        import mxnet  # noqa: F401
+    except ImportError:
+        with pytest.raises(RuntimeError):
+            TrainerOPGluon({})
