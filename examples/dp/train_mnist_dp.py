@@ -7,8 +7,9 @@ Start one scheduler and N workers from this same script, as with the reference
     python train_mnist_dp.py -r worker -w 2 -k 0 -u ipc:///tmp/nk-w0.ipc -s ipc:///tmp/nk-svr.ipc -t dp
     python train_mnist_dp.py -r worker -w 2 -k 1 -u ipc:///tmp/nk-w1.ipc -s ipc:///tmp/nk-svr.ipc -t dp
 
-Data is synthetic (uniform [0,1) images, uniform labels) unless ``--data-dir`` points at
-torchvision MNIST files.  ``--no-cuda`` keeps everything on the CPU (gloo collectives).
+``--loader shm|queue|obj`` feeds the workers from loader processes through shared memory
+(the reference's train_ngn_mnist_2_dtpt.py; loaders in dtloader.py).  Data is synthetic (uniform
+[0,1) images, uniform labels) unless ``--data-dir`` points at torchvision MNIST files.  ``--no-cuda`` keeps everything on the CPU (gloo collectives).
 """
 from __future__ import annotations
 
@@ -18,6 +19,7 @@ import os
 import sys
 
 sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", ".."))
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 import torch
 import torch.nn as nn
@@ -79,6 +81,9 @@ def main():
                     help="drive every phase of every step by RPC (the reference protocol)")
     ap.add_argument("--grad-comp-threshold", type=float, default=0.0)
     ap.add_argument("--out", type=str, default="")
+    ap.add_argument("--loader", default="ngn", choices=["ngn", "queue", "shm", "obj"],
+                    help="see dtloader.py (shm = the reference's train_ngn_mnist_2_dtpt.py)")
+    ap.add_argument("--loader-workers", type=int, default=2)
     args = ap.parse_args()
 
     tmode = args.tmode or ("dp" if args.world_size > 1 else "no")
@@ -103,11 +108,9 @@ def main():
     opt = torch.optim.SGD(net.parameters(), lr=args.lr, momentum=args.momentum)
 
     def dataloader_creator(rank, world):
+        from dtloader import make_loader
         ds = SyntheticDataset(args.dataset_len, (1, 28, 28), classes=10, seed=args.seed)
-        per = len(ds) // world
-        sampler = SliceSampler(indices=list(range(rank * per, (rank + 1) * per)))
-        return DataLoaderNgnBase(ds, batch_size=args.batch_size, sampler=sampler,
-                                 last_batch="discard")
+        return make_loader(args.loader, ds, args.batch_size, rank, world, args.loader_workers)
 
     trainer_cfg = {
         "kn": args.world_size, "ti": args.rank, "ctx": ctx, "net": net, "opt": opt,

@@ -64,7 +64,11 @@ def build_parts(n_parts, use_mp, seed):
     return parts
 
 
-def main():
+def main(build=None, in_shape=(784,)):
+    """``build(n_parts, use_mp, seed)`` returns the ``net_map`` units (default: the MLP of this
+    file) for inputs of shape ``in_shape``; other examples reuse this driver with their own
+    network (examples/pp/train_mnist_pp.py, examples/mp/train_mnist_mpnn.py)."""
+    build = build or build_parts
     ap = argparse.ArgumentParser()
     attach_nk_args_parser(ap)
     ap.add_argument("--batch-size", "-b", type=int, default=32)
@@ -106,7 +110,7 @@ def main():
     use_cuda = torch.cuda.is_available() and not args.no_cuda
     necklace_b200.init(args.gpu_rank)
     ctx = torch.device("cuda", int(args.gpu_rank)) if use_cuda else torch.device("cpu")
-    parts = build_parts(n_parts, "mp" in kinds, args.seed)
+    parts = build(n_parts, "mp" in kinds, args.seed)
     net_map = OrderedDict((i, {"net": p, "net_map_order": i}) for i, p in enumerate(parts))
 
     # which data replica am I?  ranks that differ only in pp / mp coordinates share data
@@ -118,7 +122,7 @@ def main():
     mp_rank = coord("mp")
 
     def dataloader_creator():
-        ds = SyntheticDataset(args.dataset_len, (784,), classes=10, seed=args.seed)
+        ds = SyntheticDataset(args.dataset_len, tuple(in_shape), classes=10, seed=args.seed)
         per = len(ds) // n_replica
         if "mp" in kinds and mp_rank != 0:
             return DtldDummy(DtstDummy(per), args.batch_size)
@@ -130,7 +134,8 @@ def main():
         "kn": args.world_size, "ti": args.rank, "ctx": ctx, "loss": nn.CrossEntropyLoss(),
         "batch_size": args.batch_size, "epochs": args.epochs, "dataset_len": args.dataset_len,
         "dataloader_type": "mpdp" if "mp" in kinds else "dp",
-        "dataloader_data_shape_dims": [2, 1], "dataloader_creator": dataloader_creator,
+        "dataloader_data_shape_dims": [len(in_shape) + 1, 1],
+        "dataloader_creator": dataloader_creator,
         "log_interval": 0, "tmode": tmode, "pg_cfg": pg_cfg,
         "comm_type": "gloo" if not use_cuda else args.comm_type,
         "net_map": net_map, "net_map_maxlen": n_parts, "micro_batches": args.micro_batches,
