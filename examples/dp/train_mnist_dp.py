@@ -81,6 +81,8 @@ def main():
                     help="drive every phase of every step by RPC (the reference protocol)")
     ap.add_argument("--grad-comp-threshold", type=float, default=0.0)
     ap.add_argument("--out", type=str, default="")
+    ap.add_argument("--model", default="lenet", choices=["lenet", "mixer"],
+                    help="mixer: MLP-Mixer (the reference's train_nklc_nccl_mnist_3_mlpmx.py)")
     ap.add_argument("--loader", default="ngn", choices=["ngn", "queue", "shm", "obj"],
                     help="see dtloader.py (shm = the reference's train_ngn_mnist_2_dtpt.py)")
     ap.add_argument("--loader-workers", type=int, default=2)
@@ -104,7 +106,11 @@ def main():
     necklace_b200.init(args.gpu_rank)
     ctx = torch.device("cuda", int(args.gpu_rank)) if use_cuda else torch.device("cpu")
     torch.manual_seed(args.seed)
-    net = LeNet()
+    if args.model == "mixer":
+        from necklace_b200.models.mlp_mixer import MLPMixer
+        net = MLPMixer(n_parts=2, seed=args.seed)
+    else:
+        net = LeNet()
     opt = torch.optim.SGD(net.parameters(), lr=args.lr, momentum=args.momentum)
 
     def dataloader_creator(rank, world):

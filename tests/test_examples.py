@@ -150,3 +150,22 @@ def test_dp_example_fed_from_shared_memory_loaders(tmp_path, loader):
         sums[kind] = [json.load(open(d / f"o{r}.json"))["weights_sum"] for r in range(2)]
         assert abs(sums[kind][0] - sums[kind][1]) < 1e-9
     assert abs(sums["ngn"][0] - sums[loader][0]) < 1e-6
+
+
+@pytest.mark.timeout(300)
+def test_dp_example_with_the_mixer_model(tmp_path):
+    script = os.path.join(ROOT, "examples", "dp", "train_mnist_dp.py")
+    svr = f"ipc://{tmp_path}/s.ipc"
+    procs = [subprocess.Popen([sys.executable, script, "-r", "scheduler", "-w", "2", "-u", svr,
+                               "-e", "1"], stdout=open(tmp_path / "s.log", "w"),
+                              stderr=subprocess.STDOUT, cwd=ROOT)]
+    for r in range(2):
+        procs.append(subprocess.Popen(
+            [sys.executable, script, "-r", "worker", "-w", "2", "-k", str(r), "-u",
+             f"ipc://{tmp_path}/w{r}.ipc", "-s", svr, "-t", "dp", "--no-cuda", "--dataset-len",
+             "200", "-b", "20", "--model", "mixer", "--out", str(tmp_path / f"o{r}.json")],
+            stdout=open(tmp_path / f"w{r}.log", "w"), stderr=subprocess.STDOUT, cwd=ROOT))
+    assert _wait(procs, 200) == [0, 0, 0], open(tmp_path / "w0.log").read()[-2000:]
+    outs = [json.load(open(tmp_path / f"o{r}.json")) for r in range(2)]
+    assert abs(outs[0]["weights_sum"] - outs[1]["weights_sum"]) < 1e-9
+    assert 0 < outs[0]["epoch_loss"][-1] < 10
