@@ -146,3 +146,31 @@ def test_absent_rank_gives_timeout_status_not_a_hang():
         TIMEOUT = old
     assert status[0] == 5 and status[2] == 5
     assert sh.errors == []
+
+
+def test_accuracy_of_bf16_staged_partial_sums_at_mp4_k13824():
+    """GEMM -> reduce-scatter stores the partial sums of the other ranks' rows as bf16 and
+    keeps the own partial sum in fp32.  Emulated on the CPU for the widest case asked for
+    (4 ranks, K = 13824 split four ways, bf16 operands): the root-mean-square error is less
+    than twice that of rounding the exact sum once to bf16, and every element is within
+    2^-8 * (sum of the |staged partial sums| + |result|) of the exact sum."""
+    import torch
+    torch.manual_seed(0)
+    W, K, M, N = 4, 13824, 64, 96
+    x = (torch.randn(M, K) * 0.5).bfloat16().double()
+    w = (torch.randn(N, K) * 0.02).bfloat16().double()
+    kp = K // W
+    parts = [x[:, r * kp:(r + 1) * kp] @ w[:, r * kp:(r + 1) * kp].t() for r in range(W)]
+    exact = sum(parts)
+    once = exact.float().bfloat16().double()                     # unfused: fp32 sum, one rounding
+    own = 2                                                      # any rank: its partial stays fp32
+    fused = sum(p.float().double() if r == own else p.float().bfloat16().double()
+                for r, p in enumerate(parts)).float().bfloat16().double()
+    scale = exact.abs().mean()
+    err_once = ((once - exact).pow(2).mean().sqrt() / scale).item()
+    err_fused = ((fused - exact).pow(2).mean().sqrt() / scale).item()
+    assert err_fused < 2.0 * err_once, (err_fused, err_once)
+    # element-wise: every rounding is within the bf16 unit round-off (2^-8) of what it rounds
+    u = 2.0 ** -8
+    bound = u * (sum(p.abs() for r, p in enumerate(parts) if r != own) + exact.abs()) * 1.02
+    assert bool(((fused - exact).abs() <= bound + 1e-12).all())
