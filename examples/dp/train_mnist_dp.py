@@ -81,6 +81,12 @@ def main():
                     help="drive every phase of every step by RPC (the reference protocol)")
     ap.add_argument("--grad-comp-threshold", type=float, default=0.0)
     ap.add_argument("--out", type=str, default="")
+    ap.add_argument("--checkpoint-dir", default="",
+                    help="write a checkpoint per rank after every epoch (trainer/resume.py)")
+    ap.add_argument("--resume", action="store_true",
+                    help="continue from the newest epoch every rank has a checkpoint of")
+    ap.add_argument("--fail-at-epoch", type=int, default=-1,
+                    help="rank 1 raises once at the start of this epoch (recovery demo / test)")
     ap.add_argument("--model", default="lenet", choices=["lenet", "mixer"],
                     help="mixer: MLP-Mixer (the reference's train_nklc_nccl_mnist_3_mlpmx.py)")
     ap.add_argument("--loader", default="ngn", choices=["ngn", "queue", "shm", "obj"],
@@ -92,8 +98,11 @@ def main():
     pg_cfg = pg_cfg_from_args(args)
     ncclgrp.init_nccl_groups_map(tmode, pg_cfg)
 
+    from necklace_b200.trainer import resume as nkresume
     if args.role == "scheduler":
+        done = nkresume.resume_epoch(args.checkpoint_dir, args.world_size) if args.resume else 0
         cfg = {"role": "scheduler", "url": args.url, "workers": args.world_size,
+               "start_epoch": done,
                "wdsz": args.world_size, "rank": 0, "epochs": args.epochs,
                "nccl_allreduce_typ": "grad", "stepwise": args.stepwise,
                "nccl_groups_grp_map": ncclgrp.get_nccl_groups_map_grp_dict()}
@@ -135,6 +144,18 @@ def main():
     hook = HookLogLoss(net, ctx, args.out)
     svc.svr.trnr.register_hook_after_batch(hook.on_batch)
     svc.svr.trnr.register_hook_after_epoch(hook)
+    if args.checkpoint_dir:
+        done = nkresume.attach(svc.svr.trnr, args.checkpoint_dir, args.world_size, args.resume)
+        if done:
+            print(f"worker {args.rank}: resumed after {done} epoch(s)", flush=True)
+    if args.fail_at_epoch >= 0 and args.rank == 1:
+        marker = os.path.join(args.checkpoint_dir or ".", "failed_once")
+
+        def fail_once(trnr, *a, **k):           # host-side fault injection
+            if trnr.e == args.fail_at_epoch and not os.path.exists(marker):
+                open(marker, "w").close()
+                raise RuntimeError(f"injected failure at the start of epoch {trnr.e}")
+        svc.svr.trnr.register_hook_before_epoch(fail_once)
     svc.loop()
     print(f"worker {args.rank}:", svc.exit_status)
     return 0 if svc.exit_status == "stopped" else 1

@@ -311,7 +311,8 @@ class Phase:
 class SVCScheduler(svctmp.TmplService):
     """cfg: ``url, workers (count), epochs, nccl_allreduce_typ, net_map, stepwise,
     nccl_groups_grp_map, phase_timeout (600 s), heartbeat_timeout (15 s; 0 = off),
-    register_timeout``."""
+    register_timeout, start_epoch (epochs a resumed job has already done, see
+    trainer/resume.py)``."""
 
     def __init__(self, cfg):
         super().__init__(cfg)
@@ -331,7 +332,7 @@ class SVCScheduler(svctmp.TmplService):
         self.program = None
         self.phase: Phase | None = None
         self.phase_started = 0.0
-        self.epoch = 0
+        self.epoch = int(cfg.get("start_epoch", 0))   # epochs already done (resumed job)
         self.exit_status = "running"
         self.history = []  # (fn, ret values) per completed phase, for tests / debugging
 

@@ -216,3 +216,43 @@ def test_object_ring_loader_yields_arbitrary_batches_in_order():
     finally:
         dl.clear()
     assert PYNCCL_DTYPE_MAP["float"] == 7 and torch_dtype("half") == torch.float16
+
+
+def test_trainer_epoch_checkpoints_keep_the_newest_common_epoch(tmp_path):
+    """Per-rank epoch files: the resume point is the newest epoch every rank has; a rank that
+    owns several units with one optimizer each (the ZeRO flavours) gets them all back."""
+    import torch.nn as nn
+    from necklace_b200.trainer import resume
+
+    class T:                      # the attributes the helpers read from an operator
+        def __init__(self, ti, seed):
+            torch.manual_seed(seed)
+            self.ti, self.e = ti, 0
+            self.nets = [nn.Linear(3, 3), nn.Linear(3, 2)]
+            self.opts = {i: torch.optim.SGD(m.parameters(), lr=0.1, momentum=0.9)
+                         for i, m in enumerate(self.nets)}
+
+        def step(self):
+            for i, m in enumerate(self.nets):
+                self.opts[i].zero_grad()
+                m(torch.ones(1, 3)).sum().backward()
+                self.opts[i].step()
+
+    d = str(tmp_path)
+    a, b = T(0, 1), T(1, 2)
+    for e in (1, 2, 3):
+        a.step()
+        resume.save_trainer(a, d, e, keep=2)
+        if e < 3:                                 # rank 1 died before finishing epoch 3
+            b.step()
+            resume.save_trainer(b, d, e, keep=2)
+    assert resume.epochs_of_rank(d, 0) == [2, 3] and resume.epochs_of_rank(d, 1) == [1, 2]
+    assert resume.resume_epoch(d, 2) == 2 and resume.resume_epoch(d, 3) == 0
+    assert resume.resume_epoch(str(tmp_path / "none"), 2) == 0
+    want = [p.detach().clone() for m in b.nets for p in m.parameters()]
+    mom = b.opts[0].state_dict()["state"][0]["momentum_buffer"].clone()
+    fresh = T(1, 99)
+    resume.load_trainer(fresh, d, 2)
+    got = [p.detach() for m in fresh.nets for p in m.parameters()]
+    assert fresh.e == 2 and all(torch.equal(x, y) for x, y in zip(want, got))
+    assert torch.equal(fresh.opts[0].state_dict()["state"][0]["momentum_buffer"], mom)

@@ -294,3 +294,47 @@ def test_gpt2_zero_through_scheduler_and_workers_cpu(tmp_path):
     assert codes == [0, 0, 0], open(tmp_path / "w0.log").read()[-2000:]
     outs = [json.load(open(tmp_path / f"o{r}.json")) for r in range(2)]
     assert all(o["steps"] == 3 and o["ms"] > 0 and o["loss"] < 7.5 for o in outs)
+
+
+@pytest.mark.timeout(420)
+def test_job_restarts_from_its_checkpoint_after_a_worker_failure(tmp_path):
+    """Elastic recovery on the host: worker 1 raises at the start of the second epoch, the
+    services abort the job, the supervisor starts it again with ``--resume``, scheduler and
+    workers continue after the first epoch, and the final weights equal those of a run that
+    was never interrupted."""
+    from necklace_b200.trainer import resume
+    from necklace_b200.utils.supervise import run_job
+    script = os.path.join(ROOT, "examples", "dp", "train_mnist_dp.py")
+
+    def cmds(d, extra):
+        svr = f"ipc://{d}/s.ipc"
+        base = ["--checkpoint-dir", str(d / "ckpt")]
+        out = [[sys.executable, script, "-r", "scheduler", "-w", "2", "-u", svr, "-e", "3", *base]]
+        for r in range(2):
+            out.append([sys.executable, script, "-r", "worker", "-w", "2", "-k", str(r), "-u",
+                        f"ipc://{d}/w{r}.ipc", "-s", svr, "-t", "dp", "-e", "3", "--no-cuda",
+                        "--dataset-len", "160", "-b", "20", "--momentum", "0.9", "--out",
+                        str(d / f"o{r}.json"), *base, *extra])
+        return out
+
+    def kw(d):
+        def per_attempt(attempt):
+            return [{"stdout": open(d / f"p{i}_a{attempt}.log", "w"), "stderr": subprocess.STDOUT,
+                     "cwd": ROOT} for i in range(3)]
+        return per_attempt
+
+    plain, broken = tmp_path / "plain", tmp_path / "broken"
+    for d in (plain, broken):
+        (d / "ckpt").mkdir(parents=True)
+    codes, restarts = run_job(cmds(plain, []), max_restarts=0, timeout=180, popen_kwargs=kw(plain))
+    assert codes == [0, 0, 0] and restarts == 0
+    codes, restarts = run_job(cmds(broken, ["--fail-at-epoch", "1"]), max_restarts=2, timeout=180,
+                              popen_kwargs=kw(broken))
+    logs = "".join(open(f).read()[-1500:] for f in sorted(broken.glob("p*_a*.log")))
+    assert codes == [0, 0, 0] and restarts == 1, (codes, restarts, logs)
+    assert "injected failure" in open(broken / "p2_a0.log").read()
+    assert "resumed after 1 epoch(s)" in open(broken / "p1_a1.log").read()
+    assert resume.resume_epoch(str(broken / "ckpt"), 2) == 3
+    a = json.load(open(plain / "o0.json"))["weights_sum"]
+    b = [json.load(open(broken / f"o{r}.json"))["weights_sum"] for r in range(2)]
+    assert abs(b[0] - b[1]) < 1e-9 and abs(a - b[0]) < 1e-7, (a, b)
