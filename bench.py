@@ -37,8 +37,9 @@ def parse():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "torch"])
-    ap.add_argument("--config", type=int, default=3, choices=[2, 3, 4, 5],
-                    help="which named configuration: 2 dp + 2-bit ResNet-50, 3 dp+zr GPT-2 "
+    ap.add_argument("--config", type=int, default=3, choices=[1, 2, 3, 4, 5],
+                    help="which named configuration: 1 LeNet on the CPU through one scheduler "
+                         "and one worker (plumbing; no GPU), 2 dp + 2-bit ResNet-50, 3 dp+zr GPT-2 "
                          "medium (the headline), 4 dp+pp+mp Llama-7B-like, 5 dp+zr+mp "
                          "Llama-13B-like")
     ap.add_argument("--model", default="gpt2-medium", choices=["gpt2-medium", "gpt2-tiny"])
@@ -700,6 +701,78 @@ def tp_roofline(wl, world, dev, peaks):
     return out
 
 
+def cpu_plumbing_arm(args):
+    """Config 1: trainer mode ``no`` on the CPU, LeNet, batch 100, SGD 0.01, 3 epochs of 600
+    steps, one scheduler and one worker over ZeroMQ ipc (``examples/dp/train_mnist_dp.py``),
+    against a plain single-process PyTorch loop on the same host.  Host wall-clock: there is no
+    device.  The first epoch is warm-up, the other two are timed."""
+    import subprocess
+    import tempfile
+    import torch
+    work = tempfile.mkdtemp(prefix="nkb-c1-")
+    script = os.path.join(ROOT, "examples", "dp", "train_mnist_dp.py")
+    svr, out = f"ipc://{work}/s.ipc", os.path.join(work, "o.json")
+    procs = [subprocess.Popen([sys.executable, script, "-r", "scheduler", "-w", "1", "-u", svr,
+                               "-e", "3"], stdout=subprocess.DEVNULL, stderr=subprocess.STDOUT),
+             subprocess.Popen([sys.executable, script, "-r", "worker", "-w", "1", "-k", "0", "-u",
+                               f"ipc://{work}/w.ipc", "-s", svr, "-t", "no", "-e", "3", "--no-cuda",
+                               "--log-interval", "0", "--out", out],
+                              stdout=subprocess.DEVNULL, stderr=subprocess.STDOUT)]
+    codes = []
+    for p in procs:
+        try:
+            codes.append(p.wait(timeout=900))
+        except subprocess.TimeoutExpired:
+            p.kill()
+            codes.append(-9)
+    if codes != [0, 0]:
+        print(json.dumps({"impl": "ours", "config": 1, "error": f"exit codes {codes}"}))
+        return 1
+    r = json.load(open(out))
+    secs, steps = sum(r["epoch_seconds"][1:]), sum(r["epoch_steps"][1:])
+    value = 100.0 * steps / secs
+    # the stock loop: same network, batch, optimizer, and the same synthetic dataset and
+    # in-process loader, so that the difference is the scheduler / worker / hook plumbing
+    import torch.nn.functional as F
+    from necklace_b200.data.dtldngn import DataLoaderNgnBase
+    from necklace_b200.data.dtset import SyntheticDataset
+    from necklace_b200.models.lenet import LeNet
+    torch.manual_seed(1)
+    net = LeNet()
+    opt = torch.optim.SGD(net.parameters(), lr=0.01)
+    loader = DataLoaderNgnBase(SyntheticDataset(60000, (1, 28, 28), classes=10, seed=1),
+                               batch_size=100, last_batch="discard")
+
+    def epoch(n):
+        k = 0
+        for x, y in loader:
+            opt.zero_grad()
+            loss = F.cross_entropy(net(x), y)
+            loss.backward()
+            opt.step()
+            loss.item()
+            k += 1
+            if k == n:
+                break
+    epoch(50)
+    t0 = time.time()
+    epoch(600)
+    base = 600 * 100.0 / (time.time() - t0)
+    print(json.dumps({
+        "metric": "samples/sec (host wall-clock; CPU plumbing configuration)",
+        "value": round(value, 1), "unit": "samples/s", "n_gpus": 0, "steps": steps, "warmup": 600,
+        "ms_per_step": round(secs / steps * 1e3, 3), "higher_is_better": True,
+        "vs_baseline": round(value / base, 3), "dtype": "fp32", "data": "synthetic",
+        "impl": "ours",
+        "config": {"model": "lenet", "global_batch": 100, "parallelism": "no (1 scheduler + 1 "
+                   "worker over ZeroMQ ipc)", "optimizer": "sgd 0.01", "epochs": 3,
+                   "host_threads": torch.get_num_threads()},
+        "baseline": {"impl": "single-process PyTorch loop over the same dataset and loader, same "
+                             "host", "value": round(base, 1)},
+        "loss_last": r["epoch_loss"][-1]}), flush=True)
+    return 0
+
+
 def necklace_launcher_arm(args):
     """Config 3 through the framework's own process model: every rank of the launch starts
     one worker of ``examples/gpt2/train_gpt2_necklace.py`` (scheduler / worker services over
@@ -794,6 +867,8 @@ def main():
     args = parse()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.config == 1:
+        return cpu_plumbing_arm(args)
     if args.launcher == "necklace":
         return necklace_launcher_arm(args)
 

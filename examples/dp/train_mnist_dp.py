@@ -17,6 +17,7 @@ import argparse
 import json
 import os
 import sys
+import time
 
 sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", ".."))
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
@@ -47,22 +48,29 @@ class WrpDoLoss(NklcWrapperBase):
 
 
 class HookLogLoss(NklcHookBase):
-    """After every epoch: append the mean training loss of the epoch to a JSON file."""
+    """After every epoch: append the mean training loss and the host seconds of the epoch to
+    a JSON file."""
 
     def __init__(self, net, ctx, path):
         super().__init__(net, ctx)
         self.path, self.losses, self.epochs = path, [], []
+        self.seconds, self.steps, self.t0 = [], [], None
 
     def on_batch(self, trnr, ret=None):
+        if self.t0 is None:
+            self.t0 = time.time()             # the epoch's clock starts after its first step
         if trnr.last_loss is not None and ret == "one_step":
             self.losses.append(float(trnr.last_loss))
 
     def __call__(self, trnr, *args, **kwargs):
         self.epochs.append(sum(self.losses) / max(len(self.losses), 1))
-        self.losses = []
+        self.seconds.append(time.time() - (self.t0 or time.time()))
+        self.steps.append(max(len(self.losses) - 1, 0))
+        self.losses, self.t0 = [], None
         if self.path:
             with open(self.path, "w") as f:
                 json.dump({"rank": trnr.ti, "epoch_loss": self.epochs,
+                           "epoch_seconds": self.seconds, "epoch_steps": self.steps,
                            "weights_sum": float(sum(p.double().sum() for p in
                                                     trnr.net.parameters()))}, f)
 
