@@ -47,7 +47,10 @@ SURFACE = {
         "initialize_model_parallel", "model_parallel_is_initialized", "ColumnParallelLinear",
         "ParallelEmbedding", "RowParallelLinear", "VocabParallelEmbedding",
         "copy_to_model_parallel_region", "gather_from_model_parallel_region",
-        "reduce_from_model_parallel_region", "scatter_to_model_parallel_region"],
+        "reduce_from_model_parallel_region", "scatter_to_model_parallel_region",
+        "vocab_parallel_cross_entropy", "broadcast_data", "clip_grad_norm", "checkpoint",
+        "get_cuda_rng_tracker", "model_parallel_cuda_manual_seed",
+        "partition_activations_in_checkpoint"],
     "frmwrk.pytorch.mpnn.checkpointing": ["checkpoint", "get_cuda_rng_tracker",
                                           "model_parallel_cuda_manual_seed"],
     "frmwrk.pytorch.mpnn.samplers": [], "frmwrk.pytorch.mpnn.utils": [],

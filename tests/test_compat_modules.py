@@ -95,3 +95,52 @@ def test_exchanger_dataloader_wrapper_and_gluon_placeholder():
     except ImportError:
         with pytest.raises(RuntimeError):
             TrainerOPGluon({})
+
+
+def _mpu_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import torch.nn.functional as F
+    from necklace_b200.comm import backend
+    from necklace_b200.frmwrk.pytorch import mpnn
+    backend.init_backend("mp", {"world_size": world, "my_rank": rank, "mp_size": world},
+                         comm_type="gloo", master_port=port)
+    g = torch.Generator().manual_seed(5)
+    full = torch.randn(6, 10, generator=g)
+    target = torch.randint(0, 10, (6,), generator=g)
+    per = 10 // world
+    mine = full[:, rank * per:(rank + 1) * per].clone().requires_grad_(True)
+    loss = mpnn.vocab_parallel_cross_entropy(mine, target)
+    loss.sum().backward()
+    ref_in = full.clone().requires_grad_(True)
+    ref = F.cross_entropy(ref_in, target, reduction="none")
+    ref.sum().backward()
+    ok_ce = torch.allclose(loss, ref, atol=1e-5) and \
+        torch.allclose(mine.grad, ref_in.grad[:, rank * per:(rank + 1) * per], atol=1e-5)
+    data = {"text": torch.arange(12).view(3, 4) * (7 if rank == 0 else 0)}
+    got = mpnn.broadcast_data(["text"], data, torch.int64)
+    ok_bc = torch.equal(got["text"], torch.arange(12).view(3, 4) * 7)
+    shard = torch.nn.Parameter(torch.zeros(4))
+    shard.model_parallel = True
+    shard.grad = torch.full((4,), float(rank + 1))
+    repl = torch.nn.Parameter(torch.zeros(3))
+    repl.grad = torch.full((3,), 2.0)
+    total = mpnn.clip_grad_norm([shard, repl], max_norm=1.0)
+    want = (sum(4 * (r + 1) ** 2 for r in range(world)) + 3 * 4.0) ** 0.5
+    ok_clip = abs(total - want) < 1e-5 and \
+        torch.allclose(repl.grad, torch.full((3,), 2.0 / (want + 1e-6)), atol=1e-6)
+    q.put((rank, ok_ce, ok_bc, ok_clip, total))
+    backend.shutdown_backend()
+
+
+@pytest.mark.timeout(300)
+def test_model_parallel_cross_entropy_data_broadcast_and_clipping_on_two_ranks():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q, port = ctx.Queue(), _free_port()
+    procs = [ctx.Process(target=_mpu_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=240) for _ in procs]
+    for p in procs:
+        p.join(60)
+    assert all(r[1] and r[2] and r[3] for r in res), res
