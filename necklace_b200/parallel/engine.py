@@ -129,6 +129,10 @@ class TrainEngine:
         self._order: list[int] | None = None      # parameter index per delivery
         self._fire_at: dict[int, list[int]] | None = None
         self._recording: list[int] | None = None
+        # NKB_DEBUG_STREAMS=1: logical check that bucket work on the side stream and gradient
+        # writes on the main stream are ordered by the events below (utils/streamcheck.py)
+        from ..utils import streamcheck
+        self._chk = streamcheck.from_env()
         self._deliveries = 0
         self._fired: set[int] = set()
         self._armed = False
@@ -203,11 +207,19 @@ class TrainEngine:
             return
         k = self._deliveries
         self._deliveries += 1
+        if self._chk is not None:
+            for b in self._buckets_of(i):
+                self._chk.access(f"bucket{b}", "main", True, f"gradient of parameter {i}")
         if self._order is None or k >= len(self._order) or self._order[k] != i:
             raise RuntimeError("gradient delivery order changed between steps; overlapped "
                                "buckets need a static model (construct with bucket_mb=None)")
         for b in self._fire_at.get(k, ()):
             self._launch_bucket(b, side=True)
+
+    def _buckets_of(self, i: int) -> list[int]:
+        """Buckets that hold a part of parameter ``i``."""
+        o, n = self.flat.offsets[i], self.flat.params[i].numel()
+        return [b for b, (lo, hi) in enumerate(self.buckets) if o < hi and o + n > lo]
 
     def _learn_order(self, seq: list[int]) -> None:
         f = self.flat
@@ -238,9 +250,14 @@ class TrainEngine:
             ev = torch.cuda.Event()
             ev.record(cur)
             self._comm_stream.wait_event(ev)
+            if self._chk is not None:
+                self._chk.wait("side", self._chk.record("main"))
+                self._chk.access(f"bucket{b}", "side", True, "bucket collective / update")
             with torch.cuda.stream(self._comm_stream):
                 self._bucket_work(b, self.comm_ctas)
         else:
+            if self._chk is not None:
+                self._chk.access(f"bucket{b}", "main", True, "bucket collective / update")
             self._bucket_work(b, None)
 
     def _join_side(self) -> None:
@@ -248,6 +265,8 @@ class TrainEngine:
             ev = torch.cuda.Event()
             ev.record(self._comm_stream)
             torch.cuda.current_stream().wait_event(ev)
+            if self._chk is not None:
+                self._chk.join("main", "side")
 
     # ----------------------------------------------------------- per-bucket work
     def _opt_range(self, lo: int, hi: int, grad, param, state_lo: int) -> None:
