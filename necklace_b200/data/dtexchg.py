@@ -1,13 +1,19 @@
-"""Data exchanger between workers (reference: necklace/data/dtexchg.py:3-9, a stub whose
-``exchange`` does nothing).  Here ``exchange`` calls the function it was given."""
+"""Hook point for moving samples between workers during training (reference:
+necklace/data/dtexchg.py:3-9 declares the class and leaves ``exchange`` empty).  The function
+given at construction does the work; without one nothing happens."""
+from __future__ import annotations
+
+from typing import Any, Callable, Optional
 
 
-class DataExchanger(object):
-    def __init__(self, cfg=None, exchange_fn=None):
-        self.cfg = cfg or {}
+class DataExchanger:
+    def __init__(self, cfg: Optional[dict] = None,
+                 exchange_fn: Optional[Callable[..., Any]] = None):
+        self.cfg = dict(cfg or {})
         self.exchange_fn = exchange_fn
 
-    def exchange(self, *args, **kwargs):
-        if self.exchange_fn is None:
-            return None
-        return self.exchange_fn(*args, **kwargs)
+    def exchange(self, *batch, **options):
+        fn = self.exchange_fn
+        return fn(*batch, **options) if fn is not None else None
+
+    __call__ = exchange
