@@ -20,11 +20,17 @@ def init_mp() -> None:
         pass
 
 
-def init(gpu_dev_i: int | str = 0) -> None:
-    """Process-wide initialisation: spawn start method and device selection
-    (reference: necklace/__init__.py:34-38; the numba device selection done there
-    has no counterpart because no numba kernels remain)."""
-    init_mp()
+def init_nb(gpu_dev_i: int | str = 0) -> None:
+    """Make GPU ``gpu_dev_i`` the current device before anything else touches it (the
+    reference selects the numba device here, necklace/__init__.py:19-30; no numba kernels
+    remain, so this selects the torch device)."""
     import torch
     if torch.cuda.is_available():
         torch.cuda.set_device(int(gpu_dev_i))
+
+
+def init(gpu_dev_i: int | str = 0) -> None:
+    """Process-wide initialisation: spawn start method and device selection
+    (reference: necklace/__init__.py:34-38)."""
+    init_mp()
+    init_nb(gpu_dev_i)

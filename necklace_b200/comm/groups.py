@@ -53,6 +53,10 @@ class GroupInfo:
         return f"GroupInfo({self.kind}, rank {self.rank}/{self.world_size}, {self.pg_ranks})"
 
 
+# the reference's name of the group object (necklace/cuda/ncclgrp.py:24-60)
+NcclProcessGroup = GroupInfo
+
+
 class _State:
     def __init__(self):
         self.reset()

@@ -2,3 +2,27 @@
 module name (necklace/data/dtmem.py exports ``DataLoaderSharedMemory``): worker processes
 pickle each collated batch into a ring of POSIX shared-memory slots (``data.shmem``)."""
 from .loaders import ShmObjectRingDataLoader as DataLoaderSharedMemory  # noqa: F401
+
+
+class DataLoaderShmForModule(DataLoaderSharedMemory):
+    """The same loader with the ``provide_data`` / ``provide_label`` descriptors that an
+    MXNet ``Module`` asks its data iterator for (reference: necklace/data/dtmem.py:362-396):
+    ``[(name, shape)]`` of one training batch, taken from the first sample."""
+
+    def __init__(self, *args, **kwargs):
+        super().__init__(*args, **kwargs)
+        self.mode = "train"
+        first = self.dataset[0]
+        self.data, self.label = first[0], first[1]
+
+    @property
+    def provide_data(self):
+        shape = tuple(getattr(self.data, "shape", ()))
+        return [("data", (self.batch_size,) + shape)]
+
+    @property
+    def provide_label(self):
+        return [("label", (self.batch_size,))]
+
+    def reset(self):
+        pass

@@ -7,7 +7,7 @@ import importlib
 import pytest
 
 SURFACE = {
-    "": ["init"],
+    "": ["init", "init_mp", "init_nb"],
     "utils.argutils": ["attach_nk_args_parser", "args_remake"],
     "utils.hookbase": ["NklcHookBase"],
     "utils.wrpbase": ["NklcWrapperBase"],
@@ -19,7 +19,7 @@ SURFACE = {
                      "get_nccl_group_dp", "get_nccl_group_mp", "get_nccl_group_pp",
                      "get_nccl_group_zr", "get_nccl_group_dp_or_main", "get_nccl_group_mp_or_main",
                      "get_nccl_group_pp_or_main", "get_nccl_group_zr_or_main", "get_rank",
-                     "get_world_size"],
+                     "get_world_size", "NcclProcessGroup"],
     "cuda.ncclfns": [], "cuda.ncclwrp": ["PYNCCL_DTYPE_MAP"], "cuda.quantize": [],
     "cuda.nbutils": ["cuda_select_device", "cuda_current_context", "cuda_stream", "cuda_to_device",
                      "cuda_devarr_c_void_p"],
@@ -32,10 +32,10 @@ SURFACE = {
                      "get_world_size", "ensure_divisibility", "divide", "build_pg_cfg"],
     "trainer.tndsnc": ["SVCScheduler", "SVCWorker"],
     "trainer.tndsms": ["SVCScheduler", "SVCWorker"],
-    "trainer.tndsmp": ["MPSVCScheduler", "MPSVCWorker"],
-    "trainer.tndspp": ["MPSVCScheduler", "MPSVCWorker"],
-    "trainer.tndszr": ["MPSVCScheduler", "MPSVCWorker"],
-    "trainer.tndszd": ["MPSVCScheduler", "MPSVCWorker"],
+    "trainer.tndsmp": ["MPSVCScheduler", "MPSVCWorker", "MPSVRScheduler", "MPSVRWorker"],
+    "trainer.tndspp": ["MPSVCScheduler", "MPSVCWorker", "MPSVRScheduler", "MPSVRWorker"],
+    "trainer.tndszr": ["MPSVCScheduler", "MPSVCWorker", "MPSVRScheduler", "MPSVRWorker"],
+    "trainer.tndszd": ["MPSVCScheduler", "MPSVCWorker", "MPSVRScheduler", "MPSVRWorker"],
     "trainer.tnoppt": ["TrainerOPPytorch"],
     "trainer.mpoppt": ["TrainerMPOPPytorch"], "trainer.ppoppt": ["TrainerMPOPPytorch"],
     "trainer.zroppt": ["TrainerMPOPPytorch"], "trainer.zroppf": ["TrainerMPOPPytorch"],
@@ -60,7 +60,7 @@ SURFACE = {
     "data.dtdummy": ["DtstDummy", "DtldDummy"],
     "data.dtqpto": ["DataLoaderSharedMemory"], "data.dtqptp": ["DataLoaderSharedMemory"],
     "data.dtmptp": ["DataLoaderSharedMemory"], "data.dtmptv": ["DataLoaderSharedMemory"],
-    "data.sampler": [], "data.batchify": [], "data.shmem": [], "data.dtmem": [], "data.dtshm": [],
+    "data.sampler": [], "data.batchify": [], "data.shmem": [], "data.dtmem": ["DataLoaderSharedMemory", "DataLoaderShmForModule"], "data.dtshm": [],
     "data.dtshmp": [], "data.shmpt": [], "data.dtdist": [], "data.dtset": [], "data.dtwrp": [],
     "data.dtldngn": [], "data.shmmx": ["SharedMemArray"], "data.dtmmx": ["DataLoaderSharedMemory"],
     "data.dtmmxp": ["DataLoaderSharedMemory"], "data.dtexchg": ["DataExchanger"],
