@@ -103,6 +103,26 @@ def matrix_dequantize(codes: torch.Tensor, n: int, thr: float) -> torch.Tensor:
     return A
 
 
-# names of the reference wrappers
-cu_fn_matrix_quantize_e = matrix_quantize
-cu_fn_matrix_dequantize_e = matrix_dequantize
+def _as_tensor(a):
+    return torch.from_numpy(a) if isinstance(a, np.ndarray) else a
+
+
+def cu_fn_matrix_quantize_e(A, C, R, thrd=0.3, bpg=None, tpb=None, to_device=False, stream=None):
+    """The reference wrapper's call shape (necklace/cuda/quantize.py:96-115): quantise fp32
+    ``A[n, n']`` into the code words ``C[ceil(n/16), n']`` (32-bit) and write the error-feedback
+    residual into ``R[n, n']``, all in place.  Tensors or numpy arrays; the launch geometry
+    arguments are accepted and unused."""
+    a, c, r = _as_tensor(A), _as_tensor(C), _as_tensor(R)
+    codes, _ = matrix_quantize(a.contiguous(), float(thrd), r)
+    c.view(torch.int32).copy_(codes) if c.dtype != torch.int32 else c.copy_(codes)
+    return C
+
+
+def cu_fn_matrix_dequantize_e(A, C, R=None, thrd=0.3, bpg=None, tpb=None, to_device=False,
+                              stream=None):
+    """Decode the code words ``C`` into ``A[n, n']`` (+thrd, -thrd or 0 per element), in place
+    (necklace/cuda/quantize.py:118-134; ``R`` is not read by the decode)."""
+    a, c = _as_tensor(A), _as_tensor(C)
+    c32 = c if c.dtype == torch.int32 else c.view(torch.int32)
+    a.copy_(matrix_dequantize(c32.contiguous(), a.shape[0], float(thrd)))
+    return A

@@ -144,3 +144,24 @@ def test_model_parallel_cross_entropy_data_broadcast_and_clipping_on_two_ranks()
     for p in procs:
         p.join(60)
     assert all(r[1] and r[2] and r[3] for r in res), res
+
+
+def test_matrix_codec_wrappers_take_the_reference_call_shape():
+    """``cu_fn_matrix_quantize_e(A, C, R, thrd)`` / ``cu_fn_matrix_dequantize_e(A, C, R, thrd)``
+    work in place on tensors and on numpy arrays; decoded value + residual = input (error
+    feedback), 16 fp32 values per 32-bit word."""
+    from necklace_b200.cuda import quantize as q
+    assert q.CMP_RATIO == 16
+    A = torch.randn(40, 6)
+    C = torch.zeros(3, 6, dtype=torch.int32)
+    R = torch.zeros(40, 6)
+    q.cu_fn_matrix_quantize_e(A, C, R, 0.5)
+    B = torch.ones(40, 6)
+    q.cu_fn_matrix_dequantize_e(B, C, R, 0.5)
+    assert torch.allclose(B + R, A, atol=1e-6)
+    assert set(B.unique().tolist()) <= {-0.5, 0.0, 0.5}
+    An = np.random.RandomState(0).randn(32, 4).astype(np.float32)
+    Cn, Rn, Bn = np.zeros((2, 4), dtype=np.uint32), np.zeros_like(An), np.zeros_like(An)
+    q.cu_knl_matrix_quantize_e(An, Cn, Rn, 0.3)
+    q.cu_knl_matrix_dequantize_e(Bn, Cn, Rn, 0.3)
+    assert np.allclose(Bn + Rn, An, atol=1e-6) and Cn.any()
