@@ -20,7 +20,8 @@ SURFACE = {
                      "get_nccl_group_zr", "get_nccl_group_dp_or_main", "get_nccl_group_mp_or_main",
                      "get_nccl_group_pp_or_main", "get_nccl_group_zr_or_main", "get_rank",
                      "get_world_size", "NcclProcessGroup"],
-    "cuda.ncclfns": [], "cuda.ncclwrp": ["PYNCCL_DTYPE_MAP"], "cuda.quantize": ["CMP_RATIO", "cu_fn_matrix_quantize_e", "cu_fn_matrix_dequantize_e",
+    "cuda.ncclfns": ["all_gather", "all_reduce", "broadcast", "reduce", "pg_all_gather",
+                     "pg_all_reduce", "pg_broadcast", "pg_reduce"], "cuda.ncclwrp": ["PYNCCL_DTYPE_MAP"], "cuda.quantize": ["CMP_RATIO", "cu_fn_matrix_quantize_e", "cu_fn_matrix_dequantize_e",
                       "cu_knl_matrix_quantize_e", "cu_knl_matrix_dequantize_e"],
     "cuda.nbutils": ["cuda_select_device", "cuda_current_context", "cuda_stream", "cuda_to_device",
                      "cuda_devarr_c_void_p"],

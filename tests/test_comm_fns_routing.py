@@ -75,3 +75,31 @@ def test_non_members_and_single_rank_groups_return_at_once():
     out = torch.zeros(4)
     fns.all_gather(out, t, one)
     assert torch.equal(out, t)
+
+
+def test_reference_argument_order_of_the_compat_module(monkeypatch):
+    """``cuda.ncclfns`` keeps the reference's positional order (datatype before op / group;
+    broadcast's root defaults to the caller's own group rank) and maps operator codes."""
+    from necklace_b200.cuda import ncclfns, ncclwrp
+    seen = []
+    monkeypatch.setattr(fns, "_peer", lambda group, t: None)
+    monkeypatch.setattr(dist, "all_reduce", lambda t, **k: seen.append(("ar", k["op"])))
+    monkeypatch.setattr(dist, "broadcast", lambda t, **k: seen.append(("bc", k["src"])))
+    monkeypatch.setattr(dist, "reduce", lambda t, **k: seen.append(("rd", k["dst"], k["op"])))
+    monkeypatch.setattr(dist, "all_gather_into_tensor", lambda o, i, **k: seen.append("ag"))
+    g = _group(rank=1)
+    t = torch.zeros(4)
+    ncclfns.all_reduce(t, ncclwrp.ncclFloat, ncclwrp.ncclMax, g)
+    ncclfns.all_reduce(t, group=g)
+    ncclfns.broadcast(t, None, None, g)                       # root = my group rank = 1
+    ncclfns.broadcast(t, 0, group=g)
+    ncclfns.reduce(t, 0, None, "sum", g)
+    ncclfns.all_gather(torch.zeros(8), t, None, g)
+    send = torch.arange(4.0)
+    ncclfns.pg_all_reduce(send, t, 4, None, None, g)
+    assert torch.equal(t, send)                               # copied into the receive tensor
+    assert seen == [("ar", dist.ReduceOp.MAX), ("ar", dist.ReduceOp.SUM), ("bc", 1), ("bc", 0),
+                    ("rd", 0, dist.ReduceOp.SUM), "ag", ("ar", dist.ReduceOp.SUM)]
+    import pytest
+    with pytest.raises(TypeError):
+        ncclfns.pg_all_reduce(1234, 5678, 4, group=g)
