@@ -221,6 +221,71 @@ def get_nccl_group_main_rank(*a, **k):
     return _S.main_rank
 
 
+# -- the reference's builder-level entry points (necklace/cuda/ncclgrp.py:62-121, :429-500): a
+# script that assembles its groups by hand instead of from a trainer mode uses these ----------
+def build_pg_cfg(pg_rank, pg_ranks):
+    return {"pg_rank": pg_rank, "pg_ranks": list(pg_ranks)}
+
+
+def make_pg_by_nk(nk, comm_i, pg_rank, pg_ranks):
+    """A group object for ``pg_ranks`` as seen from global rank ``pg_rank``.  ``nk`` (a
+    communicator to attach, may be ``None``) and ``comm_i`` keep the reference's positions; the
+    communicator can also be attached later with ``attach_comm``."""
+    g = GroupInfo(pg_rank, list(pg_ranks))
+    if nk is not None:
+        g.attach_comm(nk)
+    return g
+
+
+def make_pg_by_nc(nc, pg_rank, pg_ranks):
+    return make_pg_by_nk(nc, None, pg_rank, pg_ranks)
+
+
+def set_nccl_group_main_world_size(world_size):
+    _S.main_world_size = world_size
+
+
+def set_nccl_group_main_rank(rank):
+    _S.main_rank = rank
+
+
+def set_nccl_group_main_by_nc(nc, world_size):
+    """The main group of ``world_size`` ranks around an existing communicator ``nc`` (its
+    ``rank`` attribute is this process's global rank)."""
+    rank = int(getattr(nc, "rank", _S.main_rank or 0))
+    _S.main = make_pg_by_nk(nc, None, rank, list(range(world_size)))
+    _S.main.kind = "main"
+    _S.main_world_size, _S.main_rank = world_size, rank
+    return _S.main
+
+
+def get_nccl_main_nk(*a, **k):
+    """The communicator of the main group (``None`` before bring-up)."""
+    return getattr(_S.main, "comm", None)
+
+
+def set_nccl_groups_map(pg_map):
+    _S.mine = dict(pg_map)
+
+
+def init_nccl_group_pg(pg, group, ranks):
+    """Register ``group`` as this rank's group of kind ``pg`` (``'dp_group'``, ...)."""
+    assert pg not in _S.mine, f"{pg} is already initialized"
+    group.kind = pg[:2]
+    _S.mine[pg] = group
+
+
+def init_nccl_group_pgs(world_size, my_rank, pgs_dl, pgs_sz=None, is_worker=True):
+    """Groups from explicit rank lists: ``pgs_dl = {'dp_group': [[0, 2], [1, 3]], ...}``."""
+    for pg, grp in pgs_dl.items():
+        if is_worker:
+            for ranks in grp:
+                if my_rank in ranks:
+                    init_nccl_group_pg(pg, make_pg_by_nk(None, None, my_rank, ranks), ranks)
+        _S.all[pg] = [list(r) for r in grp]
+        _S.sizes[pg] = len(grp[0]) if grp else 0
+
+
 def _get(kind):
     return _S.mine.get(kind + "_group")
 

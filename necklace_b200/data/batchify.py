@@ -38,3 +38,16 @@ def stack_batchify_fn(items):
     xs = torch.stack([x if isinstance(x, torch.Tensor) else torch.as_tensor(x) for x in xs])
     ys = torch.stack([y if isinstance(y, torch.Tensor) else torch.as_tensor(y) for y in ys])
     return xs, ys
+
+
+def nothing_batchify_fn(dt):
+    """The batch as it is (reference: necklace/data/batchify.py:16-17)."""
+    return dt
+
+
+def label_reduce_batchify_fn(dt, lbl_n=1000):
+    """Fold the first label column into ``[0, lbl_n)`` in place (reference:
+    necklace/data/batchify.py:20-23): ``dt = (data, labels[B, k])``."""
+    for row in dt[1]:
+        row[0] %= lbl_n
+    return dt

@@ -211,3 +211,29 @@ def tensors_do_nccl_p2p_recv(nc, rank_send, rank_recv, recv_tensors, dtype=None)
     for w in works:
         w.wait()
     return recv_tensors
+
+
+def nccl_nc_allreduce(nc, p_arr_send, p_arr_recv, sz=None):
+    """``p_arr_recv`` = sum over the group of ``p_arr_send`` (tensors where the reference
+    passes device addresses, necklace/frmwrk/pytorch/ptprms.py:85-92)."""
+    if p_arr_recv.data_ptr() != p_arr_send.data_ptr():
+        p_arr_recv.copy_(p_arr_send)
+    fns.all_reduce(p_arr_recv, group=_group(nc))
+    return p_arr_recv
+
+
+nccl_pg_allreduce = nccl_nc_allreduce
+
+
+def nccl_pg_broadcast(pg, p_arr_send, p_arr_recv, sz=None, root=0):
+    if p_arr_recv.data_ptr() != p_arr_send.data_ptr():
+        p_arr_recv.copy_(p_arr_send)
+    fns.broadcast(p_arr_recv, root, _group(pg))
+    return p_arr_recv
+
+
+def nccl_pg_reduce(pg, p_arr_send, p_arr_recv, sz=None, root=0):
+    if p_arr_recv.data_ptr() != p_arr_send.data_ptr():
+        p_arr_recv.copy_(p_arr_send)
+    fns.reduce(p_arr_recv, root, group=_group(pg))
+    return p_arr_recv

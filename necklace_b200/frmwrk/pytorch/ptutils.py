@@ -94,3 +94,18 @@ def memory_status(msg, print_rank=-1, reset_max=False):
 
 def get_ma_status():
     return torch.cuda.memory_allocated() if torch.cuda.is_available() else 0
+
+
+def pad_line(aj, mxs):
+    """Cells of one row padded with blanks to the column widths ``mxs``."""
+    return [c + " " * (w - len(c)) for c, w in zip(aj, mxs)]
+
+
+def prnt_by_tab(a):
+    """Print rows of strings as a table: columns padded to their widest cell, joined by tabs
+    (reference: necklace/frmwrk/pytorch/ptutils.py:65-81)."""
+    if not a:
+        return
+    mxs = [max(len(row[i]) for row in a) for i in range(len(a[0]))]
+    for row in a:
+        print("\t".join(pad_line(row, mxs)))

@@ -163,3 +163,50 @@ def test_node_timers_and_stop():
     th.start()
     th.join(timeout=5)
     assert not th.is_alive() and len(hits) >= 3
+
+
+def test_groups_assembled_by_hand_with_the_builder_entry_points():
+    """The reference's lower-level calls (necklace/cuda/ncclgrp.py:62-121, :429-500): explicit
+    rank lists instead of a trainer mode."""
+    from necklace_b200.comm import groups as G
+    G.reset_nccl_groups_map()
+    try:
+        G.init_nccl_group_main(4, 3)
+        G.init_nccl_group_pgs(4, 3, {"dp_group": [[0, 2], [1, 3]], "mp_group": [[0, 1], [2, 3]]},
+                              {"dp_group": 2, "mp_group": 2}, True)
+        assert G.get_nccl_group_dp().pg_ranks == [1, 3] and G.get_nccl_group_dp().rank == 1
+        assert G.get_nccl_group_mp().pg_ranks == [2, 3] and G.get_nccl_group_mp().kind == "mp"
+        assert G.get_nccl_groups_map_grp_dict()["dp_group"] == [[0, 2], [1, 3]]
+        assert G.build_pg_cfg(3, [1, 3]) == {"pg_rank": 3, "pg_ranks": [1, 3]}
+        g = G.make_pg_by_nc("comm", 1, [3, 1])
+        assert g.comm == "comm" and g.pg_ranks == [1, 3] and g.rank == 0
+        G.set_nccl_group_main_world_size(8)
+        G.set_nccl_group_main_rank(5)
+        assert G.get_nccl_group_main_world_size() == 8 and G.get_nccl_group_main_rank() == 5
+
+        class Nc:
+            rank = 2
+        main = G.set_nccl_group_main_by_nc(Nc(), 4)
+        assert main.rank == 2 and isinstance(G.get_nccl_main_nk(), Nc)
+        G.set_nccl_groups_map({"zr_group": g})
+        assert G.get_nccl_group_zr() is g
+    finally:
+        G.reset_nccl_groups_map()
+
+
+def test_input_broadcast_helpers_accept_both_call_shapes(monkeypatch):
+    import torch
+    from necklace_b200.comm import fns
+    from necklace_b200.comm.groups import GroupInfo
+    from necklace_b200.data import dtdist
+    seen = []
+    monkeypatch.setattr(fns, "broadcast", lambda t, root, group: seen.append(("bc", root, group)))
+    monkeypatch.setattr(fns, "all_reduce", lambda t, group=None: seen.append(("ar", group)))
+    g, t = GroupInfo(0, [0, 1], "mp"), torch.zeros(2)
+    dtdist.dt_shape_do_nccl_broadcast(t, 1, g)
+    dtdist.dt_shape_do_nccl_broadcast(g, t)                 # reference order
+    dtdist.dt_input_do_nccl_broadcast(g, t, "float32")      # reference order
+    dtdist.dt_sampler_do_nccl_bcast(g, 2, 1, t)             # reference order: nc, kn, root, buf
+    dtdist.dt_sampler_do_nccl_bcast(t, 0, g)
+    dtdist.dt_sampler_do_nccl_allreduce(g, 2, 0, t)
+    assert seen == [("bc", 1, g), ("bc", 0, g), ("bc", 0, g), ("bc", 1, g), ("bc", 0, g), ("ar", g)]
