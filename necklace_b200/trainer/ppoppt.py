@@ -50,6 +50,12 @@ class TrainerMPOPPytorch(TrainerOPPytorch):
         self.stage = None
 
     # group helpers ----------------------------------------------------------------
+    def is_first_part(self):
+        return self.is_first
+
+    def is_last_part(self):
+        return self.is_last
+
     def pp_ranks(self):
         g = G.get_nccl_group_pp()
         if g is not None:

@@ -76,6 +76,45 @@ class TrainerOPPytorch(TrainerOPBase):
             self.net_init(self.net)
         self.before_train_done = False
 
+    # -------------------------------------------- small helpers hooks may call
+    def to_ctx(self, x):
+        """Tensor (or nested list / tuple of tensors) on this operator's device."""
+        return _to_ctx(x, self.ctx)
+
+    def try_to_ctx(self, x):
+        """Like ``to_ctx``; anything that cannot be moved comes back unchanged."""
+        try:
+            return _to_ctx(x, self.ctx)
+        except (TypeError, RuntimeError):
+            return x
+
+    @staticmethod
+    def to_list(x):
+        return list(x) if isinstance(x, (list, tuple)) else [x]
+
+    def cuda_sync(self):
+        """Wait for this operator's stream (the reference synchronises stream and device
+        around every collective, necklace/trainer/tnoppt.py:551-554; here only callers that
+        need host-visible results do)."""
+        self.nccl_stream_sync()
+
+    def check_if_last_batch(self):
+        n = len(self.train_data) if hasattr(self.train_data, "__len__") else -1
+        return n > 0 and self.i + 1 >= n
+
+    def clear_train_data(self):
+        dl = self.train_data
+        if dl is not None and hasattr(dl, "clear"):
+            dl.clear()
+        self.train_data, self.train_data_it = None, None
+
+    def train_loop(self, typ="grad"):
+        """All epochs in this process without a scheduler (the reference's stand-alone loop,
+        necklace/trainer/tnoppt.py ``train_loop``): for scripts that drive one operator by hand."""
+        while self.e < self.epochs:
+            self.run_steps(typ)
+            self.next_epoch()
+
     # ------------------------------------------------------------------ data
     def init_train_data_it(self, *args, **kwargs):
         if self.train_data is None and self.dataloader_creator is not None:

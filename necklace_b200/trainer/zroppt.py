@@ -108,6 +108,17 @@ class TrainerMPOPPytorch(TrainerOPPytorch):
         elif self.offload:
             net.to("cpu")
 
+    def is_first_part(self, i=None):
+        """Is unit ``i`` (default: the unit this rank owns) the first / last of the network?"""
+        return (self.cfg.get("net_map_order", self.ti) if i is None else i) == 0
+
+    def is_last_part(self, i=None):
+        return (self.cfg.get("net_map_order", self.ti) if i is None else i) == len(self.nets) - 1
+
+    def opts_zero_grad(self):
+        for o in self.opts.values():
+            o.zero_grad(set_to_none=False)
+
     def get_whole_net_cpu(self):
         """All parts in order as one CPU module (evaluation, whole-model checkpoints)."""
         parts = [p.to("cpu") if self.mm is None else p for p in self.nets]

@@ -166,3 +166,22 @@ def test_array_level_helpers_on_a_single_rank_group():
     d = nbutils.cuda_to_device(np.ones(3, dtype=np.float32))
     assert isinstance(nbutils.cuda_devarr_c_void_p(d), ctypes.c_void_p)
     assert nbutils.cuda_current_context().type in ("cpu", "cuda")
+
+
+def test_operator_convenience_methods():
+    import torch
+    from necklace_b200.trainer.ppoppt import TrainerMPOPPytorch as PP
+    from necklace_b200.trainer.tnoppt import TrainerOPPytorch
+    from necklace_b200.trainer.zroppt import TrainerMPOPPytorch as ZR
+    for name in ("to_ctx", "try_to_ctx", "to_list", "cuda_sync", "check_if_last_batch",
+                 "clear_train_data", "train_loop", "metric_log", "init_train_data_it"):
+        assert hasattr(TrainerOPPytorch, name), name
+    for cls in (PP, ZR):
+        assert hasattr(cls, "is_first_part") and hasattr(cls, "is_last_part")
+    assert hasattr(ZR, "opts_zero_grad")
+    t = TrainerOPPytorch({"ctx": torch.device("cpu"), "net": torch.nn.Linear(2, 2)})
+    x = t.to_ctx([torch.ones(2), (torch.zeros(1),)])
+    assert isinstance(x, list) and isinstance(x[1], tuple) and x[0].device.type == "cpu"
+    assert t.try_to_ctx("text") == "text" and t.to_list(3) == [3] and t.to_list((1, 2)) == [1, 2]
+    t.cuda_sync()
+    assert t.check_if_last_batch() is False
