@@ -27,6 +27,10 @@ import zmq
 from . import msgpck
 from .mixinbase import NodeMixin
 
+
+class NodeBase(object):
+    """Root of the node classes (reference: necklace/rpc/zrpc.py:34-35)."""
+
 DEFAULT_URL = "ipc:///tmp/zrpc-1.ipc"
 
 

@@ -256,3 +256,26 @@ def test_trainer_epoch_checkpoints_keep_the_newest_common_epoch(tmp_path):
     got = [p.detach() for m in fresh.nets for p in m.parameters()]
     assert fresh.e == 2 and all(torch.equal(x, y) for x, y in zip(want, got))
     assert torch.equal(fresh.opts[0].state_dict()["state"][0]["momentum_buffer"], mom)
+
+
+def test_shared_tensor_array_in_the_reference_call_shape():
+    """``SharedMemArray(name=None, obj_shape=..., dtype='torch.float')`` creates,
+    ``create_from_shmem_key(sk)`` attaches (necklace/data/shmpt.py:209-295)."""
+    import pickle
+    from necklace_b200.data import shmpt
+    a = shmpt.SharedMemArray(name=None, obj_shape=(3, 2), dtype="torch.float")
+    try:
+        a[1] = [5.0, 6.0]
+        b = shmpt.SharedMemArray.create_from_shmem_key(pickle.loads(pickle.dumps(a.sk)))
+        assert b.buf.shape == (3, 2) and b[1].tolist() == [5.0, 6.0]
+        c = shmpt.SharedMemArray(sk=a.sk)
+        c[0] = torch.tensor([1.0, 2.0])
+        assert a.buf[0].tolist() == [1.0, 2.0]
+        b.unlink()
+        c.unlink()
+        assert shmpt.dtype_to_tensor("torch.long") is torch.LongTensor
+        old = shmpt.SharedMemArray((2,), torch.int64)          # this framework's call shape
+        assert shmpt.SharedMemArray.attach(*old.key).tensor.dtype == torch.int64
+        old.close()
+    finally:
+        a.unlink()
