@@ -21,6 +21,12 @@ class DataLoaderNgnBase:
             batch_sampler = self._make_batch_sampler(sampler)
         self.batch_sampler = batch_sampler
 
+    def init_slice_sampler(self):
+        """(Re)create the default sampler over the whole dataset and its batch sampler
+        (reference: necklace/data/dtldngn.py:37-39)."""
+        self.sampler = SliceSampler(len(self.dataset), shuffle=self.shuffle)
+        self.batch_sampler = self._make_batch_sampler(self.sampler)
+
     def _make_batch_sampler(self, smplr):
         cls = SliceBatchSampler if isinstance(smplr, SliceSampler) else BatchSampler
         return cls(smplr, self.batch_size, self.last_batch)

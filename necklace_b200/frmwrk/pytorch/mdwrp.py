@@ -43,6 +43,21 @@ class MdWrpWithSelfBkwd(nn.Module):
             out.append(x)
         return out
 
+    def cache_graded_input(self, *args, **kwargs):
+        """Detach the inputs from the upstream graph (every unit but the first) so that their
+        gradients can be read after ``mp_backward``, keep them, and return them
+        (reference: necklace/frmwrk/pytorch/mdwrp.py:68-83)."""
+        self.inputs = self._graded(args)
+        return self.inputs
+
+    @property
+    def inp_cache(self):
+        return self.inputs
+
+    @property
+    def out_cache(self):
+        return self.output
+
     def forward(self, *inputs):
         self.inputs = self._graded(inputs)
         if self.do_acts_ckpt and not self.is_last_part and torch.is_grad_enabled():
