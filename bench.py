@@ -315,6 +315,8 @@ class GPT2Zero(Workload):
                              "the 126 MB L2; no explicit flush",
                        "cuda_graph": impl == "ours" and not args.no_graph,
                        "bucket_mb": args.bucket_mb}
+        if which == 4:
+            self.config["pipeline"] = self.pipeline
         if args.layers:
             self.config["reduced"] = f"{args.layers} layers: smoke run, not a benchmark number"
 
@@ -407,6 +409,9 @@ class LlamaHybrid(Workload):
             self.has_data = stage == 0
             replicas = dpg.world_size
             par = f"dp={replicas} pp={pp} mp={mp}"
+            # share of a 1F1B step in which a stage waits for the pipeline to fill and drain
+            self.pipeline = {"stages": n_stage, "micro_batches": n_mb, "schedule": "1F1B",
+                             "bubble_fraction": round((n_stage - 1) / (n_mb + n_stage - 1), 4)}
         else:
             net = Llama(cfgm, device=dev)
             zrg = G.get_nccl_group_zr()
@@ -441,6 +446,8 @@ class LlamaHybrid(Workload):
                        if fused else "NCCL all-reduce",
                        "l2": "working set exceeds L2; no explicit flush", "cuda_graph": False,
                        "bucket_mb": args.bucket_mb}
+        if which == 4:
+            self.config["pipeline"] = self.pipeline
         if args.layers:
             self.config["reduced"] = f"{args.layers} layers: smoke run, not a benchmark number"
 
