@@ -315,7 +315,7 @@ class GPT2Zero(Workload):
                              "the 126 MB L2; no explicit flush",
                        "cuda_graph": impl == "ours" and not args.no_graph,
                        "bucket_mb": args.bucket_mb}
-        if which == 4:
+        if getattr(self, "which", 0) == 4:
             self.config["pipeline"] = self.pipeline
         if args.layers:
             self.config["reduced"] = f"{args.layers} layers: smoke run, not a benchmark number"
@@ -446,7 +446,7 @@ class LlamaHybrid(Workload):
                        if fused else "NCCL all-reduce",
                        "l2": "working set exceeds L2; no explicit flush", "cuda_graph": False,
                        "bucket_mb": args.bucket_mb}
-        if which == 4:
+        if getattr(self, "which", 0) == 4:
             self.config["pipeline"] = self.pipeline
         if args.layers:
             self.config["reduced"] = f"{args.layers} layers: smoke run, not a benchmark number"
