@@ -12,11 +12,12 @@ from ..comm.groups import (GroupInfo as NcclProcessGroup, del_nccl_groups_map_co
                            get_nccl_group_main_world_size, get_nccl_group_mp,
                            get_nccl_group_mp_or_main, get_nccl_groups_map,
                            get_nccl_groups_map_cfg_dict, get_nccl_groups_map_grp_dict, get_rank,
-                           get_world_size)
+                           get_world_size, get_nccl_main_nk, make_pg_by_nc, make_pg_by_nk,
+                           set_nccl_group_main_by_nc, set_nccl_group_main_rank,
+                           set_nccl_group_main_world_size, set_nccl_groups_map)
 
 
-def build_pg_cfg(pg_rank, pg_ranks):
-    return {"pg_rank": pg_rank, "pg_ranks": list(pg_ranks)}
+build_pg_cfg = _G.build_pg_cfg
 
 
 def init_nccl_groups_map(world_size, my_rank, mp_size, dp_size=None, is_worker=True):

@@ -10,3 +10,8 @@ class NodeMixin:
 
 class ServiceMixin:
     pass
+
+
+# the reference's names of the two bases (necklace/rpc/mixinbase.py:4-9)
+SVRMixinBase = NodeMixin
+SVCMixinBase = ServiceMixin

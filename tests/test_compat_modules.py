@@ -165,3 +165,26 @@ def test_matrix_codec_wrappers_take_the_reference_call_shape():
     q.cu_knl_matrix_quantize_e(An, Cn, Rn, 0.3)
     q.cu_knl_matrix_dequantize_e(Bn, Cn, Rn, 0.3)
     assert np.allclose(Bn + Rn, An, atol=1e-6) and Cn.any()
+
+
+def test_small_data_helpers_and_dataset_wrappers():
+    from necklace_b200.data import dtwrp
+    assert dtwrp.is_generator(x for x in []) and not dtwrp.is_generator([])
+    assert dtwrp.is_iterator([]) and not dtwrp.is_iterator(3)
+    assert dtwrp.get_len([1, 2]) == 2
+    with pytest.raises(Exception):
+        dtwrp.get_len(3)
+    a = np.ones(2)
+    assert dtwrp.np_array(a) is a and dtwrp.np_is_ndarray(dtwrp.np_array([1, 2]))
+    assert dtwrp.label_to_onehot([1, 0], (2, 3)).tolist() == [[0, 1, 0], [1, 0, 0]]
+    ds = dtwrp.DatasetWrp([[10, 20, 30], ["a", "b", "c"]])
+    assert len(ds) == 3 and ds[2] == [30, "c"]
+
+    class Direct(dtwrp.DataLoaderBase):
+        def get_batch_by_dbi(self, dbi, dbf=None):
+            return ("direct", list(dbi))
+    w = dtwrp.DataLoaderWrp(Direct(), list(range(8)), rank=1, batch_size=2, kn=2)
+    assert w.get_data_batch_index(1, 1) == [6, 7]             # i*b*k + r*b = 1*2*2 + 1*2
+    assert w.get_data_batch([6, 7]) == ("direct", [6, 7])
+    plain = dtwrp.DataLoaderWrp(None, list(range(8)), rank=0, batch_size=2, kn=2)
+    assert plain.get_data_batch([0, 1], dbf=sum) == 1
