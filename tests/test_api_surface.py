@@ -185,3 +185,31 @@ def test_operator_convenience_methods():
     assert t.try_to_ctx("text") == "text" and t.to_list(3) == [3] and t.to_list((1, 2)) == [1, 2]
     t.cuda_sync()
     assert t.check_if_last_batch() is False
+
+
+def test_import_alias_for_scripts_written_against_the_reference(tmp_path):
+    """``necklace_b200.compat.install()``: ``import necklace...`` resolves to the modules of this
+    package (same objects).  Run in a child process so that the alias does not leak."""
+    import subprocess
+    import sys
+    root = __import__("os").path.dirname(__import__("os").path.dirname(__file__))
+    script = tmp_path / "s.py"
+    script.write_text(
+        "import sys\\n"
+        f"sys.path.insert(0, {root!r})\\n"
+        "import necklace_b200.compat as c\\n"
+        "assert c.install()\\n"
+        "import necklace\\n"
+        "from necklace.trainer import tndszd\\n"
+        "from necklace.cuda import ncclgrp, ncclfns\\n"
+        "from necklace.frmwrk.pytorch.mpnn import layers\\n"
+        "from necklace.utils.argutils import attach_nk_args_parser\\n"
+        "import necklace_b200.trainer.tndszd as real\\n"
+        "assert tndszd is real and necklace.init is sys.modules['necklace_b200'].init\\n"
+        "try:\\n    import necklace.nothing_here\\nexcept ImportError:\\n    pass\\n"
+        "else:\\n    raise SystemExit('a missing module resolved')\\n"
+        "c.uninstall()\\n"
+        "assert 'necklace.trainer' not in sys.modules\\n"
+        "print('alias ok')\\n")
+    r = subprocess.run([sys.executable, str(script)], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0 and "alias ok" in r.stdout, r.stderr[-1500:]
