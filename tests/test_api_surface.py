@@ -195,21 +195,21 @@ def test_import_alias_for_scripts_written_against_the_reference(tmp_path):
     root = __import__("os").path.dirname(__import__("os").path.dirname(__file__))
     script = tmp_path / "s.py"
     script.write_text(
-        "import sys\\n"
-        f"sys.path.insert(0, {root!r})\\n"
-        "import necklace_b200.compat as c\\n"
-        "assert c.install()\\n"
-        "import necklace\\n"
-        "from necklace.trainer import tndszd\\n"
-        "from necklace.cuda import ncclgrp, ncclfns\\n"
-        "from necklace.frmwrk.pytorch.mpnn import layers\\n"
-        "from necklace.utils.argutils import attach_nk_args_parser\\n"
-        "import necklace_b200.trainer.tndszd as real\\n"
-        "assert tndszd is real and necklace.init is sys.modules['necklace_b200'].init\\n"
-        "try:\\n    import necklace.nothing_here\\nexcept ImportError:\\n    pass\\n"
-        "else:\\n    raise SystemExit('a missing module resolved')\\n"
-        "c.uninstall()\\n"
-        "assert 'necklace.trainer' not in sys.modules\\n"
-        "print('alias ok')\\n")
+        "import sys\n"
+        f"sys.path.insert(0, {root!r})\n"
+        "import necklace_b200.compat as c\n"
+        "assert c.install()\n"
+        "import necklace\n"
+        "from necklace.trainer import tndszd\n"
+        "from necklace.cuda import ncclgrp, ncclfns\n"
+        "from necklace.frmwrk.pytorch.mpnn import layers\n"
+        "from necklace.utils.argutils import attach_nk_args_parser\n"
+        "import necklace_b200.trainer.tndszd as real\n"
+        "assert tndszd is real and necklace.init is sys.modules['necklace_b200'].init\n"
+        "try:\n    import necklace.nothing_here\nexcept ImportError:\n    pass\n"
+        "else:\n    raise SystemExit('a missing module resolved')\n"
+        "c.uninstall()\n"
+        "assert 'necklace.trainer' not in sys.modules\n"
+        "print('alias ok')\n")
     r = subprocess.run([sys.executable, str(script)], capture_output=True, text=True, timeout=120)
     assert r.returncode == 0 and "alias ok" in r.stdout, r.stderr[-1500:]
