@@ -48,6 +48,8 @@ def _default(obj):
         return msgpack.ExtType(_EXT_TUPLE, packb(list(obj)))
     if isinstance(obj, (set, frozenset)):
         return sorted(obj)
+    if isinstance(obj, range):           # a list on arrival (what Python 2 scripts meant)
+        return list(obj)
     if ALLOW_PICKLE_FALLBACK:
         return msgpack.ExtType(_EXT_PICKLE, pickle.dumps(obj, protocol=4))
     raise TypeError(f"cannot serialise {type(obj).__name__} for RPC; send plain data, arrays or "

@@ -99,6 +99,11 @@ class Server(NodeMixin):
         return getattr(cli, func)(*args, **kwargs)
 
     # built-in endpoints ------------------------------------------------------
+    def g_sleep(self, n):
+        """Sleep ``n`` seconds (the services' cooperative sleep, also offered on the server:
+        the reference's examples/rl/dssvsc.py calls it there)."""
+        time.sleep(n)
+
     def ping(self):
         return "pong"
 

@@ -210,3 +210,9 @@ def test_input_broadcast_helpers_accept_both_call_shapes(monkeypatch):
     dtdist.dt_sampler_do_nccl_bcast(t, 0, g)
     dtdist.dt_sampler_do_nccl_allreduce(g, 2, 0, t)
     assert seen == [("bc", 1, g), ("bc", 0, g), ("bc", 0, g), ("bc", 1, g), ("bc", 0, g), ("ar", g)]
+
+
+def test_range_travels_as_a_list_and_servers_can_sleep():
+    from necklace_b200.rpc import msgpck, zrpc
+    assert msgpck.unpackb(msgpck.packb({"data": range(4)})) == {"data": [0, 1, 2, 3]}
+    assert hasattr(zrpc.Server, "g_sleep") and hasattr(zrpc.Node, "g_sleep")
