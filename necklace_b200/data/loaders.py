@@ -88,11 +88,18 @@ def _ring_worker(dataset, collate, q_ctl, q_msg, slots, part_num):
 class _LoaderBase:
     _attr_ngn_dataloader = True
 
-    def __init__(self, dataset, batch_size, shuffle=False, sampler=None, last_batch=None,
-                 batch_sampler=None, batchify_fn=None, inter_batchify_fn=None, part_num=4,
-                 num_workers=1, device=None, seed=None, timeout=120.0):
-        if num_workers < 1:
-            raise ValueError("num_workers should be > 0")
+    def __init__(self, dataset, batch_size=None, data_shape=None, shuffle=False, sampler=None,
+                 last_batch=None, batch_sampler=None, batchify_fn=None, inter_batchify_fn=None,
+                 part_num=4, num_workers=1, device=None, seed=None, timeout=120.0):
+        """Argument order and names of the reference's loaders (necklace/data/dtqpto.py:31-38:
+        ``dataset, batch_size, data_shape, shuffle, sampler, last_batch, batch_sampler,
+        batchify_fn, inter_batchify_fn, part_num, num_workers``); ``data_shape`` (shape of one
+        data item) is only needed by the shared-tensor ring, which can also infer it;
+        ``num_workers=0`` (the reference's default) means one loader process."""
+        if num_workers < 0:
+            raise ValueError("num_workers should be >= 0")
+        num_workers = max(1, int(num_workers))
+        self.data_shape = tuple(data_shape) if data_shape is not None else None
         self.dataset, self.batch_size, self.shuffle = dataset, batch_size, shuffle
         self.last_batch = last_batch or "discard"
         self.batchify_fn = batchify_fn
@@ -210,8 +217,8 @@ class ShmRingDataLoader(_LoaderBase):
     """``data_shapes`` = list of ``(shape_without_batch, dtype)`` per tensor of a batch;
     inferred from the first sample when omitted."""
 
-    def __init__(self, dataset, batch_size, data_shape=None, data_shapes=None, **kw):
-        super().__init__(dataset, batch_size, **kw)
+    def __init__(self, dataset, batch_size=None, data_shape=None, data_shapes=None, **kw):
+        super().__init__(dataset, batch_size, data_shape=data_shape, **kw)
         if data_shapes is None:
             sample = self.collate([dataset[0]])
             sample = sample if isinstance(sample, (tuple, list)) else (sample,)
@@ -307,9 +314,9 @@ class ShmObjectRingDataLoader(_LoaderBase):
     (necklace/data/dtmem.py:19-396 over necklace/data/shmem.py); the default collate function
     here returns the list of samples unchanged."""
 
-    def __init__(self, dataset, batch_size, slot_bytes: int = 1 << 20, **kw):
+    def __init__(self, dataset, batch_size=None, data_shape=None, slot_bytes: int = 1 << 20, **kw):
         kw.setdefault("inter_batchify_fn", _samples_as_they_are)
-        super().__init__(dataset, batch_size, **kw)
+        super().__init__(dataset, batch_size, data_shape=data_shape, **kw)
         self.slot_bytes = int(slot_bytes)
 
     def _start(self):

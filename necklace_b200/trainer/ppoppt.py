@@ -29,6 +29,8 @@ from .tnoppt import TrainerOPPytorch, _to_ctx
 
 
 class TrainerMPOPPytorch(TrainerOPPytorch):
+    DEFAULT_TMODE = "pp"
+
     def __init__(self, cfg=None):
         cfg = dict(cfg or {})
         self.net_map = cfg.get("net_map")

@@ -438,8 +438,16 @@ class SVCScheduler(svctmp.TmplService):
         self.stop()
 
     # ---------------------------------------------------------------- programs
+    # The reference has one scheduler class per flavour and picks the protocol by class
+    # (tndsnc: dp, tndsmp / tndspp: pipeline over net_map, tndszr / tndszd: ZeRO); the flavour
+    # modules here subclass with FLAVOUR set, so a script that builds ``tndszr.MPSVCScheduler``
+    # with the reference's default ``nccl_allreduce_typ='grad'`` still gets the ZeRO program.
+    FLAVOUR = None
+
     def make_program(self):
         yield from self.prog_init()
+        if self.FLAVOUR == "zr" and self.typ in ("grad", "weig", None):
+            self.typ = "oozr"
         typ = self.typ
         if typ in ("oozr", "dpzr", "dpzrmp", "zrmp"):
             yield from self.prog_zr()

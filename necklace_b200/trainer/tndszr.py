@@ -5,6 +5,12 @@ from .service import (MPSVCScheduler, MPSVCWorker, MPSVRScheduler, MPSVRWorker, 
                       ILOG_I_MP_SCHEDULER, ILOG_I_MP_WORKER, ILOG_I_ZR_SCHEDULER,
                       ILOG_I_ZR_WORKER)
 
+
+class MPSVCScheduler(MPSVCScheduler):  # noqa: F811
+    """The scheduler of this flavour (see ``service.SVCScheduler.FLAVOUR``)."""
+    FLAVOUR = "zr"
+
+
 # the reference's log channel numbers of this flavour (necklace/trainer/tndszr.py:14-26)
 ILOG_I_MP_SVR_WKR = 600001
 ILOG_I_MP_SVC_WKR = 600002

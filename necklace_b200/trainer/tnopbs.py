@@ -147,6 +147,8 @@ def _free_port() -> int:
 
 
 class TrainerOPBase(ModelWrapperHooks):
+    DEFAULT_TMODE = "dp"
+
     def __init__(self, cfg=None):
         super().__init__(cfg)
         self.kn = self.cfg.get("kn", 1)       # number of workers
@@ -170,8 +172,11 @@ class TrainerOPBase(ModelWrapperHooks):
 
     def init_nccl_comm(self, msg=None, *args, **kwargs):
         nuid = (msg or {}).get("nuid") or {}
+        # no mode given and no group map built by the script: the operator's own flavour (all
+        # workers are one data-parallel group / one pipeline / one ZeRO group, which is what
+        # the reference's single-group examples mean)
         tmode = self.cfg.get("tmode") or (msg or {}).get("tmode") or \
-            (G._S.tmode if G._S.inited else "dp")
+            (G._S.tmode if G._S.inited else self.DEFAULT_TMODE)
         pg_cfg = dict(self.cfg.get("pg_cfg") or {})
         pg_cfg.setdefault("world_size", self.kn)
         pg_cfg.setdefault("my_rank", self.ti)

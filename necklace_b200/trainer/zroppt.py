@@ -38,6 +38,7 @@ from .tnoppt import TrainerOPPytorch, _to_ctx
 
 
 class TrainerMPOPPytorch(TrainerOPPytorch):
+    DEFAULT_TMODE = "zr"
     FLAT = False
 
     def __init__(self, cfg=None):

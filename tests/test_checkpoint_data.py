@@ -279,3 +279,23 @@ def test_shared_tensor_array_in_the_reference_call_shape():
         old.close()
     finally:
         a.unlink()
+
+
+def test_loaders_take_the_reference_constructor_arguments():
+    """``DataLoaderSharedMemory(dataset, batch_size=..., data_shape=..., shuffle=..., last_batch=...,
+    batchify_fn=..., inter_batchify_fn=..., part_num=..., num_workers=0)`` as in the reference's
+    examples/dp/mnist/pytorch/train_ngn_mnist_2_dtpt.py:113-122."""
+    from necklace_b200.data import batchify, dtmptv, dtqpto
+    from necklace_b200.data.dtset import SyntheticDataset
+    ds = SyntheticDataset(24, (1, 4, 4), classes=10, seed=0)
+    for mod in (dtqpto, dtmptv):
+        ld = mod.DataLoaderSharedMemory(ds, batch_size=8, data_shape=(1, 4, 4), shuffle=False,
+                                        last_batch="discard", batchify_fn=batchify.flt2int_bchfn,
+                                        inter_batchify_fn=batchify.pt_batchify_fn, part_num=4,
+                                        num_workers=0)
+        try:
+            batches = list(ld)
+            assert len(batches) == 3 and batches[0][0].shape == (8, 1, 4, 4)
+            assert ld.num_workers == 1 and ld.data_shape == (1, 4, 4)
+        finally:
+            ld.clear()

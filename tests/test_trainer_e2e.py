@@ -338,3 +338,24 @@ def test_job_restarts_from_its_checkpoint_after_a_worker_failure(tmp_path):
     a = json.load(open(plain / "o0.json"))["weights_sum"]
     b = [json.load(open(broken / f"o{r}.json"))["weights_sum"] for r in range(2)]
     assert abs(b[0] - b[1]) < 1e-9 and abs(a - b[0]) < 1e-7, (a, b)
+
+
+def test_flavour_modules_pick_their_protocol_and_default_mode(tmp_path):
+    """A script that builds ``tndszr.MPSVCScheduler`` with the reference's default
+    ``nccl_allreduce_typ='grad'`` gets the ZeRO program (not the data-parallel weight sync),
+    and an operator without ``tmode`` forms one group of its own flavour."""
+    from necklace_b200.trainer import ppoppt, tndsnc, tndspp, tndszd, tndszr, tnoppt, zroppt
+    assert tndszr.MPSVCScheduler.FLAVOUR == "zr" and tndszd.MPSVCScheduler.FLAVOUR == "zr"
+    assert tndspp.MPSVCScheduler.FLAVOUR == "pp" and tndsnc.SVCScheduler.FLAVOUR is None
+    assert (tnoppt.TrainerOPPytorch.DEFAULT_TMODE, ppoppt.TrainerMPOPPytorch.DEFAULT_TMODE,
+            zroppt.TrainerMPOPPytorch.DEFAULT_TMODE) == ("dp", "pp", "zr")
+    ran = []
+    for cls, want in ((tndszr.MPSVCScheduler, "zr:oozr"), (tndsnc.SVCScheduler, "dp:grad")):
+        svc = cls({"url": f"ipc://{tmp_path}/{want[:2]}.ipc", "workers": 1, "epochs": 1,
+                   "nccl_allreduce_typ": "grad"})
+        svc.prog_init = lambda: iter(())
+        svc.prog_zr = lambda s=svc: iter([ran.append("zr:" + s.typ)])
+        svc.prog_dp = lambda s=svc: iter([ran.append("dp:" + s.typ)])
+        list(svc.make_program())
+        svc.svr.stop() if hasattr(svc.svr, "stop") else None
+    assert ran == ["zr:oozr", "dp:grad"]
