@@ -8,6 +8,7 @@ import pytest
 
 SURFACE = {
     "": ["init", "init_mp", "init_nb"],
+    "pympi.api": ["MpiWrp", "rank_size_from_env"],
     "utils.argutils": ["attach_nk_args_parser", "args_remake"],
     "utils.hookbase": ["NklcHookBase"],
     "utils.wrpbase": ["NklcWrapperBase"],

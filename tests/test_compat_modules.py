@@ -188,3 +188,15 @@ def test_small_data_helpers_and_dataset_wrappers():
     assert w.get_data_batch([6, 7]) == ("direct", [6, 7])
     plain = dtwrp.DataLoaderWrp(None, list(range(8)), rank=0, batch_size=2, kn=2)
     assert plain.get_data_batch([0, 1], dbf=sum) == 1
+
+
+def test_launcher_environment_gives_rank_and_size():
+    from necklace_b200.pympi import api
+    assert api.rank_size_from_env({}) == (0, 1, None, None)
+    w = api.MpiWrp({"OMPI_COMM_WORLD_RANK": "3", "OMPI_COMM_WORLD_SIZE": "8",
+                    "OMPI_COMM_WORLD_LOCAL_RANK": "1"})
+    assert (w.rank, w.world_size, w.local_rank, w.launcher) == (3, 8, 1, "OMPI_COMM_WORLD_RANK")
+    assert api.rank_size_from_env({"SLURM_PROCID": "2", "SLURM_NTASKS": "4"})[:3] == (2, 4, None)
+    assert api.rank_size_from_env({"RANK": "1", "WORLD_SIZE": "2", "LOCAL_RANK": "1"})[:3] == (1, 2, 1)
+    a = np.ones(3, dtype=np.float32)
+    assert api.MpiWrp({}).do_all_reduce(a, np.zeros(3, dtype=np.float32)).tolist() == [1, 1, 1]
