@@ -29,6 +29,12 @@ CASES = [
     ("zero/mnist/pytorch/train_mnist_zf_1.py", 3, ["--gpus", "0"], {}),
     ("zero/mnist/pytorch/train_mnist_zr_5_dpzr_2.py", 4,
      ["-g", "0", "-t", "dp+zr", "-dpsz", "2", "-zrsz", "2"], {}),
+    ("pp/mnist/pytorch/train_mnist_pp_33_dppp_grps_n3.py", 6,
+     ["-g", "0", "-t", "dp+pp", "-dpsz", "2", "-ppsz", "3"], {}),
+    ("pp/mnist/pytorch/train_mnist_mp_5_nklc_w3.py", 3, ["--gpus", "0"], {}),
+    ("dp/mnist/pytorch/train_nklc_nccl_mnist_3_mlpmx.py", 2, ["--gpus", "0"], {}),
+    ("zero/mnist/pytorch/train_mnist_zr_8_dpzrmp_3.py", 8,
+     ["-g", "0", "-t", "dp+zr+mp", "-dpsz", "2", "-zrsz", "2", "-mpsz", "2"], {}),
 ]
 
 
