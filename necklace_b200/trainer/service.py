@@ -156,7 +156,9 @@ class SVCWorker(svctmp.TmplService):
         self.svr = SVRWorker(cfg)
         self.rank = self.svr.rank
         self.hb_interval = float(cfg.get("heartbeat", 2.0))
-        self.reg_deadline = time.time() + float(cfg.get("register_timeout", 120))
+        # the scheduler may come up much later than a worker (each process first builds its
+        # copy of the model): keep knocking for half an hour by default
+        self.reg_deadline = time.time() + float(cfg.get("register_timeout", 1800))
         self.exit_status = "running"
         self.q_put_state(Q_STATE_REG)
         self._hb_thread = None
@@ -311,7 +313,7 @@ class Phase:
 class SVCScheduler(svctmp.TmplService):
     """cfg: ``url, workers (count), epochs, nccl_allreduce_typ, net_map, stepwise,
     nccl_groups_grp_map, phase_timeout (600 s), heartbeat_timeout (15 s; 0 = off),
-    register_timeout, start_epoch (epochs a resumed job has already done, see
+    register_timeout (1800 s: the reference waits for registrations without limit), start_epoch (epochs a resumed job has already done, see
     trainer/resume.py)``."""
 
     def __init__(self, cfg):
@@ -325,7 +327,7 @@ class SVCScheduler(svctmp.TmplService):
         # a worker that has sent a heartbeat once and then stays silent this long is taken
         # for dead (workers send one every 2 s by default); 0 switches the check off
         self.hb_timeout = float(cfg.get("heartbeat_timeout", 15))
-        self.reg_deadline = time.time() + float(cfg.get("register_timeout", 300))
+        self.reg_deadline = time.time() + float(cfg.get("register_timeout", 1800))
         self.net_map = cfg.get("net_map")
         self.grp_map = cfg.get("nccl_groups_grp_map") or {}
         self.worker_urls, self.worker_clis = {}, {}
