@@ -26,6 +26,7 @@ What differs:
 """
 from __future__ import annotations
 
+import os
 import threading
 import time
 import traceback
@@ -322,7 +323,9 @@ class SVCScheduler(svctmp.TmplService):
         self.workers_n = int(cfg.get("workers") or cfg.get("wdsz") or 1)
         self.epochs = int(cfg.get("epochs", 1))
         self.typ = cfg.get("nccl_allreduce_typ", "grad")
-        self.stepwise = bool(cfg.get("stepwise", False))
+        # per-phase protocol of the reference instead of one command per epoch; NKB_STEPWISE=1
+        # switches it on for scripts that cannot pass the cfg key
+        self.stepwise = bool(cfg.get("stepwise", os.environ.get("NKB_STEPWISE", "0") == "1"))
         self.phase_timeout = float(cfg.get("phase_timeout", 600))
         # a worker that has sent a heartbeat once and then stays silent this long is taken
         # for dead (workers send one every 2 s by default); 0 switches the check off

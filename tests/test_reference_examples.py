@@ -35,12 +35,22 @@ CASES = [
     ("dp/mnist/pytorch/train_nklc_nccl_mnist_3_mlpmx.py", 2, ["--gpus", "0"], {}),
     ("zero/mnist/pytorch/train_mnist_zr_8_dpzrmp_3.py", 8,
      ["-g", "0", "-t", "dp+zr+mp", "-dpsz", "2", "-zrsz", "2", "-mpsz", "2"], {}),
+    # the same scripts under the reference's per-phase protocol (NKB_STEPWISE=1: one RPC round
+    # per step phase instead of one command per epoch)
+    ("dp/mnist/pytorch/train_ngn_mnist_1.py", 2, ["--gpus", "0", "-x", "nccl"], {"stepwise": True}),
+    ("pp/mnist/pytorch/train_mnist_pp_32_dppp_grps.py", 4,
+     ["-g", "0", "-t", "dp+pp", "-dpsz", "2", "-ppsz", "2"], {"stepwise": True}),
+    ("zero/mnist/pytorch/train_mnist_zr_1.py", 3, ["--gpus", "0"], {"stepwise": True}),
+    ("zero/mnist/pytorch/train_mnist_zr_5_dpzr_2.py", 4,
+     ["-g", "0", "-t", "dp+zr", "-dpsz", "2", "-zrsz", "2"], {"stepwise": True}),
 ]
 
 
 @pytest.mark.skipif(not os.path.isdir(EX), reason="NKB_REFERENCE_EXAMPLES is not set")
 @pytest.mark.timeout(600)
-@pytest.mark.parametrize("rel,world,extra,opts", CASES, ids=[c[0].split("/")[-1] for c in CASES])
+@pytest.mark.parametrize("rel,world,extra,opts", CASES,
+                         ids=[c[0].split("/")[-1] + ("-stepwise" if c[3].get("stepwise") else "")
+                              for c in CASES])
 def test_reference_example_runs_unedited(tmp_path, rel, world, extra, opts):
     script = os.path.join(EX, rel)
     svr = f"ipc://{tmp_path}/s.ipc"
@@ -51,9 +61,11 @@ def test_reference_example_runs_unedited(tmp_path, rel, world, extra, opts):
              "--epochs", "1", "-u", svr, *group]
     if opts.get("mpirun"):
         sched += ["-n", "2"]
-    procs = [subprocess.Popen(sched, stdout=open(tmp_path / "s.log", "w"), stderr=subprocess.STDOUT)]
+    base_env = dict(os.environ, NKB_STEPWISE="1" if opts.get("stepwise") else "0")
+    procs = [subprocess.Popen(sched, stdout=open(tmp_path / "s.log", "w"), stderr=subprocess.STDOUT,
+                              env=base_env)]
     for r in range(world):
-        env = dict(os.environ)
+        env = dict(base_env)
         if opts.get("mpirun"):      # rank and size the way mpirun hands them over
             env.update(OMPI_COMM_WORLD_RANK=str(r), OMPI_COMM_WORLD_SIZE=str(world))
             who, url = ["-k", "0"], f"ipc://{tmp_path}/w@{{LOCAL_RANK}}.ipc"
