@@ -214,3 +214,40 @@ def test_import_alias_for_scripts_written_against_the_reference(tmp_path):
         "print('alias ok')\n")
     r = subprocess.run([sys.executable, str(script)], capture_output=True, text=True, timeout=120)
     assert r.returncode == 0 and "alias ok" in r.stdout, r.stderr[-1500:]
+
+
+def test_alias_path_needs_no_edit_and_reaches_spawned_processes(tmp_path):
+    """``PYTHONPATH=$(python -m necklace_b200.compat --path)``: ``import necklace`` is this package
+    in the main process and in a process it spawns."""
+    import os
+    import subprocess
+    import sys
+    from necklace_b200 import compat
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = tmp_path / "s.py"
+    script.write_text(
+        "import multiprocessing as mp\n\n\n"
+        "def child(q):\n"
+        "    from necklace.rpc import ilog\n"
+        "    import necklace_b200.rpc.ilog as r\n"
+        "    q.put(ilog is r)\n\n\n"
+        "if __name__ == '__main__':\n"
+        "    import necklace\n"
+        "    from necklace.trainer import tndszd\n"
+        "    import necklace_b200\n"
+        "    import necklace_b200.trainer.tndszd as real\n"
+        "    assert necklace is necklace_b200 and tndszd is real\n"
+        "    ctx = mp.get_context('spawn')\n"
+        "    q = ctx.Queue()\n"
+        "    p = ctx.Process(target=child, args=(q,))\n"
+        "    p.start()\n"
+        "    assert q.get(timeout=120) is True\n"
+        "    p.join()\n"
+        "    print('alias path ok')\n")
+    env = dict(os.environ, PYTHONPATH=os.pathsep.join([compat.alias_path(), root]))
+    r = subprocess.run([sys.executable, str(script)], capture_output=True, text=True, timeout=300,
+                       env=env, cwd=str(tmp_path))
+    assert r.returncode == 0 and "alias path ok" in r.stdout, r.stderr[-1500:]
+    out = subprocess.run([sys.executable, "-m", "necklace_b200.compat", "--path"],
+                         capture_output=True, text=True, cwd=root, timeout=120)
+    assert out.stdout.strip() == compat.alias_path()
