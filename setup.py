@@ -36,7 +36,8 @@ setup(
     description="Hybrid-parallel training framework with hand-written sm_100a kernels and "
                 "peer-memory collectives; API of lancelee82/necklace",
     packages=find_packages(include=["necklace_b200", "necklace_b200.*"]),
-    package_data={"necklace_b200": ["csrc/*.cu", "csrc/*.cuh", "csrc/*.h", "*.so"]},
+    package_data={"necklace_b200": ["csrc/*.cu", "csrc/*.cuh", "csrc/*.h", "*.so",
+                                   "_alias/necklace/*.py"]},
     python_requires=">=3.10",
     install_requires=["torch", "numpy", "pyzmq", "msgpack"],
     cmdclass={"build_py": BuildWithNative},
